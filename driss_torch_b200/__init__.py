@@ -1,0 +1,118 @@
+"""B200-native FP8 / MX quantization ops behind the ``torch.ops.DrissTorch`` API.
+
+Drop-in for the quantization part of ``driss_torch`` (driss_torch/__init__.py:20-47,
+:114-122): same function names, positional order, defaults and return types;
+``import driss_torch_b200 as driss_torch`` is the whole migration for that path.
+
+Importing loads ``lib/libdriss_torch.so`` (the ``TORCH_LIBRARY(DrissTorch)``
+registration, which pulls in the CUDA kernels in ``lib/libdtq_b200.so``) and the
+fake-tensor implementations.  There is no CPU implementation and no fallback: if the
+libraries have not been built (``python -m driss_torch_b200.build``) the import fails.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+_LIB_DIR = Path(__file__).resolve().parent / "lib"
+lib_path = _LIB_DIR / "libdriss_torch.so"
+kernels_lib_path = _LIB_DIR / "libdtq_b200.so"
+
+if not lib_path.exists() or not kernels_lib_path.exists():
+    raise ImportError(
+        f"{lib_path.name} / {kernels_lib_path.name} not found in {_LIB_DIR}: build them with "
+        "`python -m driss_torch_b200.build` (needs nvcc with sm_100a support); there is no fallback path"
+    )
+
+torch.ops.load_library(str(lib_path))
+torch.ops.import_module("driss_torch_b200.abstract_impls")
+
+ops = torch.ops.DrissTorch
+Tensor = torch.Tensor
+
+
+def saturated_cast(
+    x: Tensor,
+    scale: Tensor,
+    out_dtype: torch.dtype,
+    transpose: bool = False,
+) -> Tensor:
+    """``fp8(x * scale)`` with saturation to the largest finite fp8 value.
+
+    Args:
+        x: 2-D bf16 or fp32 CUDA tensor.
+        scale: a one-element fp32 tensor on the same device (it is read on the device).
+        out_dtype: ``torch.float8_e4m3fn`` or ``torch.float8_e5m2``.
+        transpose: must be False.
+    For bf16 input the scale is rounded to bf16 and the product is a bf16 multiply, as in the
+    reference kernel (src/saturated_cast.cu:66,81).
+    """
+    assert not transpose, "Transpose is not supported yet"
+    return ops.saturated_cast(x, scale, out_dtype, transpose)
+
+
+def amax(x: Tensor) -> Tensor:
+    """``max(abs(x))`` as an fp32 tensor of shape [1]."""
+    return ops.amax(x)
+
+
+def dynamic_scaled_quant(inpt: Tensor, dtype: torch.dtype) -> Tensor:
+    """Tensor-wise amax -> scale -> fp8 cast in one launch; returns the fp8 tensor."""
+    return ops.dynamic_scaled_quant(inpt, dtype)
+
+
+def mx_fp8_quantize(
+    input: Tensor,
+    block_size: int = 32,
+    axis: int = 1,
+    transpose: bool = False,
+    ScalarType: torch.dtype = torch.float8_e4m3fn,
+) -> tuple[Tensor, Tensor]:
+    """bf16 [M, N] -> (e4m3 payload [M, N], E8M0 scales [M * N / 32]), blocks of 32 along N."""
+    return ops.mx_fp8_quantize(input, block_size, axis, transpose, ScalarType)
+
+
+# The north-star text calls the MX op "mx_cast"; the reference symbol is mx_fp8_quantize.
+mx_cast = mx_fp8_quantize
+
+
+# ---- additions (no counterpart in the reference) ------------------------------------------------
+
+def dynamic_scaled_quant_with_scale(inpt: Tensor, dtype: torch.dtype) -> tuple[Tensor, Tensor, Tensor]:
+    """As ``dynamic_scaled_quant`` but also returns ``amax`` [1] and the fp32 ``scale`` [1].
+
+    The payload is computed from the double-precision scale, not from the returned fp32 one.
+    """
+    return ops.dynamic_scaled_quant_with_scale(inpt, dtype)
+
+
+def dynamic_scaled_quant_rowwise(inpt: Tensor, dtype: torch.dtype) -> tuple[Tensor, Tensor, Tensor]:
+    """Per-row amax -> scale -> fp8 cast; returns (payload, amax [M,1], scale [M,1])."""
+    return ops.dynamic_scaled_quant_rowwise(inpt, dtype)
+
+
+def cast_with_amax(inpt: Tensor, amax_value: Tensor, dtype: torch.dtype) -> tuple[Tensor, Tensor]:
+    """The cast phase of ``dynamic_scaled_quant`` for a given device-resident amax; returns (payload, scale)."""
+    return ops.cast_with_amax(inpt, amax_value, dtype)
+
+
+def check_device_status() -> None:
+    """Synchronises and raises if a kernel's bounded device-side wait ever gave up."""
+    ops.check_device_status()
+
+
+from .sharded import ShardedQuantizer  # noqa: E402
+
+__all__ = [
+    "saturated_cast",
+    "amax",
+    "dynamic_scaled_quant",
+    "mx_fp8_quantize",
+    "mx_cast",
+    "dynamic_scaled_quant_with_scale",
+    "dynamic_scaled_quant_rowwise",
+    "cast_with_amax",
+    "check_device_status",
+    "ShardedQuantizer",
+]

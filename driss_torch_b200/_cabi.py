@@ -1,0 +1,154 @@
+"""ctypes view of ``lib/libdtq_b200.so`` -- the C ABI declared in ``include/dtq_b200.h``.
+
+This is how a host that is not PyTorch binds the kernels (raw device pointers, sizes and a
+stream).  The GPU parity tests and the benchmark call the kernels through it; the wrappers
+below only unwrap ``data_ptr()`` of CUDA tensors and raise on a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libdtq_b200.so"
+
+BF16, F32 = 0, 1
+E4M3, E5M2 = 0, 1
+IN_CODE = {torch.bfloat16: BF16, torch.float32: F32}
+OUT_CODE = {torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2}
+
+_vp, _i64, _i32, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_size_t
+
+SIGNATURES = {
+    "dtq_status_string": ([_i32], C.c_char_p),
+    "dtq_version": ([], C.c_char_p),
+    "dtq_workspace_bytes": ([], _sz),
+    "dtq_workspace_init": ([_vp, _sz, _vp], _i32),
+    "dtq_workspace_status": ([_vp, _vp, _vp], _i32),
+    "dtq_saturated_cast": ([_vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
+    "dtq_amax": ([_vp, _vp, _i64, _i32, _vp, _sz, _vp], _i32),
+    "dtq_dynamic_scaled_quant": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp, _sz, _vp], _i32),
+    "dtq_cast_with_amax": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
+    "dtq_dynamic_scaled_quant_rowwise": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
+    "dtq_mx_fp8_quantize": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the kernel library (no GPU needed to load it) and declares every prototype."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(f"{LIB_PATH} not built: run `python -m driss_torch_b200.build`")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (argtypes, restype) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
+        _lib = lib
+    return _lib
+
+
+class DtqError(RuntimeError):
+    def __init__(self, what: str, status: int):
+        self.status = status
+        super().__init__(f"{what} failed: {load().dtq_status_string(status).decode()} (status {status})")
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise DtqError(what, status)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+_workspaces: dict = {}
+
+
+def workspace(device=None) -> torch.Tensor:
+    """A zero-initialised workspace for the current stream of ``device`` (cached)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device.index, _stream())
+    ws = _workspaces.get(key)
+    if ws is None:
+        lib = load()
+        ws = torch.empty(lib.dtq_workspace_bytes(), dtype=torch.uint8, device=device)
+        check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), _stream()), "dtq_workspace_init")
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_status(ws: torch.Tensor) -> int:
+    out = C.c_int(0)
+    check(load().dtq_workspace_status(ws.data_ptr(), C.addressof(out), _stream()), "dtq_workspace_status")
+    return out.value
+
+
+def saturated_cast(x: torch.Tensor, scale: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None = None):
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
+    check(
+        load().dtq_saturated_cast(x.data_ptr(), out.data_ptr(), scale.data_ptr(), x.numel(), IN_CODE[x.dtype],
+                                  OUT_CODE[out_dtype], _stream()),
+        "dtq_saturated_cast",
+    )
+    return out
+
+
+def amax(x: torch.Tensor, out: torch.Tensor | None = None, ws: torch.Tensor | None = None):
+    out = torch.empty(1, dtype=torch.float32, device=x.device) if out is None else out
+    ws = workspace(x.device) if ws is None else ws
+    check(
+        load().dtq_amax(x.data_ptr(), out.data_ptr(), x.numel(), IN_CODE[x.dtype], ws.data_ptr(), ws.numel(), _stream()),
+        "dtq_amax",
+    )
+    return out
+
+
+def dynamic_scaled_quant(x, out_dtype, out=None, amax_out=None, scale_out=None, ws=None):
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
+    ws = workspace(x.device) if ws is None else ws
+    check(
+        load().dtq_dynamic_scaled_quant(x.data_ptr(), out.data_ptr(), _ptr(amax_out), _ptr(scale_out), x.numel(),
+                                        IN_CODE[x.dtype], OUT_CODE[out_dtype], ws.data_ptr(), ws.numel(), _stream()),
+        "dtq_dynamic_scaled_quant",
+    )
+    return out
+
+
+def cast_with_amax(x, amax_value, out_dtype, out=None, scale_out=None):
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
+    check(
+        load().dtq_cast_with_amax(x.data_ptr(), out.data_ptr(), amax_value.data_ptr(), _ptr(scale_out), x.numel(),
+                                  IN_CODE[x.dtype], OUT_CODE[out_dtype], _stream()),
+        "dtq_cast_with_amax",
+    )
+    return out
+
+
+def dynamic_scaled_quant_rowwise(x, out_dtype, out=None, amax_out=None, scale_out=None):
+    rows, cols = x.shape
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
+    check(
+        load().dtq_dynamic_scaled_quant_rowwise(x.data_ptr(), out.data_ptr(), _ptr(amax_out), _ptr(scale_out), rows,
+                                                cols, IN_CODE[x.dtype], OUT_CODE[out_dtype], _stream()),
+        "dtq_dynamic_scaled_quant_rowwise",
+    )
+    return out
+
+
+def mx_fp8_quantize(x, payload=None, scales=None):
+    rows, cols = x.shape
+    payload = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device) if payload is None else payload
+    scales = torch.empty(rows * (cols // 32), dtype=torch.float8_e8m0fnu, device=x.device) if scales is None else scales
+    check(load().dtq_mx_fp8_quantize(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, _stream()),
+          "dtq_mx_fp8_quantize")
+    return payload, scales

@@ -1,0 +1,49 @@
+"""Fake-tensor (meta) implementations for ``torch.ops.DrissTorch``.
+
+The first two repeat the reference's registrations (driss_torch/abstract_impls.py:5-19);
+the reference registers none for ``dynamic_scaled_quant`` and ``mx_fp8_quantize``, which
+makes them untraceable under ``torch.compile``; they are added here together with the
+fakes of the new ops.
+"""
+import torch
+from torch.library import register_fake
+
+
+@register_fake("DrissTorch::saturated_cast")
+def saturated_cast_meta(x: torch.Tensor, scale: torch.Tensor, out_dtype: torch.dtype, transpose: bool = False):
+    return torch.empty_like(x, dtype=out_dtype)
+
+
+@register_fake("DrissTorch::amax")
+def amax_meta(x: torch.Tensor):
+    return torch.empty(1, dtype=torch.float32, device=x.device)
+
+
+@register_fake("DrissTorch::dynamic_scaled_quant")
+def dynamic_scaled_quant_meta(x: torch.Tensor, dtype: torch.dtype):
+    return torch.empty_like(x, dtype=dtype)
+
+
+@register_fake("DrissTorch::mx_fp8_quantize")
+def mx_fp8_quantize_meta(x: torch.Tensor, block_size: int, axis: int, transpose: bool, fp8_type: torch.dtype):
+    m, n = x.shape
+    payload = torch.empty_like(x, dtype=fp8_type)
+    scales = torch.empty(m * ((n + 31) // 32), dtype=torch.float8_e8m0fnu, device=x.device)
+    return payload, scales
+
+
+@register_fake("DrissTorch::dynamic_scaled_quant_with_scale")
+def dynamic_scaled_quant_with_scale_meta(x: torch.Tensor, dtype: torch.dtype):
+    one = lambda: torch.empty(1, dtype=torch.float32, device=x.device)  # noqa: E731
+    return torch.empty_like(x, dtype=dtype), one(), one()
+
+
+@register_fake("DrissTorch::dynamic_scaled_quant_rowwise")
+def dynamic_scaled_quant_rowwise_meta(x: torch.Tensor, dtype: torch.dtype):
+    col = lambda: torch.empty(x.shape[0], 1, dtype=torch.float32, device=x.device)  # noqa: E731
+    return torch.empty_like(x, dtype=dtype), col(), col()
+
+
+@register_fake("DrissTorch::cast_with_amax")
+def cast_with_amax_meta(x: torch.Tensor, amax: torch.Tensor, dtype: torch.dtype):
+    return torch.empty_like(x, dtype=dtype), torch.empty(1, dtype=torch.float32, device=x.device)

@@ -1,0 +1,144 @@
+// amax: out[0] = max |in[i]| as fp32, finished grid-wide in a single launch.
+//
+// Replaces src/amax.cu:50-80 (+ the -inf fill launch at :115): a persistent grid streams the
+// input with several 128-bit loads in flight per thread, reduces with packed bf16 max, one
+// integer warp-max instruction per warp, and a last-block finish instead of one same-address
+// atomic per block on a pre-filled output.  The value is order independent, so the result is
+// bit-identical; NaNs are dropped and an empty input gives -inf, as in the reference.
+#include <cmath>
+
+#include "dtq_device.cuh"
+#include "dtq_grid.cuh"
+#include "dtq_host.h"
+
+namespace dtq {
+
+#ifndef DTQ_AMAX_UNROLL
+#define DTQ_AMAX_UNROLL 8
+#endif
+#ifndef DTQ_AMAX_BLOCKS_PER_SM
+#define DTQ_AMAX_BLOCKS_PER_SM 4
+#endif
+constexpr int kAmaxThreads = 512;
+
+template <int IN>
+struct AbsMax;
+
+template <>
+struct AbsMax<DTQ_BF16> {
+  static constexpr int kElemBytes = 2;
+  __nv_bfloat162 a, b;
+  __device__ explicit AbsMax(float identity) { a = b = __float2bfloat162_rn(identity); }
+  __device__ void chunk(uint4 v) {
+    a = absmax_bf162(a, v.x);
+    b = absmax_bf162(b, v.y);
+    a = absmax_bf162(a, v.z);
+    b = absmax_bf162(b, v.w);
+  }
+  __device__ void one(const void *p, int64_t i) {
+    const uint32_t h = static_cast<const uint16_t *>(p)[i];
+    a = absmax_bf162(a, h | (h << 16));
+  }
+  __device__ float result() const { return bf162_hmax_to_float(__hmax2(a, b)); }
+};
+
+template <>
+struct AbsMax<DTQ_F32> {
+  static constexpr int kElemBytes = 4;
+  float a, b;
+  __device__ explicit AbsMax(float identity) { a = b = identity; }
+  __device__ void chunk(uint4 v) {
+    a = fmaxf(a, fabsf(__uint_as_float(v.x)));
+    b = fmaxf(b, fabsf(__uint_as_float(v.y)));
+    a = fmaxf(a, fabsf(__uint_as_float(v.z)));
+    b = fmaxf(b, fabsf(__uint_as_float(v.w)));
+  }
+  __device__ void one(const void *p, int64_t i) { a = fmaxf(a, fabsf(static_cast<const float *>(p)[i])); }
+  __device__ float result() const { return fmaxf(a, b); }
+};
+
+// Streams chunks [0, nchunks) of `body` grid-stride in tiles of blockDim.x * UNROLL chunks.
+template <int IN, int UNROLL>
+__device__ __forceinline__ void absmax_stream(AbsMax<IN> &acc, const uint4 *__restrict__ body, int64_t nchunks) {
+  const int64_t tile_chunks = int64_t(blockDim.x) * UNROLL;
+  for (int64_t tile = blockIdx.x; tile * tile_chunks < nchunks; tile += gridDim.x) {
+    const int64_t first = tile * tile_chunks + threadIdx.x;
+    uint4 v[UNROLL];
+    if ((tile + 1) * tile_chunks <= nchunks) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) v[u] = ldg_stream(body + first + int64_t(u) * blockDim.x);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) acc.chunk(v[u]);
+    } else {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int64_t c = first + int64_t(u) * blockDim.x;
+        if (c < nchunks) acc.chunk(ldg_stream(body + c));
+      }
+    }
+  }
+}
+
+// `in` may have any element alignment: up to `head` leading and `tail` trailing elements are
+// read one by one by block 0, the 16-byte aligned middle is streamed.
+template <int IN, int UNROLL>
+__global__ void __launch_bounds__(kAmaxThreads)
+amax_kernel(const void *__restrict__ in, float *__restrict__ out, int64_t numel, int64_t head, Workspace *ws) {
+  __shared__ float smem32[32];
+  __shared__ int flag;
+  constexpr int kElems = 16 / AbsMax<IN>::kElemBytes;
+  const float identity = -INFINITY;
+  AbsMax<IN> acc(identity);
+
+  const char *base = static_cast<const char *>(in);
+  const int64_t nchunks = (numel - head) / kElems;
+  absmax_stream<IN, UNROLL>(acc, reinterpret_cast<const uint4 *>(base + head * AbsMax<IN>::kElemBytes), nchunks);
+  if (blockIdx.x == 0) {
+    const int64_t tail0 = head + nchunks * kElems;
+    if (threadIdx.x < head) acc.one(in, threadIdx.x);
+    if (tail0 + threadIdx.x < numel) acc.one(in, tail0 + threadIdx.x);
+  }
+
+  const float block_value = block_max_nonneg(acc.result(), smem32, identity);
+  if (publish_and_ticket(ws, block_value, &flag)) {
+    const float total = reduce_partials(ws, smem32, identity);
+    if (threadIdx.x == 0) {
+      out[0] = total;
+      ws->arrivals = 0;
+    }
+  }
+}
+
+int amax_grid(int64_t numel, int elem_bytes, const DeviceInfo &dev) {
+  const int64_t tiles = ceil_div64(numel * elem_bytes / 16, int64_t(kAmaxThreads) * DTQ_AMAX_UNROLL);
+  const int64_t max_grid = int64_t(dev.sm_count) * DTQ_AMAX_BLOCKS_PER_SM;
+  return static_cast<int>(tiles < 1 ? 1 : (tiles < max_grid ? tiles : max_grid));
+}
+
+int64_t head_elems(const void *p, int elem_bytes, int64_t numel) {
+  const int64_t h = static_cast<int64_t>((16 - (reinterpret_cast<uintptr_t>(p) & 15)) & 15) / elem_bytes;
+  return h < numel ? h : numel;
+}
+
+}  // namespace dtq
+
+extern "C" int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype, void *workspace,
+                        size_t workspace_bytes, void *stream) {
+  using namespace dtq;
+  if (numel < 0 || !out || (numel > 0 && !in)) return DTQ_ERR_INVALID_ARGUMENT;
+  if (in_dtype != DTQ_BF16 && in_dtype != DTQ_F32) return DTQ_ERR_UNSUPPORTED_DTYPE;
+  if (!workspace || workspace_bytes < sizeof(Workspace) || !aligned_to(workspace, 256)) return DTQ_ERR_WORKSPACE;
+  const int eb = in_dtype == DTQ_BF16 ? 2 : 4;
+  if (numel > 0 && !aligned_to(in, eb)) return DTQ_ERR_INVALID_ARGUMENT;
+  DeviceInfo dev;
+  if (int e = current_device_info(&dev)) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Workspace *ws = static_cast<Workspace *>(workspace);
+  const int grid = amax_grid(numel, eb, dev);
+  const int64_t head = head_elems(in, eb, numel);
+  if (in_dtype == DTQ_BF16)
+    amax_kernel<DTQ_BF16, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+  else
+    amax_kernel<DTQ_F32, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+  return cuda_status(cudaGetLastError());
+}

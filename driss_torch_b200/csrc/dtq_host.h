@@ -1,0 +1,45 @@
+// Host-side helpers shared by the launchers: status mapping, per-device facts, the workspace
+// layout that kernels and launchers agree on.
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/dtq_b200.h"
+
+namespace dtq {
+
+constexpr int kMaxGridBlocks = 4096;  // upper bound on any persistent grid (148 SMs x 16 CTAs fits)
+
+// Scratch shared by the single-launch reductions.  Zero-filled once by dtq_workspace_init;
+// every kernel leaves `arrivals` at zero again and only ever advances `generation`.
+struct alignas(256) Workspace {
+  unsigned int arrivals;    // blocks that have published their partial in the current launch
+  unsigned int generation;  // bumped by the last-arriving block; waiters spin on it (bounded)
+  int status;               // sticky: DTQ_ERR_TIMEOUT if a bounded wait ever gave up
+  float amax;               // the reduced value of the current launch, valid after the bump
+  unsigned int pad[60];
+  float partials[kMaxGridBlocks];
+};
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cooperative = 0;
+};
+
+// Facts about the current device, queried once per device and cached (thread-safe).
+int current_device_info(DeviceInfo *info);
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? DTQ_OK : DTQ_ERR_CUDA_BASE + static_cast<int>(e); }
+
+#define DTQ_CUDA_TRY(expr)                             \
+  do {                                                 \
+    cudaError_t _e = (expr);                           \
+    if (_e != cudaSuccess) return dtq::cuda_status(_e); \
+  } while (0)
+
+inline bool aligned_to(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+}  // namespace dtq

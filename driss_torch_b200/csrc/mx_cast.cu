@@ -1,0 +1,131 @@
+// mx_fp8_quantize: bf16 -> (e4m3 payload, one E8M0 scale per 32 consecutive elements).
+//
+// Replaces src/mx_cast.cu:44-86, :96-161 (a 128x32 tile per CTA through shared memory, one
+// element per thread, 16 block-wide syncs).  Because blocks run along the contiguous last
+// dimension and cols % 32 == 0, the matrix is a flat array of 64-byte blocks, so this is a
+// pure stream: each lane loads 16 bytes (8 elements), four neighbouring lanes form one MX
+// block and agree on its exponent with two shuffles, each lane stores its 8 payload bytes
+// with one instruction, and a warp emits the 32 scale bytes of the 2 KB it covered as one
+// contiguous 32-byte store.  Nothing is staged in shared memory and there are no block syncs.
+//
+// Arithmetic (identical to the reference): e_i = ceil(log2 |x_i|) from the exponent field
+// (+1 if the mantissa is non-zero; zero -> -128, subnormal -> -126); E = max e_i;
+// biased = clamp(E - 8 + 127, 0, 255); scale = 2^(biased-127) (0.0 for biased == 0, +inf for
+// 255); payload = e4m3_satfinite(x * rcp(scale)); scale byte = ue8m0(scale) rounded up,
+// saturating (255 -> 0xFE).  e is monotone in |x|, so the block max is taken on the raw
+// 15-bit magnitudes with packed 16-bit integer max.
+#include "dtq_device.cuh"
+#include "dtq_host.h"
+
+namespace dtq {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;  // tied to the scale-byte mapping below: lane&3 picks the iteration
+
+// Largest 15-bit magnitude among the eight bf16 of a chunk.
+__device__ __forceinline__ uint32_t chunk_absmax_bits(uint4 v) {
+  const uint32_t m = __vmaxu2(__vmaxu2(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu),
+                              __vmaxu2(v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu));
+  return max(m & 0xFFFFu, m >> 16);
+}
+
+// Biased exponent of the block scale from the block's largest magnitude bits.
+__device__ __forceinline__ int block_biased_exponent(uint32_t mag) {
+  const int be = static_cast<int>(mag >> 7);
+  int e = be - 127 + ((mag & 0x7Fu) != 0);
+  if (be == 0) e = (mag == 0) ? -128 : -126;
+  return min(255, max(0, e - 8 + 127));
+}
+
+__device__ __forceinline__ uint32_t mx_pair(uint32_t w, float inv) {
+  return cvt_fp8x2<DTQ_E4M3>(__fmul_rn(bf16_lo(w), inv), __fmul_rn(bf16_hi(w), inv));
+}
+
+__device__ __forceinline__ uint2 mx_payload(uint4 v, float inv) {
+  uint2 r;
+  r.x = mx_pair(v.x, inv) | (mx_pair(v.y, inv) << 16);
+  r.y = mx_pair(v.z, inv) | (mx_pair(v.w, inv) << 16);
+  return r;
+}
+
+// nchunks = numel / 8 is a multiple of 4.  A warp owns kUnroll consecutive 512-byte rows of
+// chunks; a CTA tile is kThreads * kUnroll chunks.
+__global__ void __launch_bounds__(kThreads)
+mx_stream_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
+                 int64_t nchunks) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int64_t kTile = int64_t(kThreads) * kUnroll;
+  for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
+    const int64_t warp_first = tile * kTile + int64_t(warp) * (32 * kUnroll);
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t c = warp_first + u * 32 + lane;
+      v[u] = c < nchunks ? ldg_stream(in + c) : make_uint4(0, 0, 0, 0);
+    }
+    uint32_t my_scale_byte = 0;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      uint32_t mag = chunk_absmax_bits(v[u]);
+      mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 1));
+      mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
+      const int biased = block_biased_exponent(mag);
+      const float scale = __int_as_float(biased << 23);
+      const float inv = __frcp_rn(scale);
+      const int64_t c = warp_first + u * 32 + lane;
+      if (c < nchunks) stg_stream(payload + c * 8, mx_payload(v[u], inv));
+      if ((lane & 3) == u) my_scale_byte = cvt_ue8m0(scale);
+    }
+    // lane = 4*k + j holds the scale of block (u = j, quad k): block index u*8 + k in the warp's span.
+    const int64_t blk = warp_first / 4 + (lane & 3) * 8 + (lane >> 2);
+    if (blk * 4 < nchunks) scales[blk] = static_cast<uint8_t>(my_scale_byte);
+  }
+}
+
+// Any alignment: one thread per MX block.
+__global__ void __launch_bounds__(kThreads)
+mx_scalar_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
+                 int64_t nblocks) {
+  for (int64_t b = int64_t(blockIdx.x) * kThreads + threadIdx.x; b < nblocks; b += int64_t(gridDim.x) * kThreads) {
+    const uint16_t *x = in + b * 32;
+    uint32_t mag = 0;
+    for (int i = 0; i < 32; ++i) mag = max(mag, uint32_t(x[i]) & 0x7FFFu);
+    const int biased = block_biased_exponent(mag);
+    const float scale = __int_as_float(biased << 23);
+    const float inv = __frcp_rn(scale);
+    for (int i = 0; i < 32; ++i)
+      payload[b * 32 + i] = cvt_fp8<DTQ_E4M3>(__fmul_rn(__uint_as_float(uint32_t(x[i]) << 16), inv));
+    scales[b] = cvt_ue8m0(scale);
+  }
+}
+
+}  // namespace
+}  // namespace dtq
+
+extern "C" int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, int64_t rows, int64_t cols,
+                                   void *stream) {
+  using namespace dtq;
+  if (rows < 0 || cols < 0) return DTQ_ERR_INVALID_ARGUMENT;
+  if (cols % 32 != 0) return DTQ_ERR_SHAPE;
+  const int64_t numel = rows * cols;
+  if (numel == 0) return DTQ_OK;
+  if (!in_bf16 || !payload || !scales_e8m0 || !aligned_to(in_bf16, 2)) return DTQ_ERR_INVALID_ARGUMENT;
+  DeviceInfo dev;
+  if (int e = current_device_info(&dev)) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t max_grid = int64_t(dev.sm_count) * 8;
+  if (aligned_to(in_bf16, 16) && aligned_to(payload, 8)) {
+    const int64_t nchunks = numel / 8;
+    const int64_t tiles = ceil_div64(nchunks, int64_t(kThreads) * kUnroll);
+    const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
+    mx_stream_kernel<<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in_bf16), static_cast<uint8_t *>(payload),
+                                                static_cast<uint8_t *>(scales_e8m0), nchunks);
+  } else {
+    const int64_t blocks = ceil_div64(numel / 32, kThreads);
+    const int grid = static_cast<int>(blocks < max_grid ? blocks : max_grid);
+    mx_scalar_kernel<<<grid, kThreads, 0, st>>>(static_cast<const uint16_t *>(in_bf16), static_cast<uint8_t *>(payload),
+                                                static_cast<uint8_t *>(scales_e8m0), numel / 32);
+  }
+  return cuda_status(cudaGetLastError());
+}

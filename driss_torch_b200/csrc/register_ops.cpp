@@ -1,0 +1,233 @@
+// PyTorch operator boundary: TORCH_LIBRARY(DrissTorch) over the torch-free C ABI.
+//
+// This is the only translation unit that sees torch headers.  It keeps the reference's
+// operator names and schema strings for the quantization path (src/register_ops.cpp:20-30,
+// :40-41), its argument checks and error behaviour (src/saturated_cast.cu:227-252,
+// src/amax.cu:106-119, src/dynamic_scaled_quant.cu:157-176, src/mx_cast.cu:168-246), CUDA-only
+// dispatch (no CPU kernel, no autograd formula), and adds three ops the reference lacks.  Unlike
+// the reference it launches on the current stream of the input's device.
+//
+// Each op: check -> allocate outputs with the caching allocator -> one C-ABI call.  Nothing
+// here computes.
+#include <ATen/ATen.h>
+#include <c10/core/DispatchKey.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include <mutex>
+#include <tuple>
+#include <unordered_map>
+
+#include "dtq_b200.h"
+
+namespace {
+
+void check_status(int status, const char *what) {
+  TORCH_CHECK(status == DTQ_OK, what, " failed: ", dtq_status_string(status), " (status ", status, ")");
+}
+
+int in_code(at::ScalarType t) { return t == at::kBFloat16 ? DTQ_BF16 : DTQ_F32; }
+int out_code(at::ScalarType t) { return t == at::kFloat8_e4m3fn ? DTQ_E4M3 : DTQ_E5M2; }
+
+void check_fp8(at::ScalarType dtype) {
+  TORCH_CHECK(dtype == at::kFloat8_e4m3fn || dtype == at::kFloat8_e5m2,
+              "Output tensor must be of type Float8_e4m3fn or Float8_e5m2");
+}
+void check_input(const at::Tensor &input) {
+  TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
+  TORCH_CHECK(input.scalar_type() == at::kBFloat16 || input.scalar_type() == at::kFloat,
+              "Input tensor must be of type BFloat16 or Float, but got ", input.dtype());
+  TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D, but got ", input.dim());
+}
+
+// One zero-initialised workspace per (device, stream): launches on one stream are ordered, so
+// they can share it; launches on different streams may overlap and must not.
+struct WorkspaceCache {
+  std::mutex mutex;
+  std::unordered_map<uint64_t, at::Tensor> map;
+  void *get(const c10::cuda::CUDAStream &stream) {
+    const uint64_t key = (static_cast<uint64_t>(stream.device_index()) << 48) ^ static_cast<uint64_t>(stream.id());
+    std::lock_guard<std::mutex> lock(mutex);
+    auto it = map.find(key);
+    if (it == map.end()) {
+      at::Tensor t = at::zeros({static_cast<int64_t>(dtq_workspace_bytes())},
+                               at::TensorOptions().dtype(at::kByte).device(at::kCUDA, stream.device_index()));
+      it = map.emplace(key, std::move(t)).first;
+    }
+    return it->second.data_ptr();
+  }
+  // Synchronises; raises if any workspace recorded a device-side timeout.
+  void check_all() {
+    std::lock_guard<std::mutex> lock(mutex);
+    for (auto &kv : map) {
+      c10::cuda::CUDAGuard guard(kv.second.device());
+      int status = 0;
+      check_status(dtq_workspace_status(kv.second.data_ptr(), &status, nullptr), "dtq_workspace_status");
+      TORCH_CHECK(status == DTQ_OK, "a quantization kernel reported: ", dtq_status_string(status));
+    }
+  }
+};
+WorkspaceCache &workspaces() {
+  static WorkspaceCache *cache = new WorkspaceCache();  // leaked on purpose: outlives CUDA teardown
+  return *cache;
+}
+
+// ---- reference ops --------------------------------------------------------------------------------
+
+at::Tensor saturated_cast(const at::Tensor &input, const at::Tensor &scale, at::ScalarType dtype, bool transpose) {
+  check_fp8(dtype);
+  check_input(input);
+  TORCH_CHECK(scale.scalar_type() == at::kFloat, "Scale tensor must be of type Float, but got ", scale.dtype());
+  TORCH_CHECK(scale.numel() == 1, "Scale tensor must be a scalar, but got ", scale.numel());
+  TORCH_CHECK(scale.is_cuda() && scale.device() == input.device(), "Scale tensor must live on the input's device");
+  TORCH_CHECK(!transpose, "transpose=True is not supported");
+  // The op is elementwise over storage: row-major or exactly transposed inputs at storage offset
+  // zero are processed in place and the output keeps their strides; anything else is made
+  // contiguous first (same rule as the reference).
+  const auto strides = input.strides();
+  const bool transposed = strides[0] == 1 && strides[1] == input.size(0);
+  const bool as_is = (input.is_contiguous() || transposed) && input.storage_offset() == 0;
+  const at::Tensor x = as_is ? input : input.contiguous();
+  at::Tensor out = at::empty_like(x, x.options().dtype(dtype));
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_saturated_cast(x.data_ptr(), out.data_ptr(), scale.data_ptr<float>(), x.numel(),
+                                  in_code(x.scalar_type()), out_code(dtype), stream.stream()),
+               "saturated_cast");
+  return out;
+}
+
+at::Tensor amax(const at::Tensor &input) {
+  check_input(input);
+  // max is order independent, so any dense layout can be reduced over its storage.
+  const at::Tensor x = input.is_non_overlapping_and_dense() ? input : input.contiguous();
+  at::Tensor out = at::empty({1}, x.options().dtype(at::kFloat));
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_amax(x.data_ptr(), out.data_ptr<float>(), x.numel(), in_code(x.scalar_type()),
+                        workspaces().get(stream), dtq_workspace_bytes(), stream.stream()),
+               "amax");
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> dynamic_scaled_quant_with_scale(const at::Tensor &input,
+                                                                                at::ScalarType dtype) {
+  check_fp8(dtype);
+  check_input(input);
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  at::Tensor out = at::empty_like(input, input.options().dtype(dtype));
+  at::Tensor amax_value = at::empty({1}, input.options().dtype(at::kFloat));
+  at::Tensor scale = at::empty({1}, input.options().dtype(at::kFloat));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_dynamic_scaled_quant(input.data_ptr(), out.data_ptr(), amax_value.data_ptr<float>(),
+                                        scale.data_ptr<float>(), input.numel(),
+                                        in_code(input.scalar_type()), out_code(dtype), workspaces().get(stream),
+                                        dtq_workspace_bytes(), stream.stream()),
+               "dynamic_scaled_quant");
+  return {out, amax_value, scale};
+}
+
+at::Tensor dynamic_scaled_quant(const at::Tensor &input, at::ScalarType dtype) {
+  check_fp8(dtype);
+  check_input(input);
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  at::Tensor out = at::empty_like(input, input.options().dtype(dtype));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_dynamic_scaled_quant(input.data_ptr(), out.data_ptr(), nullptr, nullptr, input.numel(),
+                                        in_code(input.scalar_type()), out_code(dtype), workspaces().get(stream),
+                                        dtq_workspace_bytes(), stream.stream()),
+               "dynamic_scaled_quant");
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize(at::Tensor input, int64_t block_size, int64_t axis, bool transpose,
+                                                   c10::ScalarType fp8_type) {
+  TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D");
+  // The reference accepts more here and then ignores it (it always reads bf16, blocks of 32 along
+  // the last dimension, and writes e4m3); those combinations are rejected instead of mis-computed.
+  TORCH_CHECK(input.scalar_type() == at::kBFloat16, "Input tensor must be bfloat16, but got ", input.dtype());
+  TORCH_CHECK(block_size == 32, "Block size must be 32, but got ", block_size);
+  TORCH_CHECK(axis == 1 || axis == -1, "Blocks run along the last dimension (axis=1), but got axis=", axis);
+  TORCH_CHECK(!transpose, "transpose=True is not supported");
+  TORCH_CHECK(fp8_type == at::kFloat8_e4m3fn, "FP8 type must be Float8_e4m3fn");
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(n % 32 == 0, "The last dimension must be a multiple of the block size 32, but got ", n);
+  at::Tensor out = at::empty_like(input, input.options().dtype(fp8_type));
+  at::Tensor scale = at::empty({m * (n / 32)}, input.options().dtype(at::kFloat8_e8m0fnu));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_mx_fp8_quantize(input.data_ptr(), out.data_ptr(), scale.data_ptr(), m, n, stream.stream()),
+               "mx_fp8_quantize");
+  return {out, scale};
+}
+
+// ---- additions ---------------------------------------------------------------------------------------
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> dynamic_scaled_quant_rowwise(const at::Tensor &input,
+                                                                             at::ScalarType dtype) {
+  check_fp8(dtype);
+  check_input(input);
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(m == 0 || n > 0, "Rows must not be empty");
+  at::Tensor out = at::empty_like(input, input.options().dtype(dtype));
+  at::Tensor amax_rows = at::empty({m, 1}, input.options().dtype(at::kFloat));
+  at::Tensor scale_rows = at::empty({m, 1}, input.options().dtype(at::kFloat));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_dynamic_scaled_quant_rowwise(input.data_ptr(), out.data_ptr(), amax_rows.data_ptr<float>(),
+                                                scale_rows.data_ptr<float>(), m, n, in_code(input.scalar_type()),
+                                                out_code(dtype), stream.stream()),
+               "dynamic_scaled_quant_rowwise");
+  return {out, amax_rows, scale_rows};
+}
+
+std::tuple<at::Tensor, at::Tensor> cast_with_amax(const at::Tensor &input, const at::Tensor &amax_value,
+                                                  at::ScalarType dtype) {
+  check_fp8(dtype);
+  check_input(input);
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  TORCH_CHECK(amax_value.scalar_type() == at::kFloat && amax_value.numel() == 1 && amax_value.is_cuda() &&
+                  amax_value.device() == input.device(),
+              "amax must be one fp32 value on the input's device");
+  at::Tensor out = at::empty_like(input, input.options().dtype(dtype));
+  at::Tensor scale = at::empty({1}, input.options().dtype(at::kFloat));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_cast_with_amax(input.data_ptr(), out.data_ptr(), amax_value.data_ptr<float>(),
+                                  scale.data_ptr<float>(), input.numel(), in_code(input.scalar_type()),
+                                  out_code(dtype), stream.stream()),
+               "cast_with_amax");
+  return {out, scale};
+}
+
+void check_device_status() { workspaces().check_all(); }
+
+}  // namespace
+
+TORCH_LIBRARY(DrissTorch, m) {
+  m.set_python_module("driss_torch_b200.abstract_impls");
+  // the reference's schemas, verbatim
+  m.def("saturated_cast(Tensor input, Tensor scale, ScalarType dtype, bool transpose) -> Tensor");
+  m.impl("saturated_cast", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast));
+  m.def("amax(Tensor input) -> Tensor");
+  m.impl("amax", c10::DispatchKey::CUDA, TORCH_FN(amax));
+  m.def("dynamic_scaled_quant(Tensor input, ScalarType dtype) -> Tensor");
+  m.impl("dynamic_scaled_quant", c10::DispatchKey::CUDA, TORCH_FN(dynamic_scaled_quant));
+  m.def("mx_fp8_quantize(Tensor input, int block_size, int axis, bool transpose, ScalarType fp8_type) -> (Tensor, Tensor)");
+  m.impl("mx_fp8_quantize", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize));
+  // additions: the fused op's amax and scale as outputs, the row-wise variant, the cast phase alone
+  m.def("dynamic_scaled_quant_with_scale(Tensor input, ScalarType dtype) -> (Tensor, Tensor, Tensor)");
+  m.impl("dynamic_scaled_quant_with_scale", c10::DispatchKey::CUDA, TORCH_FN(dynamic_scaled_quant_with_scale));
+  m.def("dynamic_scaled_quant_rowwise(Tensor input, ScalarType dtype) -> (Tensor, Tensor, Tensor)");
+  m.impl("dynamic_scaled_quant_rowwise", c10::DispatchKey::CUDA, TORCH_FN(dynamic_scaled_quant_rowwise));
+  m.def("cast_with_amax(Tensor input, Tensor amax, ScalarType dtype) -> (Tensor, Tensor)");
+  m.impl("cast_with_amax", c10::DispatchKey::CUDA, TORCH_FN(cast_with_amax));
+  m.def("check_device_status() -> ()");
+  m.impl("check_device_status", c10::DispatchKey::CompositeExplicitAutograd, TORCH_FN(check_device_status));
+}

@@ -1,0 +1,210 @@
+// Row-wise dynamic quantisation of a contiguous [rows, cols] matrix: per row r
+//   amax_r = max |x[r,:]|;  scale_d = fp8_max / ((double)amax_r + 1e-12);
+//   out[r,c] = fp8_satfinite((float)(scale_d * (double)x[r,c])).
+// The reference has no such op; the arithmetic is its tensor-wise kernel's
+// (src/dynamic_scaled_quant.cu:111-117) applied per row, and the per-row fp32 scales are what
+// its row-wise scaled GEMM consumes (src/sweep_mm.cu:28-40).
+//
+// Single pass over HBM: a row (or a share of it) is loaded into registers with all its 128-bit
+// loads in flight at once, the row maximum is agreed by shuffle (one warp per row) or through
+// shared memory (one CTA per row), and the payload is produced from the registers.  Rows too
+// long for registers (> 32768 bf16 / 16384 fp32 elements) or not 16-byte aligned take a
+// two-pass CTA-per-row kernel whose second read is served by L2.
+#include <cmath>
+
+#include "dtq_device.cuh"
+#include "dtq_host.h"
+
+namespace dtq {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+template <int IN>
+struct RowIn;
+template <>
+struct RowIn<DTQ_BF16> {
+  static constexpr int kElems = 8, kElemBytes = 2;
+  __device__ static float absmax(uint4 v) {
+    __nv_bfloat162 m = __hmax2(__hmax2(as_bf162(v.x & 0x7FFF7FFFu), as_bf162(v.y & 0x7FFF7FFFu)),
+                               __hmax2(as_bf162(v.z & 0x7FFF7FFFu), as_bf162(v.w & 0x7FFF7FFFu)));
+    return fmaxf(__bfloat162float(m.x), __bfloat162float(m.y));
+  }
+  template <int OUT>
+  __device__ static void convert_store(uint4 v, double sd, uint8_t *dst) {
+    uint2 r;
+    r.x = cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.x)), dsq_mul(sd, bf16_hi(v.x))) |
+          (cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.y)), dsq_mul(sd, bf16_hi(v.y))) << 16);
+    r.y = cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.z)), dsq_mul(sd, bf16_hi(v.z))) |
+          (cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.w)), dsq_mul(sd, bf16_hi(v.w))) << 16);
+    stg_stream(dst, r);
+  }
+  __device__ static float load_one(const void *p, int64_t i) {
+    return __uint_as_float(uint32_t(static_cast<const uint16_t *>(p)[i]) << 16);
+  }
+};
+template <>
+struct RowIn<DTQ_F32> {
+  static constexpr int kElems = 4, kElemBytes = 4;
+  __device__ static float absmax(uint4 v) {
+    return fmaxf(fmaxf(fabsf(__uint_as_float(v.x)), fabsf(__uint_as_float(v.y))),
+                 fmaxf(fabsf(__uint_as_float(v.z)), fabsf(__uint_as_float(v.w))));
+  }
+  template <int OUT>
+  __device__ static void convert_store(uint4 v, double sd, uint8_t *dst) {
+    stg_stream(dst, cvt_fp8x4<OUT>(dsq_mul(sd, __uint_as_float(v.x)), dsq_mul(sd, __uint_as_float(v.y)),
+                                   dsq_mul(sd, __uint_as_float(v.z)), dsq_mul(sd, __uint_as_float(v.w))));
+  }
+  __device__ static float load_one(const void *p, int64_t i) { return static_cast<const float *>(p)[i]; }
+};
+
+// TEAM_WARPS warps share a row (1: warp per row, kWarps: CTA per row); each thread holds up to
+// CHUNKS 16-byte chunks of it.  chunks_per_row = cols / kElems <= 32 * TEAM_WARPS * CHUNKS.
+template <int IN, int OUT, int CHUNKS, int TEAM_WARPS>
+__global__ void __launch_bounds__(kThreads)
+rowwise_regs_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float *__restrict__ amax_out,
+                    float *__restrict__ scale_out, int64_t rows, int chunks_per_row) {
+  using R = RowIn<IN>;
+  constexpr int kTeam = 32 * TEAM_WARPS;
+  constexpr int kRowsPerCta = kWarps / TEAM_WARPS;
+  __shared__ float smem32[32];
+  const int team = (threadIdx.x >> 5) / TEAM_WARPS;
+  const int t = threadIdx.x - team * kTeam;
+  const int64_t row = int64_t(blockIdx.x) * kRowsPerCta + team;
+  const bool live = row < rows;
+
+  const uint4 *src = in + row * chunks_per_row;
+  uint4 v[CHUNKS];
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int c = t + j * kTeam;
+    v[j] = (live && c < chunks_per_row) ? ldg_stream(src + c) : make_uint4(0, 0, 0, 0);
+  }
+  float a = 0.0f;
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) a = fmaxf(a, R::absmax(v[j]));
+
+  float amax;
+  if constexpr (TEAM_WARPS == 1) {
+    amax = warp_max_nonneg(a);
+  } else {
+    amax = block_max_nonneg(a, smem32, 0.0f);
+    if (threadIdx.x == 0) smem32[0] = amax;
+    __syncthreads();
+    amax = smem32[0];
+  }
+  if (!live) return;
+  const double sd = dsq_scale<OUT>(amax);
+  if (t == 0) {
+    if (amax_out) amax_out[row] = amax;
+    if (scale_out) scale_out[row] = static_cast<float>(sd);
+  }
+  uint8_t *dst = out + row * chunks_per_row * R::kElems;
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    const int c = t + j * kTeam;
+    if (c < chunks_per_row) R::template convert_store<OUT>(v[j], sd, dst + int64_t(c) * R::kElems);
+  }
+}
+
+// One CTA per row, two passes, any cols and any alignment (VEC = rows are 16-byte aligned and
+// cols is a whole number of chunks).
+template <int IN, int OUT, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+rowwise_looped_kernel(const void *__restrict__ in, uint8_t *__restrict__ out, float *__restrict__ amax_out,
+                      float *__restrict__ scale_out, int64_t rows, int64_t cols) {
+  using R = RowIn<IN>;
+  __shared__ float smem32[32];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const char *src = static_cast<const char *>(in) + row * cols * R::kElemBytes;
+    uint8_t *dst = out + row * cols;
+    float a = 0.0f;
+    if constexpr (VEC) {
+      const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+      for (int64_t c = threadIdx.x; c < cols / R::kElems; c += kThreads) a = fmaxf(a, R::absmax(ldg_keep(s4 + c)));
+    } else {
+      for (int64_t c = threadIdx.x; c < cols; c += kThreads) a = fmaxf(a, fabsf(R::load_one(src, c)));
+    }
+    float amax = block_max_nonneg(a, smem32, 0.0f);
+    __syncthreads();
+    if (threadIdx.x == 0) smem32[0] = amax;
+    __syncthreads();
+    amax = smem32[0];
+    __syncthreads();
+    const double sd = dsq_scale<OUT>(amax);
+    if (threadIdx.x == 0) {
+      if (amax_out) amax_out[row] = amax;
+      if (scale_out) scale_out[row] = static_cast<float>(sd);
+    }
+    if constexpr (VEC) {
+      const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+      for (int64_t c = threadIdx.x; c < cols / R::kElems; c += kThreads)
+        R::template convert_store<OUT>(ldg_stream(s4 + c), sd, dst + c * R::kElems);
+    } else {
+      for (int64_t c = threadIdx.x; c < cols; c += kThreads) dst[c] = cvt_fp8<OUT>(dsq_mul(sd, R::load_one(src, c)));
+    }
+  }
+}
+
+template <int IN, int OUT, int TEAM_WARPS>
+int launch_regs(const void *in, void *out, float *amax_out, float *scale_out, int64_t rows, int chunks_per_row,
+                cudaStream_t st) {
+  constexpr int kTeam = 32 * TEAM_WARPS;
+  constexpr int kRowsPerCta = kWarps / TEAM_WARPS;
+  const int per_thread = (chunks_per_row + kTeam - 1) / kTeam;
+  const unsigned grid = static_cast<unsigned>(ceil_div64(rows, kRowsPerCta));
+  const uint4 *i4 = static_cast<const uint4 *>(in);
+  uint8_t *o = static_cast<uint8_t *>(out);
+#define DTQ_ROW_CASE(N)                                                                                          \
+  rowwise_regs_kernel<IN, OUT, N, TEAM_WARPS><<<grid, kThreads, 0, st>>>(i4, o, amax_out, scale_out, rows, chunks_per_row)
+  if (per_thread <= 1) DTQ_ROW_CASE(1);
+  else if (per_thread <= 2) DTQ_ROW_CASE(2);
+  else if (per_thread <= 4) DTQ_ROW_CASE(4);
+  else if (per_thread <= 8) DTQ_ROW_CASE(8);
+  else DTQ_ROW_CASE(16);
+#undef DTQ_ROW_CASE
+  return cuda_status(cudaGetLastError());
+}
+
+template <int IN, int OUT>
+int launch(const void *in, void *out, float *amax_out, float *scale_out, int64_t rows, int64_t cols,
+           const DeviceInfo &dev, cudaStream_t st) {
+  using R = RowIn<IN>;
+  const bool vec = aligned_to(in, 16) && aligned_to(out, R::kElems) && cols % R::kElems == 0;
+  const int64_t chunks = cols / R::kElems;
+  if (vec && chunks <= 32 * 16) return launch_regs<IN, OUT, 1>(in, out, amax_out, scale_out, rows, int(chunks), st);
+  if (vec && chunks <= kThreads * 16)
+    return launch_regs<IN, OUT, kWarps>(in, out, amax_out, scale_out, rows, int(chunks), st);
+  const int64_t max_grid = int64_t(dev.sm_count) * 8;
+  const unsigned grid = static_cast<unsigned>(rows < max_grid ? rows : max_grid);
+  uint8_t *o = static_cast<uint8_t *>(out);
+  if (vec)
+    rowwise_looped_kernel<IN, OUT, true><<<grid, kThreads, 0, st>>>(in, o, amax_out, scale_out, rows, cols);
+  else
+    rowwise_looped_kernel<IN, OUT, false><<<grid, kThreads, 0, st>>>(in, o, amax_out, scale_out, rows, cols);
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace dtq
+
+extern "C" int dtq_dynamic_scaled_quant_rowwise(const void *in, void *out, float *amax_out, float *scale_out,
+                                                int64_t rows, int64_t cols, int in_dtype, int out_dtype, void *stream) {
+  using namespace dtq;
+  if (rows < 0 || cols < 0) return DTQ_ERR_INVALID_ARGUMENT;
+  if ((in_dtype != DTQ_BF16 && in_dtype != DTQ_F32) || (out_dtype != DTQ_E4M3 && out_dtype != DTQ_E5M2))
+    return DTQ_ERR_UNSUPPORTED_DTYPE;
+  if (rows == 0) return DTQ_OK;
+  if (cols == 0) return DTQ_ERR_SHAPE;
+  if (rows > 0x7FFFFFFFLL * 8) return DTQ_ERR_TOO_LARGE;
+  if (!in || !out || !aligned_to(in, in_dtype == DTQ_BF16 ? 2 : 4)) return DTQ_ERR_INVALID_ARGUMENT;
+  DeviceInfo dev;
+  if (int e = current_device_info(&dev)) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (in_dtype == DTQ_BF16)
+    return out_dtype == DTQ_E4M3 ? launch<DTQ_BF16, DTQ_E4M3>(in, out, amax_out, scale_out, rows, cols, dev, st)
+                                 : launch<DTQ_BF16, DTQ_E5M2>(in, out, amax_out, scale_out, rows, cols, dev, st);
+  return out_dtype == DTQ_E4M3 ? launch<DTQ_F32, DTQ_E4M3>(in, out, amax_out, scale_out, rows, cols, dev, st)
+                               : launch<DTQ_F32, DTQ_E5M2>(in, out, amax_out, scale_out, rows, cols, dev, st);
+}

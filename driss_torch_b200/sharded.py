@@ -1,0 +1,88 @@
+"""Row-sharded quantization of one large matrix over the GPUs of a node.
+
+One process per GPU (``torch.distributed``, NCCL over NVLink/NVSwitch).  Every op on this
+path is independent per element, per 32-element block or per row, so rank ``g`` simply
+runs the single-GPU kernels on its rows; the one cross-rank dependency is the tensor-wise
+amax, a single fp32 that is max-all-reduced between the amax kernel and the cast kernel.
+``max`` of non-negative floats is exact and order independent, so the sharded payload is
+bit-identical to the single-GPU payload of the concatenated matrix.
+
+The reference has no multi-GPU path; the per-shard arithmetic is its kernels'
+(src/amax.cu:50-80, src/dynamic_scaled_quant.cu:111-117, src/mx_cast.cu:44-86,:131-155).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(rows: int, world_size: int, rank: int, multiple: int = 1) -> Tuple[int, int]:
+    """Rows ``[start, stop)`` owned by ``rank``: contiguous, in rank order, sizes a multiple of
+    ``multiple`` except possibly the last non-empty shard, and as even as that allows."""
+    if rows < 0 or world_size <= 0 or not (0 <= rank < world_size) or multiple <= 0:
+        raise ValueError("invalid sharding request")
+    units = -(-rows // multiple)  # ceil
+    base, extra = divmod(units, world_size)
+    first_unit = rank * base + min(rank, extra)
+    n_units = base + (1 if rank < extra else 0)
+    start = min(rows, first_unit * multiple)
+    stop = min(rows, (first_unit + n_units) * multiple)
+    return start, stop
+
+
+class _CudaKernels:
+    """The product kernels; resolved lazily so that importing this module needs no GPU."""
+
+    def __getattr__(self, name):
+        import driss_torch_b200 as pkg
+
+        return getattr(pkg, name)
+
+
+class ShardedQuantizer:
+    """Quantizes this rank's row shard of a matrix that is row-sharded over ``group``.
+
+    ``kernels`` supplies ``amax``, ``cast_with_amax``, ``mx_fp8_quantize`` and
+    ``dynamic_scaled_quant_rowwise``; it defaults to this package's CUDA ops and exists so
+    that the host logic can be exercised on CPU ranks with another implementation.
+    """
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, kernels=None):
+        self.group = group
+        self.kernels = _CudaKernels() if kernels is None else kernels
+
+    @property
+    def world_size(self) -> int:
+        return dist.get_world_size(self.group) if dist.is_initialized() else 1
+
+    @property
+    def rank(self) -> int:
+        return dist.get_rank(self.group) if dist.is_initialized() else 0
+
+    def global_amax(self, shard: torch.Tensor) -> torch.Tensor:
+        """max |x| over every rank's shard, as fp32 [1] on the shard's device (one collective)."""
+        local = self.kernels.amax(shard)
+        # an empty shard contributes -inf; clamp so that it cannot win the reduction
+        local = torch.clamp_min(local, 0.0)
+        if self.world_size > 1:
+            dist.all_reduce(local, op=dist.ReduceOp.MAX, group=self.group)
+        return local
+
+    def tensorwise(self, shard: torch.Tensor, dtype: torch.dtype):
+        """Tensor-wise dynamic quantisation of the whole sharded matrix.
+
+        Returns ``(payload_shard, amax[1], scale[1])``; amax and scale are global.
+        """
+        amax = self.global_amax(shard)
+        payload, scale = self.kernels.cast_with_amax(shard, amax, dtype)
+        return payload, amax, scale
+
+    def mx(self, shard: torch.Tensor):
+        """MX block-32 cast of this rank's rows; no communication."""
+        return self.kernels.mx_fp8_quantize(shard)
+
+    def rowwise(self, shard: torch.Tensor, dtype: torch.dtype):
+        """Row-wise dynamic quantisation of this rank's rows; no communication."""
+        return self.kernels.dynamic_scaled_quant_rowwise(shard, dtype)

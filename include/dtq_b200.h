@@ -1,0 +1,129 @@
+/*
+ * dtq_b200 -- C ABI of the B200 (sm_100a) FP8 / MX quantization kernels.
+ *
+ * This is the boundary a host binding talks to.  It is what the reference's
+ * C++ host functions `driss_torch::<op>(at::Tensor...)` do below their tensor
+ * checks (validate, pick a launch shape, launch), with torch types replaced by
+ * plain device pointers and sizes.  Every pointer is a DEVICE pointer unless a
+ * name ends in `_host`.  Nothing here allocates, synchronises the host, or
+ * throws: every call enqueues work on `stream` of the CURRENT device and
+ * returns a status (0 = ok, see dtq_status_string).  `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).
+ *
+ * Arithmetic is bit-exact with the reference CUDA kernels; the citations give
+ * the reference function each entry point replaces (paths inside the
+ * drisspg/driss_torch checkout).
+ */
+#ifndef DTQ_B200_H
+#define DTQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define DTQ_BF16 0
+#define DTQ_F32 1
+#define DTQ_E4M3 0 /* float8_e4m3fn */
+#define DTQ_E5M2 1 /* float8_e5m2   */
+
+/* status codes */
+#define DTQ_OK 0
+#define DTQ_ERR_INVALID_ARGUMENT 1
+#define DTQ_ERR_UNSUPPORTED_DTYPE 2
+#define DTQ_ERR_SHAPE 3
+#define DTQ_ERR_WORKSPACE 4
+#define DTQ_ERR_TIMEOUT 5 /* a bounded device-side wait gave up (see dtq_workspace_status) */
+#define DTQ_ERR_TOO_LARGE 6
+#define DTQ_ERR_CUDA_BASE 1000 /* 1000 + cudaError_t */
+
+const char *dtq_status_string(int status);
+
+/* Library version and the GPU architecture the kernels were built for ("sm_100a"). */
+const char *dtq_version(void);
+
+/*
+ * Workspace.  amax and the fused ops finish their grid-wide reduction in the
+ * same launch through a small scratch area (per-block partials, an arrival
+ * counter, a barrier generation word and a status word).  The caller owns it:
+ * allocate dtq_workspace_bytes() bytes of device memory (256-byte aligned),
+ * call dtq_workspace_init once (a memset on `stream`), then pass it to any
+ * number of calls.  Calls that may overlap on the GPU (different streams) need
+ * different workspaces.  The kernels leave it ready for the next call.
+ */
+size_t dtq_workspace_bytes(void);
+int dtq_workspace_init(void *workspace, size_t workspace_bytes, void *stream);
+/* Copies the sticky device-side status word to the host (synchronises `stream`). */
+int dtq_workspace_status(const void *workspace, int *status_host, void *stream);
+
+/*
+ * out[i] = fp8_satfinite(in[i] * scale), i < numel, over flat storage.
+ * bf16 input: scale is rounded to bf16 and the product is a bf16 multiply
+ * (one rounding), as in the reference; fp32 input: fp32 multiply.
+ * `scale` points to one fp32 on the device (no host read).
+ * Replaces driss_torch::saturated_cast / dispatch_best_kernel and its three
+ * kernels: src/saturated_cast.cu:38-57, :59-104, :106-153, :168-252.
+ */
+int dtq_saturated_cast(const void *in, void *out, const float *scale, int64_t numel, int in_dtype,
+                       int out_dtype, void *stream);
+
+/*
+ * out[0] = max_i |in[i]| as fp32 (-inf for numel == 0; NaNs are dropped), one
+ * launch, no pre-initialised output.
+ * Replaces driss_torch::amax and amax_kernel: src/amax.cu:50-80, :82-119.
+ */
+int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype, void *workspace,
+             size_t workspace_bytes, void *stream);
+
+/*
+ * Fused tensor-wise dynamic quantisation in ONE launch:
+ *   amax = max |in| (>= 0);  scale_d = fp8_max / ((double)amax + 1e-12);
+ *   out[i] = fp8_satfinite((float)(scale_d * (double)in[i])).
+ * amax_out / scale_out (one fp32 each, nullable) receive amax and
+ * (float)scale_d.  bf16 and fp32 inputs.
+ * Replaces driss_torch::dynamic_scaled_quant and its cooperative kernel:
+ * src/dynamic_scaled_quant.cu:83-118, :119-176.
+ */
+int dtq_dynamic_scaled_quant(const void *in, void *out, float *amax_out, float *scale_out,
+                             int64_t numel, int in_dtype, int out_dtype, void *workspace,
+                             size_t workspace_bytes, void *stream);
+
+/*
+ * Cast phase alone, for an amax that already exists on the device (a sharded
+ * tensor after its max all-reduce): same arithmetic as the second half of
+ * dtq_dynamic_scaled_quant (src/dynamic_scaled_quant.cu:111-117).
+ * `amax` points to one fp32 on the device; scale_out is nullable.
+ */
+int dtq_cast_with_amax(const void *in, void *out, const float *amax, float *scale_out,
+                       int64_t numel, int in_dtype, int out_dtype, void *stream);
+
+/*
+ * Row-wise dynamic quantisation of a contiguous [rows, cols] matrix: the
+ * arithmetic of dtq_dynamic_scaled_quant applied to each row with that row's
+ * amax.  amax_out / scale_out hold `rows` fp32 each (nullable).  Single pass:
+ * a row is read from HBM once.  No counterpart op in the reference; the
+ * arithmetic is src/dynamic_scaled_quant.cu:111-117 per row, the scales are
+ * what its row-wise GEMM consumes (src/sweep_mm.cu:28-40).
+ */
+int dtq_dynamic_scaled_quant_rowwise(const void *in, void *out, float *amax_out, float *scale_out,
+                                     int64_t rows, int64_t cols, int in_dtype, int out_dtype,
+                                     void *stream);
+
+/*
+ * MX block cast of a contiguous bf16 [rows, cols] matrix, cols % 32 == 0:
+ * per 32 consecutive elements one E8M0 scale byte (row-major [rows, cols/32])
+ * and 32 e4m3 payload bytes.
+ * Replaces driss_torch::mx_fp8_quantize and mx_fp8_quantize_kernel:
+ * src/mx_cast.cu:44-86, :96-161, :168-246.  Unlike the reference, rows need
+ * not be a multiple of 128.
+ */
+int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, int64_t rows,
+                        int64_t cols, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DTQ_B200_H */

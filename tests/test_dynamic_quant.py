@@ -1,0 +1,182 @@
+"""Fused tensor-wise dynamic quantisation parity (GPU): reference grid
+(test/test_dynamic_quant.py:28-44, fp32) extended to bf16, extra outputs, the cast phase
+alone, and the row-wise variant."""
+import pytest
+import torch
+
+from conftest import FP8_DTYPES, IN_DTYPES, assert_fp8_equal
+from driss_torch_b200 import workloads
+from oracle import eager
+from oracle import quant_oracle as qo
+
+pytestmark = pytest.mark.gpu
+
+ROWS = [3, 64, 512, 4096]
+COLS = [7, 17, 127, 512, 3212, 4097]
+
+
+def _bits(t):
+    return t.detach().cpu().view(torch.int32).flatten().tolist()
+
+
+@pytest.mark.parametrize("num_rows", ROWS)
+@pytest.mark.parametrize("num_cols", COLS)
+@pytest.mark.parametrize("fp8_dtype", FP8_DTYPES)
+@pytest.mark.parametrize("in_dtype", IN_DTYPES)
+def test_fused(num_rows, num_cols, in_dtype, fp8_dtype):
+    from driss_torch_b200 import _cabi
+
+    g = torch.Generator().manual_seed(num_rows * 7919 + num_cols)
+    a = torch.rand(num_rows, num_cols, generator=g).to(in_dtype)
+    want, want_amax, want_scale = qo.dynamic_scaled_quant(a, fp8_dtype)
+    ad = a.cuda()
+    amax_out = torch.full((1,), -1.0, device="cuda")
+    scale_out = torch.full((1,), -1.0, device="cuda")
+    got = _cabi.dynamic_scaled_quant(ad, fp8_dtype, amax_out=amax_out, scale_out=scale_out)
+    assert_fp8_equal(got, want, fp8_dtype, "fused")
+    assert _bits(amax_out) == _bits(want_amax) and _bits(scale_out) == _bits(want_scale)
+    # second call on the same workspace; nullable extras
+    assert_fp8_equal(_cabi.dynamic_scaled_quant(ad, fp8_dtype), want, fp8_dtype, "fused again")
+
+
+@pytest.mark.parametrize("fp8_dtype", FP8_DTYPES)
+@pytest.mark.parametrize("in_dtype", IN_DTYPES)
+def test_ops_and_signed_outlier_data(in_dtype, fp8_dtype):
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg2(rows=2048, cols=2048).to(in_dtype)
+    want, want_amax, want_scale = qo.dynamic_scaled_quant(a, fp8_dtype)
+    ad = a.cuda()
+    out = dt.dynamic_scaled_quant(ad, fp8_dtype)
+    assert out.dtype == fp8_dtype and out.shape == a.shape
+    assert_fp8_equal(out, want, fp8_dtype, "op")
+    p, am, sc = dt.dynamic_scaled_quant_with_scale(ad, fp8_dtype)
+    assert_fp8_equal(p, want, fp8_dtype, "op with scale")
+    assert _bits(am) == _bits(want_amax) and _bits(sc) == _bits(want_scale)
+    # eager double-precision formula agrees with the oracle on this data
+    assert_fp8_equal(eager.dynamic_scaled_quant_eager(a, fp8_dtype), want, fp8_dtype, "eager")
+    # cast phase alone, from the amax op
+    p2, sc2 = dt.cast_with_amax(ad, dt.amax(ad), fp8_dtype)
+    assert_fp8_equal(p2, want, fp8_dtype, "amax + cast")
+    assert _bits(sc2) == _bits(want_scale)
+
+
+@pytest.mark.parametrize("fp8_dtype", FP8_DTYPES)
+def test_every_bf16_bit_pattern_through_the_cast_phase(fp8_dtype):
+    from driss_torch_b200 import _cabi
+
+    a = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).view(256, 256)
+    for amax in (1.0, 3.3, 1e-30, 65000.0, 0.0):
+        want, want_scale = qo.cast_with_amax(a, amax, fp8_dtype)
+        scale_out = torch.zeros(1, device="cuda")
+        got = _cabi.cast_with_amax(a.cuda(), torch.tensor([amax], device="cuda"), fp8_dtype, scale_out=scale_out)
+        assert_fp8_equal(got, want, fp8_dtype, f"amax={amax}")
+        assert _bits(scale_out) == _bits(want_scale)
+
+
+@pytest.mark.parametrize("in_dtype", IN_DTYPES)
+def test_fp32_rounding_boundaries(in_dtype):
+    # products that land on or next to fp8 midpoints: the double product and its single
+    # narrowing to fp32 decide the byte
+    from driss_torch_b200 import _cabi
+
+    g = torch.Generator().manual_seed(3)
+    grid = torch.arange(0, 449, dtype=torch.float32) / 448.0  # amax 1 -> scale ~448: products near integers
+    near = torch.cat([grid, torch.nextafter(grid, torch.tensor(2.0)), torch.nextafter(grid, torch.tensor(-1.0)),
+                      torch.rand(100_000, generator=g), torch.tensor([1.0])])
+    a = near[: near.numel() // 2 * 2].view(2, -1).to(in_dtype).contiguous()
+    for fp8_dtype in FP8_DTYPES:
+        want, _, _ = qo.dynamic_scaled_quant(a, fp8_dtype)
+        assert_fp8_equal(_cabi.dynamic_scaled_quant(a.cuda(), fp8_dtype), want, fp8_dtype, "boundaries")
+
+
+@pytest.mark.parametrize("in_dtype", IN_DTYPES)
+def test_all_zero_and_tiny_inputs(in_dtype):
+    from driss_torch_b200 import _cabi
+
+    for a in (torch.zeros(8, 64), torch.full((8, 64), 1e-38), torch.full((3, 5), -2.0)):
+        a = a.to(in_dtype)
+        want, want_amax, want_scale = qo.dynamic_scaled_quant(a, torch.float8_e4m3fn)
+        amax_out, scale_out = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+        got = _cabi.dynamic_scaled_quant(a.cuda(), torch.float8_e4m3fn, amax_out=amax_out, scale_out=scale_out)
+        assert_fp8_equal(got, want, torch.float8_e4m3fn, "degenerate")
+        assert _bits(amax_out) == _bits(want_amax) and _bits(scale_out) == _bits(want_scale)
+
+
+@pytest.mark.parametrize("in_dtype", IN_DTYPES)
+@pytest.mark.parametrize("numel,offset", [(1, 0), (9, 0), (4099, 0), (100_003, 0), (10_000, 1), (10_000, 3)])
+def test_ragged_and_misaligned(in_dtype, numel, offset):
+    from driss_torch_b200 import _cabi
+
+    g = torch.Generator().manual_seed(numel + offset)
+    base = torch.randn(numel + 8, generator=g).to(in_dtype)
+    a = base[offset : offset + numel].view(1, numel)
+    want, _, _ = qo.dynamic_scaled_quant(a.contiguous(), torch.float8_e4m3fn)
+    buf = torch.full((numel + 16,), 0x5A, dtype=torch.uint8, device="cuda")
+    out = buf[offset : offset + numel].view(torch.float8_e4m3fn).view(1, numel)
+    _cabi.dynamic_scaled_quant(base.cuda()[offset : offset + numel].view(1, numel), torch.float8_e4m3fn, out=out)
+    assert_fp8_equal(out, want, torch.float8_e4m3fn, "ragged")
+    assert (buf[:offset] == 0x5A).all() and (buf[offset + numel :] == 0x5A).all()
+
+
+def test_larger_than_one_wave():
+    # enough tiles that every block runs several and the reverse-order second pass is exercised
+    from driss_torch_b200 import _cabi
+
+    a = workloads.make_cfg2(rows=4096, cols=8192)
+    want, want_amax, _ = qo.dynamic_scaled_quant(a, torch.float8_e4m3fn)
+    amax_out = torch.zeros(1, device="cuda")
+    got = _cabi.dynamic_scaled_quant(a.cuda(), torch.float8_e4m3fn, amax_out=amax_out)
+    assert_fp8_equal(got, want, torch.float8_e4m3fn, "multi-wave")
+    assert _bits(amax_out) == _bits(want_amax)
+    assert _cabi.workspace_status(_cabi.workspace()) == 0
+
+
+def test_errors_and_compile():
+    import driss_torch_b200 as dt
+
+    a = torch.rand(64, 64, device="cuda")
+    with pytest.raises(RuntimeError):
+        dt.dynamic_scaled_quant(a, torch.float16)
+    with pytest.raises(RuntimeError):
+        dt.dynamic_scaled_quant(a.t(), torch.float8_e4m3fn)  # must be contiguous, as in the reference
+    with pytest.raises(RuntimeError):
+        dt.dynamic_scaled_quant(a.view(-1), torch.float8_e4m3fn)
+    torch._dynamo.reset()
+    fn = torch.compile(dt.dynamic_scaled_quant, fullgraph=True, backend="aot_eager")
+    assert_fp8_equal(fn(a, torch.float8_e4m3fn), dt.dynamic_scaled_quant(a, torch.float8_e4m3fn))
+    dt.check_device_status()
+
+
+# ---- row-wise ---------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (5, 64), (33, 256), (64, 4096), (17, 4104), (9, 8192), (4, 32768),
+                                       (3, 40000), (7, 127), (6, 3212), (2, 65536 + 24)])
+@pytest.mark.parametrize("fp8_dtype", FP8_DTYPES)
+@pytest.mark.parametrize("in_dtype", IN_DTYPES)
+def test_rowwise(rows, cols, in_dtype, fp8_dtype):
+    from driss_torch_b200 import _cabi
+
+    a = workloads.make_cfg4(rows=rows, cols=cols).to(in_dtype)
+    want, want_amax, want_scale = qo.dynamic_scaled_quant_rowwise(a, fp8_dtype)
+    amax_out = torch.full((rows, 1), -1.0, device="cuda")
+    scale_out = torch.full((rows, 1), -1.0, device="cuda")
+    got = _cabi.dynamic_scaled_quant_rowwise(a.cuda(), fp8_dtype, amax_out=amax_out, scale_out=scale_out)
+    assert_fp8_equal(got, want, fp8_dtype, "rowwise")
+    assert _bits(amax_out) == _bits(want_amax) and _bits(scale_out) == _bits(want_scale)
+
+
+def test_rowwise_op_cfg4_slice_and_zero_rows():
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg4(rows=2048, cols=4096)
+    a[5] = 0
+    a[77] = -0.0
+    want, want_amax, want_scale = qo.dynamic_scaled_quant_rowwise(a, torch.float8_e4m3fn)
+    p, am, sc = dt.dynamic_scaled_quant_rowwise(a.cuda(), torch.float8_e4m3fn)
+    assert am.shape == (2048, 1) and sc.shape == (2048, 1)
+    assert_fp8_equal(p, want, torch.float8_e4m3fn, "rowwise op")
+    assert _bits(am) == _bits(want_amax) and _bits(sc) == _bits(want_scale)
+    e_p, e_am, e_sc = eager.dynamic_scaled_quant_rowwise_eager(a, torch.float8_e4m3fn)
+    assert_fp8_equal(e_p, want, torch.float8_e4m3fn, "rowwise eager")
+    assert _bits(e_am) == _bits(want_amax) and _bits(e_sc) == _bits(want_scale)

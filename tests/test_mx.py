@@ -1,0 +1,145 @@
+"""mx_fp8_quantize parity (GPU) on the reference test's sizes (test/test_mx.py:70-94) and on
+the degenerate blocks the reference arithmetic defines (zero / tiny / non-finite)."""
+import pytest
+import torch
+
+from conftest import as_bytes, assert_fp8_equal
+from driss_torch_b200 import workloads
+from oracle import eager
+from oracle import quant_oracle as qo
+
+pytestmark = pytest.mark.gpu
+
+E4M3 = torch.float8_e4m3fn
+SIZES = [(128, 32), (256, 32), (8192, 32), (128, 64), (128, 128), (128, 8192), (256, 64), (256, 128), (8192, 8192)]
+
+
+def _check(a, what):
+    from driss_torch_b200 import _cabi
+
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    p, s = _cabi.mx_fp8_quantize(a.cuda())
+    assert_fp8_equal(p, want_p, E4M3, what + " payload")
+    assert torch.equal(as_bytes(s), as_bytes(want_s)), what + " scales"
+    return p, s
+
+
+@pytest.mark.parametrize("size", SIZES, ids=lambda s: f"{s[0]}x{s[1]}")
+def test_mx_cast(size):
+    import driss_torch_b200 as dt
+
+    g = torch.Generator().manual_seed(size[0] + size[1])
+    a = torch.rand(size, generator=g).to(torch.bfloat16)
+    _check(a, "rand")
+    data, scale = dt.mx_fp8_quantize(a.cuda())
+    assert data.dtype == E4M3 and data.shape == a.shape
+    assert scale.dtype == torch.float8_e8m0fnu and scale.shape == (size[0] * size[1] // 32,)
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    assert_fp8_equal(data, want_p, E4M3, "op payload")
+    assert torch.equal(as_bytes(scale), as_bytes(want_s))
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 32), (3, 96), (5, 4128), (130, 160), (1000, 32), (77, 2048)])
+def test_rows_need_not_be_a_multiple_of_128(rows, cols):
+    _check(workloads.make_cfg3(rows=rows, cols=cols), "ragged rows")
+
+
+def test_wide_exponent_range_matches_eager_form_too():
+    a = workloads.make_cfg3(rows=512, cols=8192)
+    p, s = _check(a, "cfg3")
+    e_p, e_s = eager.mx_fp8_quantize_eager(a)
+    assert_fp8_equal(p, e_p, E4M3, "eager payload")
+    assert torch.equal(as_bytes(s), as_bytes(e_s))
+    assert not p.float().isnan().any()
+
+
+def test_every_bf16_pattern_as_block_maximum():
+    # block b = [pattern b, then 31 elements that are small relative to it or zero]
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    a = torch.zeros(65536, 32, dtype=torch.bfloat16)
+    a[:, 0] = bits
+    a[:, 5] = (bits.float() * 0.37).to(torch.bfloat16)
+    a[:, 31] = (bits.float() * -0.011).to(torch.bfloat16)
+    _check(a.view(8192, 256), "all patterns")
+
+
+def test_every_bf16_pattern_everywhere_in_a_block():
+    # all 65536 patterns laid out contiguously: blocks mix neighbours in value
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    _check(bits.view(64, 1024), "dense patterns")
+    g = torch.Generator().manual_seed(1)
+    perm = torch.randperm(65536, generator=g)
+    _check(bits[perm].view(64, 1024), "shuffled patterns")
+
+
+def test_degenerate_blocks():
+    inf, nan = float("inf"), float("nan")
+    rows = [
+        [0.0] * 32,                                  # all zero -> scale byte 0, payload NaN bytes
+        [-0.0] * 32,
+        [2.0**-125] * 16 + [0.0] * 16,               # E <= -119 -> scale 0.0 -> +-448 and NaN
+        [2.0**-119, -(2.0**-120)] * 16,
+        [2.0**-118] * 32,                            # just inside the normal range
+        [1e-40] * 31 + [0.0],                        # subnormals
+        [inf] + [1.0] * 31,
+        [-inf] * 32,
+        [nan] + [1.0] * 31,
+        [3.0e38] * 32,                               # largest exponents
+        [1.0] * 32,                                  # power of two maximum -> code 0x78 region
+        [1.5, -1.0] * 16,
+    ]
+    a = torch.tensor(rows, dtype=torch.float32).to(torch.bfloat16)
+    _check(a, "degenerate")
+
+
+def test_misaligned_pointers_take_the_scalar_path():
+    from driss_torch_b200 import _cabi
+
+    a = workloads.make_cfg3(rows=64, cols=512)
+    base = torch.zeros(64 * 512 + 8, dtype=torch.bfloat16, device="cuda")
+    view = base[3 : 3 + 64 * 512].view(64, 512)
+    view.copy_(a)
+    pbuf = torch.zeros(64 * 512 + 8, dtype=torch.uint8, device="cuda")
+    payload = pbuf[5 : 5 + 64 * 512].view(E4M3).view(64, 512)
+    p, s = _cabi.mx_fp8_quantize(view, payload=payload)
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    assert_fp8_equal(p, want_p, E4M3, "misaligned payload")
+    assert torch.equal(as_bytes(s), as_bytes(want_s))
+
+
+def test_no_byte_outside_the_outputs_is_written():
+    from driss_torch_b200 import _cabi
+
+    a = workloads.make_cfg3(rows=33, cols=96)
+    n = a.numel()
+    pbuf = torch.full((n + 256,), 0x5A, dtype=torch.uint8, device="cuda")
+    sbuf = torch.full((n // 32 + 256,), 0x5A, dtype=torch.uint8, device="cuda")
+    _cabi.mx_fp8_quantize(a.cuda(), payload=pbuf[:n].view(E4M3).view(33, 96), scales=sbuf[: n // 32].view(torch.float8_e8m0fnu))
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    assert_fp8_equal(pbuf[:n].view(E4M3).view(33, 96), want_p, E4M3, "payload")
+    assert torch.equal(sbuf[: n // 32].cpu(), as_bytes(want_s))
+    assert (pbuf[n:] == 0x5A).all() and (sbuf[n // 32 :] == 0x5A).all()
+
+
+def test_errors_and_compile():
+    import driss_torch_b200 as dt
+
+    a = torch.rand(128, 64, device="cuda").to(torch.bfloat16)
+    for bad in (
+        lambda: dt.mx_fp8_quantize(a.float()),
+        lambda: dt.mx_fp8_quantize(a, block_size=16),
+        lambda: dt.mx_fp8_quantize(a, axis=0),
+        lambda: dt.mx_fp8_quantize(a, transpose=True),
+        lambda: dt.mx_fp8_quantize(a, ScalarType=torch.float8_e5m2),
+        lambda: dt.mx_fp8_quantize(a[:, :48]),
+        lambda: dt.mx_fp8_quantize(a.t()),
+        lambda: dt.mx_fp8_quantize(a.view(-1)),
+    ):
+        with pytest.raises(RuntimeError):
+            bad()
+    assert dt.mx_cast is dt.mx_fp8_quantize
+    torch._dynamo.reset()
+    fn = torch.compile(dt.mx_fp8_quantize, fullgraph=True, backend="aot_eager")
+    p, s = fn(a)
+    p0, s0 = dt.mx_fp8_quantize(a)
+    assert torch.equal(as_bytes(p), as_bytes(p0)) and torch.equal(as_bytes(s), as_bytes(s0))
