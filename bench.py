@@ -128,13 +128,16 @@ def algorithmic_bytes(op: str, rows: int, cols: int, s_in: int = 2) -> int:
 
 def time_rotating(fn, nsets: int, iters: int, warmup: int = 3):
     """Median/min ms of fn(i % nsets); consecutive calls touch different buffer sets so that every
-    timed launch starts with its inputs out of L2."""
+    timed launch starts with its inputs out of L2.  A short spin kernel is queued first so that the
+    start event, the launch and the stop event are all enqueued while the GPU is still busy: the
+    interval then holds device time only, not the host's launch latency."""
     for i in range(warmup):
         fn(i % nsets)
     torch.cuda.synchronize()
     times = []
     for i in range(iters):
         a, b = event_pair()
+        torch.cuda._sleep(400_000)
         a.record()
         fn(i % nsets)
         b.record()
