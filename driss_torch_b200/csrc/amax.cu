@@ -19,7 +19,10 @@ namespace dtq {
 #ifndef DTQ_AMAX_BLOCKS_PER_SM
 #define DTQ_AMAX_BLOCKS_PER_SM 4
 #endif
-constexpr int kAmaxThreads = 512;
+#ifndef DTQ_AMAX_THREADS
+#define DTQ_AMAX_THREADS 512
+#endif
+constexpr int kAmaxThreads = DTQ_AMAX_THREADS;
 
 template <int IN>
 struct AbsMax;
@@ -112,7 +115,7 @@ amax_kernel(const void *__restrict__ in, float *__restrict__ out, int64_t numel,
 int amax_grid(int64_t numel, int elem_bytes, const DeviceInfo &dev) {
   const int64_t tiles = ceil_div64(numel * elem_bytes / 16, int64_t(kAmaxThreads) * DTQ_AMAX_UNROLL);
   const int64_t max_grid = int64_t(dev.sm_count) * DTQ_AMAX_BLOCKS_PER_SM;
-  return static_cast<int>(tiles < 1 ? 1 : (tiles < max_grid ? tiles : max_grid));
+  return balanced_grid(tiles, max_grid);
 }
 
 int64_t head_elems(const void *p, int elem_bytes, int64_t numel) {

@@ -85,6 +85,81 @@ __device__ __forceinline__ float dsq_mul(double sd, float x) {
   return __double2float_rn(__dmul_rn(sd, static_cast<double>(x)));
 }
 
+// The double-precision product costs two 64-bit conversions per element on the slow
+// conversion pipe, which (not HBM) bounds a kernel that uses it for every element.  The final
+// fp8 byte, however, only depends on which side of an fp8 rounding boundary the reference value
+//   R = fp32_rne(fp64_rne(x * scale_d))
+// falls, and fp8 conversion is monotone.  So bracket R in fp32:
+//   lo = fp32(scale_d * (1 - 2^-21)),  hi = fp32(scale_d * (1 + 2^-21)),
+//   p_lo = fp32(x * lo),  p_hi = fp32(x * hi).
+// Every rounding involved is within 2^-24 relative, so R lies between p_lo and p_hi (for either
+// sign of x; underflow keeps the sign and everything that small converts to a signed zero;
+// overflow saturates on both sides; NaN stays NaN).  If both ends convert to the same fp8 byte,
+// that byte is fp8(R) exactly.  Otherwise (about 2^-16 of random elements) the caller recomputes
+// with the double product.
+struct DsqScale {
+  double sd;
+  float lo, hi;
+};
+template <int OUT>
+__device__ __forceinline__ DsqScale make_dsq_scale(float amax) {
+  DsqScale s;
+  s.sd = dsq_scale<OUT>(amax);
+  s.lo = __double2float_rn(s.sd * (1.0 - 0x1p-21));
+  s.hi = __double2float_rn(s.sd * (1.0 + 0x1p-21));
+  return s;
+}
+// Two elements -> two fp8 bytes via the lower bracket end; `mismatch` collects (by OR) the
+// difference to the upper end's bytes.
+template <int OUT>
+__device__ __forceinline__ uint32_t dsq_pair_bracket(float x0, float x1, const DsqScale &s, uint32_t &mismatch) {
+  const float2 x = make_float2(x0, x1);
+  const float2 pl = __fmul2_rn(x, make_float2(s.lo, s.lo));
+  const float2 ph = __fmul2_rn(x, make_float2(s.hi, s.hi));
+  const uint32_t a = cvt_fp8x2<OUT>(pl.x, pl.y);
+  const uint32_t b = cvt_fp8x2<OUT>(ph.x, ph.y);
+  mismatch |= a ^ b;
+  return a;
+}
+// The exact recomputation lives in functions that are never inlined, so that it stays behind a
+// real branch: were it merged into the caller as predicated code, its 64-bit conversions would
+// occupy the conversion pipe for every element again.
+template <int OUT>
+__device__ __noinline__ uint2 dsq_exact_bf16x8(uint4 v, double sd) {
+  uint2 r;
+  r.x = cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.x)), dsq_mul(sd, bf16_hi(v.x))) |
+        (cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.y)), dsq_mul(sd, bf16_hi(v.y))) << 16);
+  r.y = cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.z)), dsq_mul(sd, bf16_hi(v.z))) |
+        (cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.w)), dsq_mul(sd, bf16_hi(v.w))) << 16);
+  return r;
+}
+template <int OUT>
+__device__ __noinline__ uint32_t dsq_exact_f32x4(uint4 v, double sd) {
+  return cvt_fp8x4<OUT>(dsq_mul(sd, __uint_as_float(v.x)), dsq_mul(sd, __uint_as_float(v.y)),
+                        dsq_mul(sd, __uint_as_float(v.z)), dsq_mul(sd, __uint_as_float(v.w)));
+}
+// Eight bf16 (four packed words) -> eight fp8 bytes.
+template <int OUT>
+__device__ __forceinline__ uint2 dsq_convert_bf16x8(uint4 v, const DsqScale &s) {
+  uint32_t mismatch = 0;
+  uint2 r;
+  r.x = dsq_pair_bracket<OUT>(bf16_lo(v.x), bf16_hi(v.x), s, mismatch) |
+        (dsq_pair_bracket<OUT>(bf16_lo(v.y), bf16_hi(v.y), s, mismatch) << 16);
+  r.y = dsq_pair_bracket<OUT>(bf16_lo(v.z), bf16_hi(v.z), s, mismatch) |
+        (dsq_pair_bracket<OUT>(bf16_lo(v.w), bf16_hi(v.w), s, mismatch) << 16);
+  if (__builtin_expect(mismatch != 0, 0)) r = dsq_exact_bf16x8<OUT>(v, s.sd);
+  return r;
+}
+// Four fp32 -> four fp8 bytes.
+template <int OUT>
+__device__ __forceinline__ uint32_t dsq_convert_f32x4(uint4 v, const DsqScale &s) {
+  uint32_t mismatch = 0;
+  uint32_t r = dsq_pair_bracket<OUT>(__uint_as_float(v.x), __uint_as_float(v.y), s, mismatch) |
+               (dsq_pair_bracket<OUT>(__uint_as_float(v.z), __uint_as_float(v.w), s, mismatch) << 16);
+  if (__builtin_expect(mismatch != 0, 0)) r = dsq_exact_f32x4<OUT>(v, s.sd);
+  return r;
+}
+
 // ---- reductions of non-negative floats (or -inf) ------------------------------------------------
 // Such floats order like their bit patterns read as signed ints (-inf is negative), so the
 // warp-wide integer max instruction does the job exactly.

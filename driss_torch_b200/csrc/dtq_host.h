@@ -42,4 +42,14 @@ inline bool aligned_to(const void *p, uintptr_t a) { return (reinterpret_cast<ui
 
 inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Grid for a persistent kernel that walks `tiles` tiles grid-stride: at most `max_grid` blocks,
+// and when every block needs several tiles, as few blocks as keep the number of rounds, so that
+// all blocks run the same number of tiles (no straggler round with most of the GPU idle).
+inline int balanced_grid(int64_t tiles, int64_t max_grid) {
+  if (tiles < 1) return 1;
+  if (tiles <= max_grid) return static_cast<int>(tiles);
+  const int64_t rounds = ceil_div64(tiles, max_grid);
+  return static_cast<int>(ceil_div64(tiles, rounds));
+}
+
 }  // namespace dtq

@@ -38,7 +38,17 @@ namespace {
 #ifndef DTQ_DSQ_UNROLL
 #define DTQ_DSQ_UNROLL 4
 #endif
-constexpr int kThreads = 256;
+#ifndef DTQ_DSQ_COOP
+#define DTQ_DSQ_COOP 1
+#endif
+#ifndef DTQ_DSQ_THREADS
+#define DTQ_DSQ_THREADS 256
+#endif
+// Grid cap of the stand-alone cast kernel; default "no cap" (one tile per block), see saturated_cast.cu.
+#ifndef DTQ_CAST_BLOCKS_PER_SM
+#define DTQ_CAST_BLOCKS_PER_SM (1 << 20)
+#endif
+constexpr int kThreads = DTQ_DSQ_THREADS;
 
 // ---- per-chunk arithmetic ----------------------------------------------------------------------
 template <int IN, int OUT>
@@ -49,14 +59,8 @@ struct DsqChunk<DTQ_BF16, OUT> {
   static constexpr int kElems = 8;
   static constexpr int kElemBytes = 2;
   static constexpr int kOutAlign = 8;
-  __device__ static uint32_t pair(uint32_t w, double sd) {
-    return cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(w)), dsq_mul(sd, bf16_hi(w)));
-  }
-  __device__ static void convert_store(uint4 v, double sd, uint8_t *out, int64_t chunk) {
-    uint2 r;
-    r.x = pair(v.x, sd) | (pair(v.y, sd) << 16);
-    r.y = pair(v.z, sd) | (pair(v.w, sd) << 16);
-    stg_stream(out + chunk * kElems, r);
+  __device__ static void convert_store(uint4 v, const DsqScale &s, uint8_t *out, int64_t chunk) {
+    stg_stream(out + chunk * kElems, dsq_convert_bf16x8<OUT>(v, s));
   }
   __device__ static float load_one(const void *in, int64_t i) {
     return __uint_as_float(uint32_t(static_cast<const uint16_t *>(in)[i]) << 16);
@@ -76,10 +80,8 @@ struct DsqChunk<DTQ_F32, OUT> {
   static constexpr int kElems = 4;
   static constexpr int kElemBytes = 4;
   static constexpr int kOutAlign = 4;
-  __device__ static void convert_store(uint4 v, double sd, uint8_t *out, int64_t chunk) {
-    const uint32_t r = cvt_fp8x4<OUT>(dsq_mul(sd, __uint_as_float(v.x)), dsq_mul(sd, __uint_as_float(v.y)),
-                                      dsq_mul(sd, __uint_as_float(v.z)), dsq_mul(sd, __uint_as_float(v.w)));
-    stg_stream(out + chunk * kElems, r);
+  __device__ static void convert_store(uint4 v, const DsqScale &s, uint8_t *out, int64_t chunk) {
+    stg_stream(out + chunk * kElems, dsq_convert_f32x4<OUT>(v, s));
   }
   __device__ static float load_one(const void *in, int64_t i) { return static_cast<const float *>(in)[i]; }
   __device__ static void absmax(float &a, float &b, uint4 v) {
@@ -144,7 +146,7 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
     return;  // status word says why; nothing more is written
   }
   const float amax = ld_relaxed_f32(&ws->amax);
-  const double sd = dsq_scale<OUT>(amax);
+  const DsqScale sd = make_dsq_scale<OUT>(amax);
 
   // phase 2: the kept tile from registers, the rest newest-first
   if (last_tile >= 0) {
@@ -161,7 +163,7 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
     }
   }
   if (blockIdx.x == 0 && tail0 + threadIdx.x < numel)
-    out[tail0 + threadIdx.x] = cvt_fp8<OUT>(dsq_mul(sd, C::load_one(in, tail0 + threadIdx.x)));
+    out[tail0 + threadIdx.x] = cvt_fp8<OUT>(dsq_mul(sd.sd, C::load_one(in, tail0 + threadIdx.x)));
 }
 
 // ---- cast phase alone ---------------------------------------------------------------------------------
@@ -171,8 +173,8 @@ cast_with_amax_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, c
                       float *__restrict__ scale_out, int64_t numel) {
   using C = DsqChunk<IN, OUT>;
   const float amax = fmaxf(*amax_p, 0.0f);
-  const double sd = dsq_scale<OUT>(amax);
-  if (scale_out && blockIdx.x == 0 && threadIdx.x == 0) *scale_out = static_cast<float>(sd);
+  const DsqScale sd = make_dsq_scale<OUT>(amax);
+  if (scale_out && blockIdx.x == 0 && threadIdx.x == 0) *scale_out = static_cast<float>(sd.sd);
   const int64_t nchunks = numel / C::kElems;
   constexpr int64_t kTile = int64_t(kThreads) * UNROLL;
   for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
@@ -192,7 +194,7 @@ cast_with_amax_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, c
   }
   const int64_t tail0 = nchunks * C::kElems;
   if (blockIdx.x == 0 && tail0 + threadIdx.x < numel)
-    out[tail0 + threadIdx.x] = cvt_fp8<OUT>(dsq_mul(sd, C::load_one(in, tail0 + threadIdx.x)));
+    out[tail0 + threadIdx.x] = cvt_fp8<OUT>(dsq_mul(sd.sd, C::load_one(in, tail0 + threadIdx.x)));
 }
 
 template <int IN, int OUT>
@@ -257,11 +259,16 @@ int launch_fused(const void *in, void *out, float *amax_out, float *scale_out, i
     const int limit = coop_grid_limit(kernel, dev, cache);
     if (limit <= 0) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorLaunchFailure);
     const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * DTQ_DSQ_UNROLL);
-    const int grid = static_cast<int>(tiles < 1 ? 1 : (tiles < limit ? tiles : limit));
+    const int grid = balanced_grid(tiles, limit);
     const uint4 *in4 = static_cast<const uint4 *>(in);
     void *args[] = {&in4, &o, &amax_out, &scale_out, &numel, &ws};
+#if DTQ_DSQ_COOP
     DTQ_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kernel), dim3(grid), dim3(kThreads), args, 0, st));
     return DTQ_OK;
+#else
+    kernel<<<grid, kThreads, 0, st>>>(in4, o, amax_out, scale_out, numel, ws);
+    return cuda_status(cudaGetLastError());
+#endif
   }
   const int64_t blocks = ceil_div64(numel, kThreads);
   const int64_t max_grid = int64_t(dev.sm_count) * 8;
@@ -276,10 +283,10 @@ int launch_cast(const void *in, void *out, const float *amax, float *scale_out, 
                 cudaStream_t st) {
   using C = DsqChunk<IN, OUT>;
   uint8_t *o = static_cast<uint8_t *>(out);
-  const int64_t max_grid = int64_t(dev.sm_count) * 8;
+  const int64_t max_grid = int64_t(dev.sm_count) * DTQ_CAST_BLOCKS_PER_SM;
   if (aligned_to(in, 16) && aligned_to(out, C::kOutAlign)) {
     const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * DTQ_DSQ_UNROLL);
-    const int grid = static_cast<int>(tiles < 1 ? 1 : (tiles < max_grid ? tiles : max_grid));
+    const int grid = balanced_grid(tiles, max_grid);
     cast_with_amax_stream<IN, OUT, DTQ_DSQ_UNROLL><<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in), o, amax,
                                                                              scale_out, numel);
   } else {

@@ -20,6 +20,10 @@
 namespace dtq {
 namespace {
 
+// Grid cap in blocks per SM; the default is "no cap" (one tile per block), see saturated_cast.cu.
+#ifndef DTQ_MX_BLOCKS_PER_SM
+#define DTQ_MX_BLOCKS_PER_SM (1 << 20)
+#endif
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;  // tied to the scale-byte mapping below: lane&3 picks the iteration
 
@@ -114,11 +118,11 @@ extern "C" int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *sca
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t max_grid = int64_t(dev.sm_count) * 8;
+  const int64_t max_grid = int64_t(dev.sm_count) * DTQ_MX_BLOCKS_PER_SM;
   if (aligned_to(in_bf16, 16) && aligned_to(payload, 8)) {
     const int64_t nchunks = numel / 8;
     const int64_t tiles = ceil_div64(nchunks, int64_t(kThreads) * kUnroll);
-    const int grid = static_cast<int>(tiles < max_grid ? tiles : max_grid);
+    const int grid = balanced_grid(tiles, max_grid);
     mx_stream_kernel<<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in_bf16), static_cast<uint8_t *>(payload),
                                                 static_cast<uint8_t *>(scales_e8m0), nchunks);
   } else {

@@ -32,13 +32,8 @@ struct RowIn<DTQ_BF16> {
     return fmaxf(__bfloat162float(m.x), __bfloat162float(m.y));
   }
   template <int OUT>
-  __device__ static void convert_store(uint4 v, double sd, uint8_t *dst) {
-    uint2 r;
-    r.x = cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.x)), dsq_mul(sd, bf16_hi(v.x))) |
-          (cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.y)), dsq_mul(sd, bf16_hi(v.y))) << 16);
-    r.y = cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.z)), dsq_mul(sd, bf16_hi(v.z))) |
-          (cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.w)), dsq_mul(sd, bf16_hi(v.w))) << 16);
-    stg_stream(dst, r);
+  __device__ static void convert_store(uint4 v, const DsqScale &s, uint8_t *dst) {
+    stg_stream(dst, dsq_convert_bf16x8<OUT>(v, s));
   }
   __device__ static float load_one(const void *p, int64_t i) {
     return __uint_as_float(uint32_t(static_cast<const uint16_t *>(p)[i]) << 16);
@@ -52,9 +47,8 @@ struct RowIn<DTQ_F32> {
                  fmaxf(fabsf(__uint_as_float(v.z)), fabsf(__uint_as_float(v.w))));
   }
   template <int OUT>
-  __device__ static void convert_store(uint4 v, double sd, uint8_t *dst) {
-    stg_stream(dst, cvt_fp8x4<OUT>(dsq_mul(sd, __uint_as_float(v.x)), dsq_mul(sd, __uint_as_float(v.y)),
-                                   dsq_mul(sd, __uint_as_float(v.z)), dsq_mul(sd, __uint_as_float(v.w))));
+  __device__ static void convert_store(uint4 v, const DsqScale &s, uint8_t *dst) {
+    stg_stream(dst, dsq_convert_f32x4<OUT>(v, s));
   }
   __device__ static float load_one(const void *p, int64_t i) { return static_cast<const float *>(p)[i]; }
 };
@@ -95,10 +89,10 @@ rowwise_regs_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, flo
     amax = smem32[0];
   }
   if (!live) return;
-  const double sd = dsq_scale<OUT>(amax);
+  const DsqScale sd = make_dsq_scale<OUT>(amax);
   if (t == 0) {
     if (amax_out) amax_out[row] = amax;
-    if (scale_out) scale_out[row] = static_cast<float>(sd);
+    if (scale_out) scale_out[row] = static_cast<float>(sd.sd);
   }
   uint8_t *dst = out + row * chunks_per_row * R::kElems;
 #pragma unroll
@@ -132,17 +126,17 @@ rowwise_looped_kernel(const void *__restrict__ in, uint8_t *__restrict__ out, fl
     __syncthreads();
     amax = smem32[0];
     __syncthreads();
-    const double sd = dsq_scale<OUT>(amax);
+    const DsqScale sd = make_dsq_scale<OUT>(amax);
     if (threadIdx.x == 0) {
       if (amax_out) amax_out[row] = amax;
-      if (scale_out) scale_out[row] = static_cast<float>(sd);
+      if (scale_out) scale_out[row] = static_cast<float>(sd.sd);
     }
     if constexpr (VEC) {
       const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
       for (int64_t c = threadIdx.x; c < cols / R::kElems; c += kThreads)
         R::template convert_store<OUT>(ldg_stream(s4 + c), sd, dst + c * R::kElems);
     } else {
-      for (int64_t c = threadIdx.x; c < cols; c += kThreads) dst[c] = cvt_fp8<OUT>(dsq_mul(sd, R::load_one(src, c)));
+      for (int64_t c = threadIdx.x; c < cols; c += kThreads) dst[c] = cvt_fp8<OUT>(dsq_mul(sd.sd, R::load_one(src, c)));
     }
   }
 }
