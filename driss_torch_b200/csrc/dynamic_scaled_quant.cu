@@ -6,21 +6,27 @@
 // which is the arithmetic of the reference's cooperative kernel
 // (src/dynamic_scaled_quant.cu:83-118), restated for bf16 and fp32 inputs.
 //
-// dtq_dynamic_scaled_quant is one cooperative launch of a persistent grid:
-//   phase 1  every block streams its tiles (128-bit loads, several in flight), keeps its LAST
-//            tile in registers, and publishes a partial max;
-//   finish   the last-arriving block reduces the partials, writes amax / scale and releases
-//            a generation word; the others wait on it with a bounded spin;
-//   phase 2  every block converts the tile it kept, then walks its remaining tiles in REVERSE
-//            order, so the most recently read part of the tensor is re-read while it is still
-//            in the 126 MB L2.
-// The reference reads the tensor twice with scalar loads, writes single bytes and needs a
-// separate memset launch for its scratch.
+// dtq_dynamic_scaled_quant is one cooperative launch of a persistent grid (block b owns tiles
+// b, b+G, b+2G, ...).  The tensor-wise dependency forces a second look at every element; the
+// kernel makes as little of that second look as possible come from HBM:
+//   phase 1  each block keeps its FIRST tile in registers and its next few tiles in shared
+//            memory (filled through the registers the max is taken from), then streams the rest;
+//   finish   the last-arriving block reduces the per-block partials, writes amax / scale and
+//            bumps a generation word; the others wait on it with a bounded spin;
+//   phase 2  each block converts its streamed tiles newest-first, so the re-read starts with
+//            what L2 still holds (about 50 MB on B200, measured), with the next tile's loads in
+//            flight while the current one is converted and stored; then the tiles it kept in
+//            shared memory and registers, which cost no memory traffic at all.
+// Keeping the OLDEST tiles on chip matters: L2 retains the most recently read lines, and those
+// must be lines phase 2 will actually ask for.
+// The reference reads the tensor twice from HBM with scalar loads, writes single bytes and needs
+// a separate memset launch for its scratch.
 //
 // dtq_cast_with_amax is phase 2 alone for an amax that already sits in device memory (the
 // sharded path: local amax -> max all-reduce -> cast).
 #include <atomic>
 #include <cmath>
+#include <mutex>
 
 #include "dtq_device.cuh"
 #include "dtq_grid.cuh"
@@ -40,6 +46,22 @@ namespace {
 #endif
 #ifndef DTQ_DSQ_COOP
 #define DTQ_DSQ_COOP 1
+#endif
+// The fused kernel: threads per block, resident blocks per SM it is sized for, and how many
+// tiles (of FUSED_THREADS * UNROLL 16-byte chunks) a block keeps in shared memory.
+#ifndef DTQ_FUSED_THREADS
+#define DTQ_FUSED_THREADS 512
+#endif
+#ifndef DTQ_FUSED_BLOCKS_PER_SM
+#define DTQ_FUSED_BLOCKS_PER_SM 2
+#endif
+#ifndef DTQ_FUSED_SMEM_TILES
+#define DTQ_FUSED_SMEM_TILES 3
+#endif
+// 1: a block's first tile stays in registers across the barrier (one more tile kept on chip,
+// 4 * UNROLL registers per thread); 0: only shared memory keeps tiles.
+#ifndef DTQ_FUSED_KEEP_REGS
+#define DTQ_FUSED_KEEP_REGS 1
 #endif
 #ifndef DTQ_DSQ_THREADS
 #define DTQ_DSQ_THREADS 256
@@ -92,44 +114,94 @@ struct DsqChunk<DTQ_F32, OUT> {
 
 // ---- fused single launch -------------------------------------------------------------------------
 // Requires `in` 16-byte aligned and `out` aligned for the packed store; numel may be anything
-// (block 0 handles the elements past the last whole chunk).
+// (block 0 handles the elements past the last whole chunk).  Dynamic shared memory holds
+// `smem_tiles` tiles.
+constexpr int kFusedThreads = DTQ_FUSED_THREADS;
+
+template <int UNROLL>
+__device__ __forceinline__ void load_tile(uint4 (&v)[UNROLL], const uint4 *__restrict__ in, int64_t tile,
+                                          int64_t nchunks) {
+  constexpr int64_t kTile = int64_t(kFusedThreads) * UNROLL;
+  const int64_t first = tile * kTile + threadIdx.x;
+  if ((tile + 1) * kTile <= nchunks) {
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) v[u] = ldg_stream(in + first + u * kFusedThreads);
+  } else {
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      v[u] = (first + u * kFusedThreads < nchunks) ? ldg_stream(in + first + u * kFusedThreads) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+template <typename C, int UNROLL>
+__device__ __forceinline__ void store_tile(const uint4 (&v)[UNROLL], const DsqScale &sd, uint8_t *__restrict__ out,
+                                           int64_t tile, int64_t nchunks) {
+  constexpr int64_t kTile = int64_t(kFusedThreads) * UNROLL;
+  const int64_t first = tile * kTile + threadIdx.x;
+  if ((tile + 1) * kTile <= nchunks) {
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) C::convert_store(v[u], sd, out, first + u * kFusedThreads);
+  } else {
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      if (first + u * kFusedThreads < nchunks) C::convert_store(v[u], sd, out, first + u * kFusedThreads);
+  }
+}
+
 template <int IN, int OUT, int UNROLL>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kFusedThreads, DTQ_FUSED_BLOCKS_PER_SM)
 dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float *__restrict__ amax_out,
-                 float *__restrict__ scale_out, int64_t numel, Workspace *ws) {
+                 float *__restrict__ scale_out, int64_t numel, Workspace *ws, int smem_tiles) {
   using C = DsqChunk<IN, OUT>;
+  extern __shared__ uint4 kept_smem[];  // [smem_tiles][UNROLL][kFusedThreads]
   __shared__ float smem32[32];
   __shared__ int flag;
   unsigned int gen0 = 0;
   if (threadIdx.x == 0) gen0 = ld_acquire(&ws->generation);
+#ifdef DTQ_FUSED_TIMING
+  unsigned long long *stamps = reinterpret_cast<unsigned long long *>(ws->pad);
+  auto now = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+  if (threadIdx.x == 0) atomicMin(&stamps[0], now());
+#endif
 
   const int64_t nchunks = numel / C::kElems;
-  constexpr int64_t kTile = int64_t(kThreads) * UNROLL;
+  constexpr int64_t kTile = int64_t(kFusedThreads) * UNROLL;
   const int64_t ntiles = (nchunks + kTile - 1) / kTile;
   const int64_t tail0 = nchunks * C::kElems;
+  const int64_t G = gridDim.x;
+  // this block's tiles: blockIdx.x + k * G for k in [0, count)
+  const int64_t count = blockIdx.x < ntiles ? (ntiles - blockIdx.x + G - 1) / G : 0;
+  constexpr int kRegTiles = DTQ_FUSED_KEEP_REGS;  // tile k = 0 lives in registers if 1
+  // tiles k in [kRegTiles, kept) live in shared memory, tiles k >= kept are streamed
+  const int64_t kept = count < smem_tiles + kRegTiles ? count : smem_tiles + kRegTiles;
 
   // phase 1
   float a = 0.0f, b = 0.0f;
-  uint4 v[UNROLL];
-  int64_t tile = blockIdx.x;
-  int64_t last_tile = -1;
-  for (; tile < ntiles; tile += gridDim.x) {
-    const int64_t first = tile * kTile + threadIdx.x;
-    if ((tile + 1) * kTile <= nchunks) {
+  uint4 first_tile[UNROLL];
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u) v[u] = ldg_stream(in + first + u * kThreads);
-    } else {
+  for (int u = 0; u < UNROLL; ++u) first_tile[u] = make_uint4(0, 0, 0, 0);
+  if (kRegTiles && count > 0) {
+    load_tile<UNROLL>(first_tile, in, blockIdx.x, nchunks);
 #pragma unroll
-      for (int u = 0; u < UNROLL; ++u)
-        v[u] = (first + u * kThreads < nchunks) ? ldg_stream(in + first + u * kThreads) : make_uint4(0, 0, 0, 0);
-    }
+    for (int u = 0; u < UNROLL; ++u) C::absmax(a, b, first_tile[u]);
+  }
+  for (int64_t k = kRegTiles; k < count; ++k) {
+    uint4 v[UNROLL];
+    load_tile<UNROLL>(v, in, blockIdx.x + k * G, nchunks);
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) C::absmax(a, b, v[u]);
-    last_tile = tile;
+    if (k < kept) {
+      uint4 *slot = kept_smem + (k - kRegTiles) * kTile + threadIdx.x;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) slot[u * kFusedThreads] = v[u];
+    }
   }
   if (blockIdx.x == 0 && tail0 + threadIdx.x < numel) a = fmaxf(a, fabsf(C::load_one(in, tail0 + threadIdx.x)));
 
   // finish
+#ifdef DTQ_FUSED_TIMING
+  if (threadIdx.x == 0) { atomicMin(&stamps[1], now()); atomicMax(&stamps[2], now()); }
+#endif
   const float block_value = block_max_nonneg(fmaxf(a, b), smem32, 0.0f);
   if (publish_and_ticket(ws, block_value, &flag)) {
     const float total = reduce_partials(ws, smem32, 0.0f);
@@ -147,21 +219,39 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   }
   const float amax = ld_relaxed_f32(&ws->amax);
   const DsqScale sd = make_dsq_scale<OUT>(amax);
+#ifdef DTQ_FUSED_TIMING
+  if (threadIdx.x == 0) { atomicMin(&stamps[3], now()); atomicMax(&stamps[4], now()); }
+#endif
 
-  // phase 2: the kept tile from registers, the rest newest-first
-  if (last_tile >= 0) {
-    const int64_t first = last_tile * kTile + threadIdx.x;
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-      if (first + u * kThreads < nchunks) C::convert_store(v[u], sd, out, first + u * kThreads);
-    for (tile = last_tile - gridDim.x; tile >= 0; tile -= gridDim.x) {
-      const int64_t f = tile * kTile + threadIdx.x;  // always a whole tile
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) v[u] = ldg_stream(in + f + u * kThreads);
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u) C::convert_store(v[u], sd, out, f + u * kThreads);
+  // phase 2a: streamed tiles, newest first, two register buffers so that the next tile's loads
+  // are in flight while the current tile is converted and stored
+  {
+    uint4 va[UNROLL], vb[UNROLL];
+    int64_t k = count - 1;
+    const int64_t stop = kept - 1;  // tiles k > stop were streamed
+    if (k > stop) load_tile<UNROLL>(va, in, blockIdx.x + k * G, nchunks);
+    while (k > stop) {
+      if (k - 1 > stop) load_tile<UNROLL>(vb, in, blockIdx.x + (k - 1) * G, nchunks);
+      store_tile<C, UNROLL>(va, sd, out, blockIdx.x + k * G, nchunks);
+      --k;
+      if (k <= stop) break;
+      if (k - 1 > stop) load_tile<UNROLL>(va, in, blockIdx.x + (k - 1) * G, nchunks);
+      store_tile<C, UNROLL>(vb, sd, out, blockIdx.x + k * G, nchunks);
+      --k;
     }
   }
+  // phase 2b: tiles kept in shared memory, then the one kept in registers
+  for (int64_t k = kept - 1; k >= kRegTiles; --k) {
+    uint4 v[UNROLL];
+    const uint4 *slot = kept_smem + (k - kRegTiles) * kTile + threadIdx.x;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) v[u] = slot[u * kFusedThreads];
+    store_tile<C, UNROLL>(v, sd, out, blockIdx.x + k * G, nchunks);
+  }
+  if (kRegTiles && count > 0) store_tile<C, UNROLL>(first_tile, sd, out, blockIdx.x, nchunks);
+#ifdef DTQ_FUSED_TIMING
+  if (threadIdx.x == 0) { atomicMin(&stamps[5], now()); atomicMax(&stamps[6], now()); }
+#endif
   if (blockIdx.x == 0 && tail0 + threadIdx.x < numel)
     out[tail0 + threadIdx.x] = cvt_fp8<OUT>(dsq_mul(sd.sd, C::load_one(in, tail0 + threadIdx.x)));
 }
@@ -232,20 +322,44 @@ amax_scalar_kernel(const void *__restrict__ in, int64_t numel, float *__restrict
   }
 }
 
-// Largest grid the cooperative launch accepts for this kernel on this device, cached.
+// Per device and kernel instantiation: the shared memory the kernel may keep tiles in and the
+// largest grid a cooperative launch accepts with it (cached after the first call).
+struct FusedPlan {
+  int smem_tiles = 0;
+  int max_grid = 0;
+};
+
 template <typename Kernel>
-int coop_grid_limit(Kernel kernel, const DeviceInfo &dev, std::atomic<int> *cache) {
+int fused_plan(Kernel kernel, const DeviceInfo &dev, FusedPlan *cache, std::atomic<int> *ready, FusedPlan *plan) {
   int dev_id = 0;
-  if (cudaGetDevice(&dev_id) != cudaSuccess) return 0;
-  int v = cache[dev_id & 63].load(std::memory_order_relaxed);
-  if (v == 0) {
-    int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess) return 0;
-    v = per_sm * dev.sm_count;
-    if (v > kMaxGridBlocks) v = kMaxGridBlocks;
-    cache[dev_id & 63].store(v, std::memory_order_relaxed);
+  DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
+  dev_id &= 63;
+  if (!ready[dev_id].load(std::memory_order_acquire)) {
+    static std::mutex mutex;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!ready[dev_id].load(std::memory_order_relaxed)) {
+      int smem_per_sm = 0, reserved = 0;
+      DTQ_CUDA_TRY(cudaDeviceGetAttribute(&smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev_id));
+      DTQ_CUDA_TRY(cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev_id));
+      const size_t tile_bytes = size_t(kFusedThreads) * DTQ_DSQ_UNROLL * 16;
+      FusedPlan p;
+      // what one of DTQ_FUSED_BLOCKS_PER_SM co-resident blocks can have, minus static use and reserve
+      const size_t budget = size_t(smem_per_sm) / DTQ_FUSED_BLOCKS_PER_SM - reserved - 512;
+      p.smem_tiles = static_cast<int>(budget / tile_bytes);
+      if (p.smem_tiles > DTQ_FUSED_SMEM_TILES) p.smem_tiles = DTQ_FUSED_SMEM_TILES;
+      const size_t dyn = size_t(p.smem_tiles) * tile_bytes;
+      DTQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dyn)));
+      int per_sm = 0;
+      DTQ_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFusedThreads, dyn));
+      p.max_grid = per_sm * dev.sm_count;
+      if (p.max_grid > kMaxGridBlocks) p.max_grid = kMaxGridBlocks;
+      if (p.max_grid <= 0) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorLaunchOutOfResources);
+      cache[dev_id] = p;
+      ready[dev_id].store(1, std::memory_order_release);
+    }
   }
-  return v;
+  *plan = cache[dev_id];
+  return DTQ_OK;
 }
 
 template <int IN, int OUT>
@@ -254,19 +368,23 @@ int launch_fused(const void *in, void *out, float *amax_out, float *scale_out, i
   using C = DsqChunk<IN, OUT>;
   uint8_t *o = static_cast<uint8_t *>(out);
   if (aligned_to(in, 16) && aligned_to(out, C::kOutAlign) && dev.cooperative) {
-    static std::atomic<int> cache[64];
+    static FusedPlan cache[64];
+    static std::atomic<int> ready[64];
     auto kernel = dsq_fused_kernel<IN, OUT, DTQ_DSQ_UNROLL>;
-    const int limit = coop_grid_limit(kernel, dev, cache);
-    if (limit <= 0) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorLaunchFailure);
-    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * DTQ_DSQ_UNROLL);
-    const int grid = balanced_grid(tiles, limit);
+    FusedPlan plan;
+    if (int e = fused_plan(kernel, dev, cache, ready, &plan)) return e;
+    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kFusedThreads) * DTQ_DSQ_UNROLL);
+    const int grid = balanced_grid(tiles, plan.max_grid);
     const uint4 *in4 = static_cast<const uint4 *>(in);
-    void *args[] = {&in4, &o, &amax_out, &scale_out, &numel, &ws};
+    int smem_tiles = plan.smem_tiles;
+    const size_t dyn = size_t(smem_tiles) * kFusedThreads * DTQ_DSQ_UNROLL * 16;
 #if DTQ_DSQ_COOP
-    DTQ_CUDA_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kernel), dim3(grid), dim3(kThreads), args, 0, st));
+    void *args[] = {&in4, &o, &amax_out, &scale_out, &numel, &ws, &smem_tiles};
+    DTQ_CUDA_TRY(
+        cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kernel), dim3(grid), dim3(kFusedThreads), args, dyn, st));
     return DTQ_OK;
 #else
-    kernel<<<grid, kThreads, 0, st>>>(in4, o, amax_out, scale_out, numel, ws);
+    kernel<<<grid, kFusedThreads, dyn, st>>>(in4, o, amax_out, scale_out, numel, ws, smem_tiles);
     return cuda_status(cudaGetLastError());
 #endif
   }

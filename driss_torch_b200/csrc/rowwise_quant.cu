@@ -5,9 +5,9 @@
 // (src/dynamic_scaled_quant.cu:111-117) applied per row, and the per-row fp32 scales are what
 // its row-wise scaled GEMM consumes (src/sweep_mm.cu:28-40).
 //
-// Single pass over HBM: a row (or a share of it) is loaded into registers with all its 128-bit
-// loads in flight at once, the row maximum is agreed by shuffle (one warp per row) or through
-// shared memory (one CTA per row), and the payload is produced from the registers.  Rows too
+// Single pass over HBM: a row is loaded into the registers of a warp (short rows) or of a CTA
+// sized to the row, with all its 128-bit loads in flight at once; the row maximum is agreed by
+// shuffle or through shared memory, and the payload is produced from the registers.  Rows too
 // long for registers (> 32768 bf16 / 16384 fp32 elements) or not 16-byte aligned take a
 // two-pass CTA-per-row kernel whose second read is served by L2.
 #include <cmath>
@@ -53,19 +53,27 @@ struct RowIn<DTQ_F32> {
   __device__ static float load_one(const void *p, int64_t i) { return static_cast<const float *>(p)[i]; }
 };
 
-// TEAM_WARPS warps share a row (1: warp per row, kWarps: CTA per row); each thread holds up to
-// CHUNKS 16-byte chunks of it.  chunks_per_row = cols / kElems <= 32 * TEAM_WARPS * CHUNKS.
+// A team of TEAM_WARPS warps shares a row; each thread holds up to CHUNKS 16-byte chunks of it
+// (chunks_per_row = cols / kElems <= 32 * TEAM_WARPS * CHUNKS).  TEAM_WARPS == 1: a CTA is eight
+// independent warps, one row each, and never synchronises.  TEAM_WARPS > 1: the CTA is the team
+// (one row per CTA), so short rows get small CTAs, many of which are resident per SM and drift
+// out of phase -- some loading while others convert -- which keeps HBM busy.
 template <int IN, int OUT, int CHUNKS, int TEAM_WARPS>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(TEAM_WARPS == 1 ? kThreads : 32 * TEAM_WARPS)
 rowwise_regs_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float *__restrict__ amax_out,
                     float *__restrict__ scale_out, int64_t rows, int chunks_per_row) {
   using R = RowIn<IN>;
   constexpr int kTeam = 32 * TEAM_WARPS;
-  constexpr int kRowsPerCta = kWarps / TEAM_WARPS;
   __shared__ float smem32[32];
-  const int team = (threadIdx.x >> 5) / TEAM_WARPS;
-  const int t = threadIdx.x - team * kTeam;
-  const int64_t row = int64_t(blockIdx.x) * kRowsPerCta + team;
+  int64_t row;
+  int t;
+  if constexpr (TEAM_WARPS == 1) {
+    row = int64_t(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+    t = threadIdx.x & 31;
+  } else {
+    row = blockIdx.x;
+    t = threadIdx.x;
+  }
   const bool live = row < rows;
 
   const uint4 *src = in + row * chunks_per_row;
@@ -141,24 +149,31 @@ rowwise_looped_kernel(const void *__restrict__ in, uint8_t *__restrict__ out, fl
   }
 }
 
-template <int IN, int OUT, int TEAM_WARPS>
+template <int IN, int OUT, int CHUNKS, int TEAM_WARPS>
 int launch_regs(const void *in, void *out, float *amax_out, float *scale_out, int64_t rows, int chunks_per_row,
                 cudaStream_t st) {
-  constexpr int kTeam = 32 * TEAM_WARPS;
-  constexpr int kRowsPerCta = kWarps / TEAM_WARPS;
-  const int per_thread = (chunks_per_row + kTeam - 1) / kTeam;
-  const unsigned grid = static_cast<unsigned>(ceil_div64(rows, kRowsPerCta));
-  const uint4 *i4 = static_cast<const uint4 *>(in);
-  uint8_t *o = static_cast<uint8_t *>(out);
-#define DTQ_ROW_CASE(N)                                                                                          \
-  rowwise_regs_kernel<IN, OUT, N, TEAM_WARPS><<<grid, kThreads, 0, st>>>(i4, o, amax_out, scale_out, rows, chunks_per_row)
-  if (per_thread <= 1) DTQ_ROW_CASE(1);
-  else if (per_thread <= 2) DTQ_ROW_CASE(2);
-  else if (per_thread <= 4) DTQ_ROW_CASE(4);
-  else if (per_thread <= 8) DTQ_ROW_CASE(8);
-  else DTQ_ROW_CASE(16);
-#undef DTQ_ROW_CASE
+  const unsigned grid = static_cast<unsigned>(TEAM_WARPS == 1 ? ceil_div64(rows, kWarps) : rows);
+  const int threads = TEAM_WARPS == 1 ? kThreads : 32 * TEAM_WARPS;
+  rowwise_regs_kernel<IN, OUT, CHUNKS, TEAM_WARPS><<<grid, threads, 0, st>>>(
+      static_cast<const uint4 *>(in), static_cast<uint8_t *>(out), amax_out, scale_out, rows, chunks_per_row);
   return cuda_status(cudaGetLastError());
+}
+
+// Smallest team that keeps a thread at <= 4 chunks (64 bytes in flight); the largest team may
+// hold up to 16.
+template <int IN, int OUT>
+int dispatch_regs(const void *in, void *out, float *amax_out, float *scale_out, int64_t rows, int chunks,
+                  cudaStream_t st) {
+#define DTQ_ROW(C, W) return launch_regs<IN, OUT, C, W>(in, out, amax_out, scale_out, rows, chunks, st)
+  if (chunks <= 32) DTQ_ROW(1, 1);
+  if (chunks <= 64) DTQ_ROW(2, 1);
+  if (chunks <= 128) DTQ_ROW(4, 1);
+  if (chunks <= 256) DTQ_ROW(4, 2);
+  if (chunks <= 512) DTQ_ROW(4, 4);
+  if (chunks <= 1024) DTQ_ROW(4, 8);
+  if (chunks <= 2048) DTQ_ROW(8, 8);
+  DTQ_ROW(16, 8);
+#undef DTQ_ROW
 }
 
 template <int IN, int OUT>
@@ -167,9 +182,8 @@ int launch(const void *in, void *out, float *amax_out, float *scale_out, int64_t
   using R = RowIn<IN>;
   const bool vec = aligned_to(in, 16) && aligned_to(out, R::kElems) && cols % R::kElems == 0;
   const int64_t chunks = cols / R::kElems;
-  if (vec && chunks <= 32 * 16) return launch_regs<IN, OUT, 1>(in, out, amax_out, scale_out, rows, int(chunks), st);
   if (vec && chunks <= kThreads * 16)
-    return launch_regs<IN, OUT, kWarps>(in, out, amax_out, scale_out, rows, int(chunks), st);
+    return dispatch_regs<IN, OUT>(in, out, amax_out, scale_out, rows, int(chunks), st);
   const int64_t max_grid = int64_t(dev.sm_count) * 8;
   const unsigned grid = static_cast<unsigned>(rows < max_grid ? rows : max_grid);
   uint8_t *o = static_cast<uint8_t *>(out);
