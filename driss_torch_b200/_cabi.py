@@ -28,6 +28,7 @@ SIGNATURES = {
     "dtq_workspace_status": ([_vp, _vp, _vp], _i32),
     "dtq_saturated_cast": ([_vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_amax": ([_vp, _vp, _i64, _i32, _vp, _sz, _vp], _i32),
+    "dtq_amax_static_scratch": ([_vp, _vp, _i64, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp, _sz, _vp], _i32),
     "dtq_cast_with_amax": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant_rowwise": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
@@ -110,6 +111,14 @@ def amax(x: torch.Tensor, out: torch.Tensor | None = None, ws: torch.Tensor | No
         load().dtq_amax(x.data_ptr(), out.data_ptr(), x.numel(), IN_CODE[x.dtype], ws.data_ptr(), ws.numel(), _stream()),
         "dtq_amax",
     )
+    return out
+
+
+def amax_static_scratch(x: torch.Tensor, out: torch.Tensor | None = None):
+    """amax through the entry point that allocates nothing (scratch inside the library image)."""
+    out = torch.empty(1, dtype=torch.float32, device=x.device) if out is None else out
+    check(load().dtq_amax_static_scratch(x.data_ptr(), out.data_ptr(), x.numel(), IN_CODE[x.dtype], _stream()),
+          "dtq_amax_static_scratch")
     return out
 
 

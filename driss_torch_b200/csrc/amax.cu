@@ -5,7 +5,9 @@
 // integer warp-max instruction per warp, and a last-block finish instead of one same-address
 // atomic per block on a pre-filled output.  The value is order independent, so the result is
 // bit-identical; NaNs are dropped and an empty input gives -inf, as in the reference.
+#include <atomic>
 #include <cmath>
+#include <mutex>
 
 #include "dtq_device.cuh"
 #include "dtq_grid.cuh"
@@ -138,6 +140,74 @@ extern "C" int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Workspace *ws = static_cast<Workspace *>(workspace);
   const int grid = amax_grid(numel, eb, dev);
+  const int64_t head = head_elems(in, eb, numel);
+  if (in_dtype == DTQ_BF16)
+    amax_kernel<DTQ_BF16, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+  else
+    amax_kernel<DTQ_F32, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+  return cuda_status(cudaGetLastError());
+}
+
+// ---- amax without any caller- or library-allocated scratch -------------------------------------------------
+//
+// Some hosts may not allocate device memory at the point where they need an amax: a runtime that
+// hands the whole device heap to its own pool and forbids cudaMalloc in plugins, or a
+// latency-critical section that cannot afford the device-wide synchronisation cudaMalloc and
+// cudaFree imply.  For them the scratch of the reduction lives in this library's image: one
+// Workspace in a file-scope __device__ array, present on every GPU that loads the library until
+// the process exits.
+//
+// In host code the array's NAME is only a host-side handle, not a device address, so the address
+// is looked up once per device with cudaGetSymbolAddress (with that device current) and cached.
+// One block per tile is launched, so the array's kMaxGridBlocks partial slots bound the input:
+// kMaxGridBlocks tiles of kAmaxThreads * DTQ_AMAX_UNROLL 16-byte chunks = DTQ_AMAX_STATIC_MAX_BYTES.
+namespace dtq {
+namespace {
+
+static __device__ __align__(256) unsigned char g_static_scratch[sizeof(Workspace)];
+
+constexpr int kStaticMaxDevices = 64;
+void *g_static_scratch_ptr[kStaticMaxDevices];
+std::atomic<int> g_static_scratch_ready[kStaticMaxDevices];
+std::mutex g_static_scratch_mutex;
+
+// Device address of the scratch array on the current device (looked up on first use).
+int static_scratch_address(Workspace **ws) {
+  int dev = 0;
+  DTQ_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kStaticMaxDevices) return DTQ_ERR_INVALID_ARGUMENT;
+  if (!g_static_scratch_ready[dev].load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (!g_static_scratch_ready[dev].load(std::memory_order_relaxed)) {
+      void *ptr = nullptr;
+      DTQ_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+      g_static_scratch_ptr[dev] = ptr;
+      g_static_scratch_ready[dev].store(1, std::memory_order_release);
+    }
+  }
+  *ws = static_cast<Workspace *>(g_static_scratch_ptr[dev]);
+  return DTQ_OK;
+}
+
+}  // namespace
+}  // namespace dtq
+
+extern "C" int dtq_amax_static_scratch(const void *in, float *out, int64_t numel, int in_dtype, void *stream) {
+  using namespace dtq;
+  static_assert(int64_t(kMaxGridBlocks) * kAmaxThreads * DTQ_AMAX_UNROLL * 16 == DTQ_AMAX_STATIC_MAX_BYTES,
+                "the documented limit must match the scratch array");
+  if (numel < 0 || !out || (numel > 0 && !in)) return DTQ_ERR_INVALID_ARGUMENT;
+  if (in_dtype != DTQ_BF16 && in_dtype != DTQ_F32) return DTQ_ERR_UNSUPPORTED_DTYPE;
+  const int eb = in_dtype == DTQ_BF16 ? 2 : 4;
+  if (numel > DTQ_AMAX_STATIC_MAX_BYTES / eb) return DTQ_ERR_TOO_LARGE;  // needs more partial slots than the array has
+  if (numel > 0 && !aligned_to(in, eb)) return DTQ_ERR_INVALID_ARGUMENT;
+  Workspace *ws = nullptr;
+  if (int e = static_scratch_address(&ws)) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: start the arrival counter from zero.
+  DTQ_CUDA_TRY(cudaMemsetAsync(&ws->arrivals, 0, sizeof(ws->arrivals), st));
+  const int64_t tiles = ceil_div64(numel * eb / 16, int64_t(kAmaxThreads) * DTQ_AMAX_UNROLL);
+  const int grid = static_cast<int>(tiles < 1 ? 1 : tiles);  // <= kMaxGridBlocks by the size check
   const int64_t head = head_elems(in, eb, numel);
   if (in_dtype == DTQ_BF16)
     amax_kernel<DTQ_BF16, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);

@@ -79,6 +79,25 @@ int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype, void *work
              size_t workspace_bytes, void *stream);
 
 /*
+ * dtq_amax for callers that cannot allocate device memory -- a host whose own pool owns the
+ * device heap and forbids cudaMalloc in plugins, or a latency-critical section that cannot
+ * take the device-wide synchronisation of cudaMalloc / cudaFree.  Same result as dtq_amax,
+ * but the reduction's scratch is a fixed array inside the library image (about 16.5 KB of
+ * device memory on every GPU that loads the library, until the process exits), so there is
+ * no workspace argument and the call allocates nothing.  Limits and rules:
+ *   - inputs of at most DTQ_AMAX_STATIC_MAX_BYTES bytes (one partial slot of the array per
+ *     64 KiB tile); larger inputs are rejected with DTQ_ERR_TOO_LARGE, nothing is launched;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture begins;
+ *   - every call on a device uses the same array: calls that may overlap on the GPU
+ *     (different streams, several host threads) race -- serialise them on one stream;
+ *   - the arrival counter in the array is cleared on `stream` before each launch.
+ * No counterpart in the reference (its amax allocates its output and relies on a fill launch).
+ */
+#define DTQ_AMAX_STATIC_MAX_BYTES (268435456LL) /* 256 MiB: 4096 tiles x 64 KiB */
+int dtq_amax_static_scratch(const void *in, float *out, int64_t numel, int in_dtype, void *stream);
+
+/*
  * Fused tensor-wise dynamic quantisation in ONE launch:
  *   amax = max |in| (>= 0);  scale_d = fp8_max / ((double)amax + 1e-12);
  *   out[i] = fp8_satfinite((float)(scale_d * (double)in[i])).
