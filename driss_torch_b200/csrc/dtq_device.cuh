@@ -1,6 +1,7 @@
 // Device-side building blocks shared by the quantization kernels (sm_100a).
 #pragma once
 
+#include <cmath>
 #include <cstdint>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -85,21 +86,35 @@ __device__ __forceinline__ float dsq_mul(double sd, float x) {
   return __double2float_rn(__dmul_rn(sd, static_cast<double>(x)));
 }
 
-// The double-precision product costs two 64-bit conversions per element on the slow
-// conversion pipe, which (not HBM) bounds a kernel that uses it for every element.  The final
-// fp8 byte, however, only depends on which side of an fp8 rounding boundary the reference value
-//   R = fp32_rne(fp64_rne(x * scale_d))
-// falls, and fp8 conversion is monotone.  So bracket R in fp32:
-//   lo = fp32(scale_d * (1 - 2^-21)),  hi = fp32(scale_d * (1 + 2^-21)),
-//   p_lo = fp32(x * lo),  p_hi = fp32(x * hi).
-// Every rounding involved is within 2^-24 relative, so R lies between p_lo and p_hi (for either
-// sign of x; underflow keeps the sign and everything that small converts to a signed zero;
-// overflow saturates on both sides; NaN stays NaN).  If both ends convert to the same fp8 byte,
-// that byte is fp8(R) exactly.  Otherwise (about 2^-16 of random elements) the caller recomputes
-// with the double product.
+// ---- the double-precision product without the 64-bit conversion pipe -----------------------------
+// Done literally, (float)(scale_d * (double)x) costs two 64-bit conversions per element on the
+// conversion (XU) pipe, and that pipe, not HBM, then bounds the kernel.  Two exact substitutes:
+//
+// (A) compensated fp32, for bf16 x and a bf16-valued amax in [0.25, 2^64] -- the normal case, amax
+//     being an element of the tensor.  With head = fp32(sd), tail = fp32(sd - head):
+//       r1 = fp32(x*head), c = fma(x, head, -r1) (exact), c2 = fma(x, tail, c), R' = fp32(r1 + c2).
+//     r1 + c2 differs from P = x*sd by < 2^-46 |P|, so R' equals the reference
+//     R = fp32(fp64(P)) unless P lies within 2^-46 of an fp32 rounding midpoint.  It cannot:
+//     P = Q(1+theta) with Q = 7n 2^k / m (n, m <= 255 the integer mantissas of x and amax; both fp8
+//     maxima are 7 * 2^j) and |theta| <= 1e-12/amax + 2^-51 <= 2^-36.9.  If m divides 7n 2^i, Q has
+//     at most 11 significant bits, is an fp32 number, and P stays within 2^-36.9 of it; otherwise
+//     |Q - M| >= 2^-33 |Q| for every 25-bit midpoint M (the difference of the two fractions is a
+//     non-zero integer over m times a power of two).  Results below the fp32 normal range convert to
+//     a signed zero either way; the sign is copied from x.  Products that overflow fp32 (possible
+//     only when the caller's amax is smaller than |x|) are detected and left infinite.
+//     This matters because with bf16 data about one e4m3 product in 128 sits exactly on an fp8
+//     rounding tie (sd is a ratio of small integers), so any scheme that falls back to fp64 "near
+//     a boundary" falls back in almost every warp.
+// (B) bracket, for everything else (fp32 x, arbitrary amax): fp8 conversion is monotone, so if
+//       fp8(fp32(x * fp32(sd(1 - 2^-21)))) == fp8(fp32(x * fp32(sd(1 + 2^-21))))
+//     that byte is fp8(R) (every rounding involved is within 2^-24; underflow keeps the sign,
+//     overflow saturates on both sides, NaN stays NaN); otherwise the pair is recomputed in fp64 by
+//     a never-inlined function, so that the 64-bit conversions stay behind a real branch.
 struct DsqScale {
   double sd;
-  float lo, hi;
+  float lo, hi;      // (B) bracket ends
+  float head, tail;  // (A) sd = head + tail + O(2^-48 sd)
+  bool compensated;  // (A) is valid for bf16 inputs
 };
 template <int OUT>
 __device__ __forceinline__ DsqScale make_dsq_scale(float amax) {
@@ -107,56 +122,97 @@ __device__ __forceinline__ DsqScale make_dsq_scale(float amax) {
   s.sd = dsq_scale<OUT>(amax);
   s.lo = __double2float_rn(s.sd * (1.0 - 0x1p-21));
   s.hi = __double2float_rn(s.sd * (1.0 + 0x1p-21));
+  s.head = __double2float_rn(s.sd);
+  s.tail = __double2float_rn(s.sd - static_cast<double>(s.head));
+  s.compensated = (__float_as_uint(amax) & 0xFFFFu) == 0u && amax >= 0.25f && amax <= 0x1p64f;
   return s;
 }
-// Two elements -> two fp8 bytes via the lower bracket end; `mismatch` collects (by OR) the
-// difference to the upper end's bytes.
+
+// (A) two bf16-valued elements -> two fp8 bytes.  BOUNDED: the caller guarantees |x| <= amax (or
+// NaN), so no product overflows.
+template <int OUT, bool BOUNDED>
+__device__ __forceinline__ uint32_t dsq_pair_compensated(float x0, float x1, const DsqScale &s) {
+  const float2 x = make_float2(x0, x1);
+  const float2 h = make_float2(s.head, s.head);
+  const float2 q = __fmul2_rn(x, make_float2(-s.head, -s.head));  // -r1
+  const float2 c = __ffma2_rn(x, h, q);                           // x*head - r1, exact
+  const float2 c2 = __ffma2_rn(x, make_float2(s.tail, s.tail), c);
+  float2 r = __ffma2_rn(q, make_float2(-1.0f, -1.0f), c2);        // r1 + c2, one rounding
+  if (!BOUNDED) {
+    if (fabsf(q.x) == INFINITY) r.x = -q.x;
+    if (fabsf(q.y) == INFINITY) r.y = -q.y;
+  }
+  return cvt_fp8x2<OUT>(copysignf(r.x, x0), copysignf(r.y, x1));
+}
+
+// (B) two elements -> the fp8 bytes of the lower bracket end and of the upper end.
 template <int OUT>
-__device__ __forceinline__ uint32_t dsq_pair_bracket(float x0, float x1, const DsqScale &s, uint32_t &mismatch) {
+__device__ __forceinline__ void dsq_pair_bracket(float x0, float x1, const DsqScale &s, uint32_t &lo_bytes,
+                                                 uint32_t &hi_bytes) {
   const float2 x = make_float2(x0, x1);
   const float2 pl = __fmul2_rn(x, make_float2(s.lo, s.lo));
   const float2 ph = __fmul2_rn(x, make_float2(s.hi, s.hi));
-  const uint32_t a = cvt_fp8x2<OUT>(pl.x, pl.y);
-  const uint32_t b = cvt_fp8x2<OUT>(ph.x, ph.y);
-  mismatch |= a ^ b;
-  return a;
+  lo_bytes = cvt_fp8x2<OUT>(pl.x, pl.y);
+  hi_bytes = cvt_fp8x2<OUT>(ph.x, ph.y);
 }
-// The exact recomputation lives in functions that are never inlined, so that it stays behind a
-// real branch: were it merged into the caller as predicated code, its 64-bit conversions would
-// occupy the conversion pipe for every element again.
+// fp32 -> fp64 is exact, so normal numbers are widened on the integer pipe (re-bias the exponent,
+// move the mantissa); zeros, subnormals, infinities and NaNs take the conversion instruction.
+__device__ __forceinline__ double widen_exact(float x) {
+  const uint32_t w = __float_as_uint(x);
+  const uint32_t a = w & 0x7FFFFFFFu;
+  const uint32_t e = a >> 23;
+  if (e - 1u >= 254u) return static_cast<double>(x);
+  return __hiloint2double(static_cast<int>((w & 0x80000000u) | ((a >> 3) + 0x38000000u)), static_cast<int>(w << 29));
+}
 template <int OUT>
-__device__ __noinline__ uint2 dsq_exact_bf16x8(uint4 v, double sd) {
-  uint2 r;
-  r.x = cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.x)), dsq_mul(sd, bf16_hi(v.x))) |
-        (cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.y)), dsq_mul(sd, bf16_hi(v.y))) << 16);
-  r.y = cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.z)), dsq_mul(sd, bf16_hi(v.z))) |
-        (cvt_fp8x2<OUT>(dsq_mul(sd, bf16_lo(v.w)), dsq_mul(sd, bf16_hi(v.w))) << 16);
+__device__ __forceinline__ uint32_t dsq_pair_exact(float x0, float x1, double sd) {
+  return cvt_fp8x2<OUT>(__double2float_rn(__dmul_rn(sd, widen_exact(x0))),
+                        __double2float_rn(__dmul_rn(sd, widen_exact(x1))));
+}
+// `r` = bytes of the lower bracket end, `m` = xor with the upper end's bytes: a non-zero 16-bit
+// half marks a pair to redo.
+template <int OUT>
+__device__ __noinline__ uint2 dsq_redo_bf16x8(uint4 v, uint2 r, uint2 m, double sd) {
+  if (m.x & 0xFFFFu) r.x = (r.x & 0xFFFF0000u) | dsq_pair_exact<OUT>(bf16_lo(v.x), bf16_hi(v.x), sd);
+  if (m.x >> 16) r.x = (r.x & 0xFFFFu) | (dsq_pair_exact<OUT>(bf16_lo(v.y), bf16_hi(v.y), sd) << 16);
+  if (m.y & 0xFFFFu) r.y = (r.y & 0xFFFF0000u) | dsq_pair_exact<OUT>(bf16_lo(v.z), bf16_hi(v.z), sd);
+  if (m.y >> 16) r.y = (r.y & 0xFFFFu) | (dsq_pair_exact<OUT>(bf16_lo(v.w), bf16_hi(v.w), sd) << 16);
   return r;
 }
 template <int OUT>
-__device__ __noinline__ uint32_t dsq_exact_f32x4(uint4 v, double sd) {
-  return cvt_fp8x4<OUT>(dsq_mul(sd, __uint_as_float(v.x)), dsq_mul(sd, __uint_as_float(v.y)),
-                        dsq_mul(sd, __uint_as_float(v.z)), dsq_mul(sd, __uint_as_float(v.w)));
+__device__ __noinline__ uint32_t dsq_redo_f32x4(uint4 v, uint32_t r, uint32_t m, double sd) {
+  if (m & 0xFFFFu) r = (r & 0xFFFF0000u) | dsq_pair_exact<OUT>(__uint_as_float(v.x), __uint_as_float(v.y), sd);
+  if (m >> 16) r = (r & 0xFFFFu) | (dsq_pair_exact<OUT>(__uint_as_float(v.z), __uint_as_float(v.w), sd) << 16);
+  return r;
 }
 // Eight bf16 (four packed words) -> eight fp8 bytes.
-template <int OUT>
+template <int OUT, bool BOUNDED>
 __device__ __forceinline__ uint2 dsq_convert_bf16x8(uint4 v, const DsqScale &s) {
-  uint32_t mismatch = 0;
-  uint2 r;
-  r.x = dsq_pair_bracket<OUT>(bf16_lo(v.x), bf16_hi(v.x), s, mismatch) |
-        (dsq_pair_bracket<OUT>(bf16_lo(v.y), bf16_hi(v.y), s, mismatch) << 16);
-  r.y = dsq_pair_bracket<OUT>(bf16_lo(v.z), bf16_hi(v.z), s, mismatch) |
-        (dsq_pair_bracket<OUT>(bf16_lo(v.w), bf16_hi(v.w), s, mismatch) << 16);
-  if (__builtin_expect(mismatch != 0, 0)) r = dsq_exact_bf16x8<OUT>(v, s.sd);
+  if (s.compensated) {
+    return make_uint2(dsq_pair_compensated<OUT, BOUNDED>(bf16_lo(v.x), bf16_hi(v.x), s) |
+                          (dsq_pair_compensated<OUT, BOUNDED>(bf16_lo(v.y), bf16_hi(v.y), s) << 16),
+                      dsq_pair_compensated<OUT, BOUNDED>(bf16_lo(v.z), bf16_hi(v.z), s) |
+                          (dsq_pair_compensated<OUT, BOUNDED>(bf16_lo(v.w), bf16_hi(v.w), s) << 16));
+  }
+  uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+  dsq_pair_bracket<OUT>(bf16_lo(v.x), bf16_hi(v.x), s, a0, b0);
+  dsq_pair_bracket<OUT>(bf16_lo(v.y), bf16_hi(v.y), s, a1, b1);
+  dsq_pair_bracket<OUT>(bf16_lo(v.z), bf16_hi(v.z), s, a2, b2);
+  dsq_pair_bracket<OUT>(bf16_lo(v.w), bf16_hi(v.w), s, a3, b3);
+  uint2 r = make_uint2(a0 | (a1 << 16), a2 | (a3 << 16));
+  const uint2 m = make_uint2(r.x ^ (b0 | (b1 << 16)), r.y ^ (b2 | (b3 << 16)));
+  if (__builtin_expect((m.x | m.y) != 0, 0)) r = dsq_redo_bf16x8<OUT>(v, r, m, s.sd);
   return r;
 }
 // Four fp32 -> four fp8 bytes.
 template <int OUT>
 __device__ __forceinline__ uint32_t dsq_convert_f32x4(uint4 v, const DsqScale &s) {
-  uint32_t mismatch = 0;
-  uint32_t r = dsq_pair_bracket<OUT>(__uint_as_float(v.x), __uint_as_float(v.y), s, mismatch) |
-               (dsq_pair_bracket<OUT>(__uint_as_float(v.z), __uint_as_float(v.w), s, mismatch) << 16);
-  if (__builtin_expect(mismatch != 0, 0)) r = dsq_exact_f32x4<OUT>(v, s.sd);
+  uint32_t a0, a1, b0, b1;
+  dsq_pair_bracket<OUT>(__uint_as_float(v.x), __uint_as_float(v.y), s, a0, b0);
+  dsq_pair_bracket<OUT>(__uint_as_float(v.z), __uint_as_float(v.w), s, a1, b1);
+  uint32_t r = a0 | (a1 << 16);
+  const uint32_t m = r ^ (b0 | (b1 << 16));
+  if (__builtin_expect(m != 0, 0)) r = dsq_redo_f32x4<OUT>(v, r, m, s.sd);
   return r;
 }
 

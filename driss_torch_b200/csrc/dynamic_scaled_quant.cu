@@ -63,6 +63,11 @@ namespace {
 #ifndef DTQ_FUSED_KEEP_REGS
 #define DTQ_FUSED_KEEP_REGS 1
 #endif
+// 1: the second pass holds two tiles in registers (next tile's loads in flight while the current
+// one is converted); 0: one tile, overlap comes from occupancy alone.
+#ifndef DTQ_FUSED_PIPELINE
+#define DTQ_FUSED_PIPELINE 1
+#endif
 #ifndef DTQ_DSQ_THREADS
 #define DTQ_DSQ_THREADS 256
 #endif
@@ -73,16 +78,17 @@ namespace {
 constexpr int kThreads = DTQ_DSQ_THREADS;
 
 // ---- per-chunk arithmetic ----------------------------------------------------------------------
-template <int IN, int OUT>
+// BOUNDED: |x| <= amax is guaranteed (amax was computed from the same data in this launch).
+template <int IN, int OUT, bool BOUNDED = false>
 struct DsqChunk;
 
-template <int OUT>
-struct DsqChunk<DTQ_BF16, OUT> {
+template <int OUT, bool BOUNDED>
+struct DsqChunk<DTQ_BF16, OUT, BOUNDED> {
   static constexpr int kElems = 8;
   static constexpr int kElemBytes = 2;
   static constexpr int kOutAlign = 8;
   __device__ static void convert_store(uint4 v, const DsqScale &s, uint8_t *out, int64_t chunk) {
-    stg_stream(out + chunk * kElems, dsq_convert_bf16x8<OUT>(v, s));
+    stg_stream(out + chunk * kElems, dsq_convert_bf16x8<OUT, BOUNDED>(v, s));
   }
   __device__ static float load_one(const void *in, int64_t i) {
     return __uint_as_float(uint32_t(static_cast<const uint16_t *>(in)[i]) << 16);
@@ -97,8 +103,8 @@ struct DsqChunk<DTQ_BF16, OUT> {
   }
 };
 
-template <int OUT>
-struct DsqChunk<DTQ_F32, OUT> {
+template <int OUT, bool BOUNDED>
+struct DsqChunk<DTQ_F32, OUT, BOUNDED> {
   static constexpr int kElems = 4;
   static constexpr int kElemBytes = 4;
   static constexpr int kOutAlign = 4;
@@ -152,7 +158,7 @@ template <int IN, int OUT, int UNROLL>
 __global__ void __launch_bounds__(kFusedThreads, DTQ_FUSED_BLOCKS_PER_SM)
 dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float *__restrict__ amax_out,
                  float *__restrict__ scale_out, int64_t numel, Workspace *ws, int smem_tiles) {
-  using C = DsqChunk<IN, OUT>;
+  using C = DsqChunk<IN, OUT, true>;
   extern __shared__ uint4 kept_smem[];  // [smem_tiles][UNROLL][kFusedThreads]
   __shared__ float smem32[32];
   __shared__ int flag;
@@ -223,9 +229,9 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   if (threadIdx.x == 0) { atomicMin(&stamps[3], now()); atomicMax(&stamps[4], now()); }
 #endif
 
-  // phase 2a: streamed tiles, newest first, two register buffers so that the next tile's loads
-  // are in flight while the current tile is converted and stored
-  {
+  // phase 2a: streamed tiles, newest first
+#if DTQ_FUSED_PIPELINE
+  {  // two register buffers: the next tile's loads are in flight while this one is converted
     uint4 va[UNROLL], vb[UNROLL];
     int64_t k = count - 1;
     const int64_t stop = kept - 1;  // tiles k > stop were streamed
@@ -240,6 +246,13 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
       --k;
     }
   }
+#else
+  for (int64_t k = count - 1; k >= kept; --k) {
+    uint4 v[UNROLL];
+    load_tile<UNROLL>(v, in, blockIdx.x + k * G, nchunks);
+    store_tile<C, UNROLL>(v, sd, out, blockIdx.x + k * G, nchunks);
+  }
+#endif
   // phase 2b: tiles kept in shared memory, then the one kept in registers
   for (int64_t k = kept - 1; k >= kRegTiles; --k) {
     uint4 v[UNROLL];
@@ -258,7 +271,7 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
 
 // ---- cast phase alone ---------------------------------------------------------------------------------
 template <int IN, int OUT, int UNROLL>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2048 / kThreads)
 cast_with_amax_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, const float *__restrict__ amax_p,
                       float *__restrict__ scale_out, int64_t numel) {
   using C = DsqChunk<IN, OUT>;

@@ -33,7 +33,7 @@ struct RowIn<DTQ_BF16> {
   }
   template <int OUT>
   __device__ static void convert_store(uint4 v, const DsqScale &s, uint8_t *dst) {
-    stg_stream(dst, dsq_convert_bf16x8<OUT>(v, s));
+    stg_stream(dst, dsq_convert_bf16x8<OUT, true>(v, s));
   }
   __device__ static float load_one(const void *p, int64_t i) {
     return __uint_as_float(uint32_t(static_cast<const uint16_t *>(p)[i]) << 16);

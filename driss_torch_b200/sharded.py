@@ -44,8 +44,8 @@ class _CudaKernels:
 class ShardedQuantizer:
     """Quantizes this rank's row shard of a matrix that is row-sharded over ``group``.
 
-    ``kernels`` supplies ``amax``, ``cast_with_amax``, ``mx_fp8_quantize`` and
-    ``dynamic_scaled_quant_rowwise``; it defaults to this package's CUDA ops and exists so
+    ``kernels`` supplies ``amax``, ``cast_with_amax``, ``dynamic_scaled_quant_with_scale``,
+    ``mx_fp8_quantize`` and ``dynamic_scaled_quant_rowwise``; it defaults to this package's CUDA ops and exists so
     that the host logic can be exercised on CPU ranks with another implementation.
     """
 
@@ -73,8 +73,11 @@ class ShardedQuantizer:
     def tensorwise(self, shard: torch.Tensor, dtype: torch.dtype):
         """Tensor-wise dynamic quantisation of the whole sharded matrix.
 
-        Returns ``(payload_shard, amax[1], scale[1])``; amax and scale are global.
+        Returns ``(payload_shard, amax[1], scale[1])``; amax and scale are global.  A single rank
+        needs no exchange and takes the fused single-launch op.
         """
+        if self.world_size == 1:
+            return self.kernels.dynamic_scaled_quant_with_scale(shard, dtype)
         amax = self.global_amax(shard)
         payload, scale = self.kernels.cast_with_amax(shard, amax, dtype)
         return payload, amax, scale

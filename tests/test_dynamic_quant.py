@@ -74,6 +74,24 @@ def test_every_bf16_bit_pattern_through_the_cast_phase(fp8_dtype):
         assert _bits(scale_out) == _bits(want_scale)
 
 
+@pytest.mark.parametrize("fp8_dtype", FP8_DTYPES)
+def test_every_bf16_pattern_against_every_amax_mantissa(fp8_dtype):
+    # amax is itself a bf16 value, so fp8_max / amax is a ratio of small integers and many bf16
+    # products land exactly on fp8 rounding ties (up to the 1e-12 in the scale): every mantissa
+    # of amax gives a different tie lattice.  One launch per amax over all 65536 inputs.
+    from driss_torch_b200 import _cabi
+
+    a = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).view(256, 256)
+    ad = a.cuda()
+    amax_dev = torch.zeros(1, device="cuda")
+    for exponent in (-3, -2, 0, 9, 40, 63, 64, 70):  # the compensated path covers [0.25, 2^64], the bracket path the rest
+        for mant in range(128, 256):
+            amax = mant / 128.0 * 2.0**exponent
+            want, _ = qo.cast_with_amax(a, amax, fp8_dtype)
+            got = _cabi.cast_with_amax(ad, amax_dev.fill_(amax), fp8_dtype)
+            assert_fp8_equal(got, want, fp8_dtype, f"amax={amax}")
+
+
 @pytest.mark.parametrize("in_dtype", IN_DTYPES)
 def test_fp32_rounding_boundaries(in_dtype):
     # products that land on or next to fp8 midpoints: the double product and its single

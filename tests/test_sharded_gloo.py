@@ -25,6 +25,7 @@ class OracleKernels:
     amax = staticmethod(qo.amax)
     mx_fp8_quantize = staticmethod(qo.mx_fp8_quantize)
     dynamic_scaled_quant_rowwise = staticmethod(qo.dynamic_scaled_quant_rowwise)
+    dynamic_scaled_quant_with_scale = staticmethod(qo.dynamic_scaled_quant)
 
     @staticmethod
     def cast_with_amax(x, amax, dtype):
