@@ -127,10 +127,14 @@ def algorithmic_bytes(op: str, rows: int, cols: int, s_in: int = 2) -> int:
 
 
 def time_rotating(fn, nsets: int, iters: int, warmup: int = 3):
-    """Median/min ms of fn(i % nsets); consecutive calls touch different buffer sets so that every
-    timed launch starts with its inputs out of L2.  A short spin kernel is queued first so that the
-    start event, the launch and the stop event are all enqueued while the GPU is still busy: the
-    interval then holds device time only, not the host's launch latency."""
+    """Device time of fn(i % nsets), two ways; consecutive calls touch different buffer sets, so every
+    launch starts with its inputs out of L2.  A spin kernel is queued first each time so that the
+    events and launches are enqueued while the GPU is busy: the intervals hold device time only.
+
+    Returns (steady, single, single_min) in ms: `steady` = `iters` launches back to back between one
+    event pair, divided by `iters` (what a pipeline of such launches sustains); `single` = median
+    over `iters` isolated launches, each between its own event pair (adds the start-up and drain of
+    a lone kernel, several microseconds that matter for the sub-100 us configurations)."""
     for i in range(warmup):
         fn(i % nsets)
     torch.cuda.synchronize()
@@ -143,12 +147,19 @@ def time_rotating(fn, nsets: int, iters: int, warmup: int = 3):
         b.record()
         b.synchronize()
         times.append(a.elapsed_time(b))
-    return statistics.median(times), min(times)
+    a, b = event_pair()
+    torch.cuda._sleep(4_000_000)  # about 2 ms: covers the host time of enqueueing `iters` launches
+    a.record()
+    for i in range(iters):
+        fn(i % nsets)
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b) / iters, statistics.median(times), min(times)
 
 
 # ---- the single-GPU per-op table (cfg1..cfg4) ----------------------------------------------------------------
 
-def per_op_table(dev, peak, iters: int):
+def per_op_table(dev, peak, iters: int, warmup: int = 3):
     import driss_torch_b200  # noqa: F401  (registers the ops; loads the CUDA libraries)
     from driss_torch_b200 import _cabi, workloads
 
@@ -163,11 +174,18 @@ def per_op_table(dev, peak, iters: int):
 
     rows = []
 
-    def line(cfg, op, shape, ms, ms_min, nbytes, ref_ms=None, note=None):
+    def timed(fn, nsets, iters):
+        return time_rotating(fn, nsets, iters, warmup)
+
+    def line(cfg, op, shape, t, nbytes, ref_t=None, note=None):
+        ms, single, single_min = t
+        ref_ms = ref_t[0] if ref_t else None
         gbs = nbytes / (ms * 1e-3) / 1e9
-        d = {"config": cfg, "op": op, "shape": list(shape), "us": round(ms * 1e3, 2), "us_min": round(ms_min * 1e3, 2),
+        d = {"config": cfg, "op": op, "shape": list(shape), "us": round(ms * 1e3, 2),
+             "us_single_launch": round(single * 1e3, 2), "us_single_launch_min": round(single_min * 1e3, 2),
              "algorithmic_bytes": nbytes, "GBps": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4),
-             "frac_of_nominal_8TBps": round(gbs / NOMINAL_HBM_GBS, 4)}
+             "frac_of_nominal_8TBps": round(gbs / NOMINAL_HBM_GBS, 4),
+             "GBps_single_launch": round(nbytes / (single * 1e-3) / 1e9, 1)}
         if ref_ms is not None:
             d["reference_kernel_us"] = round(ref_ms * 1e3, 2)
             d["speedup_vs_reference_kernel"] = round(ref_ms / ms, 2)
@@ -185,9 +203,9 @@ def per_op_table(dev, peak, iters: int):
     ns = sets_for(x.numel() * 3)
     xs = [x.clone() for _ in range(ns)]
     outs = [torch.empty(x.shape, dtype=E4M3, device=dev) for _ in range(ns)]
-    ms, mn = time_rotating(lambda i: _cabi.saturated_cast(xs[i], scale, E4M3, out=outs[i]), ns, iters)
-    rms = time_rotating(lambda i: ref.saturated_cast(xs[i], scale, E4M3, False), ns, iters)[0] if ref else None
-    line("cfg1", "saturated_cast", x.shape, ms, mn, algorithmic_bytes("saturated_cast", w.rows, w.cols), rms)
+    t = timed(lambda i: _cabi.saturated_cast(xs[i], scale, E4M3, out=outs[i]), ns, iters)
+    rt = timed(lambda i: ref.saturated_cast(xs[i], scale, E4M3, False), ns, iters) if ref else None
+    line("cfg1", "saturated_cast", x.shape, t, algorithmic_bytes("saturated_cast", w.rows, w.cols), rt)
     del xs, outs
 
     # cfg2: amax + fused dynamic_scaled_quant bf16 [8192,8192], e4m3 and e5m2
@@ -197,20 +215,23 @@ def per_op_table(dev, peak, iters: int):
     xs = [x.clone() for _ in range(ns)]
     outs = [torch.empty(x.shape, dtype=E4M3, device=dev) for _ in range(ns)]
     one = torch.empty(1, dtype=torch.float32, device=dev)
-    ms, mn = time_rotating(lambda i: _cabi.amax(xs[i], out=one), ns, iters)
-    rms = time_rotating(lambda i: ref.amax(xs[i]), ns, iters)[0] if ref else None
-    line("cfg2", "amax", x.shape, ms, mn, algorithmic_bytes("amax", w.rows, w.cols), rms)
+    t = timed(lambda i: _cabi.amax(xs[i], out=one), ns, iters)
+    rt = timed(lambda i: ref.amax(xs[i]), ns, iters) if ref else None
+    line("cfg2", "amax", x.shape, t, algorithmic_bytes("amax", w.rows, w.cols), rt)
+    t = timed(lambda i: _cabi.cast_with_amax(xs[i], one, E4M3, out=outs[i]), ns, iters)
+    line("cfg2", "cast_with_amax->e4m3", x.shape, t, algorithmic_bytes("cast_with_amax", w.rows, w.cols), None,
+         note="phase 2 of the sharded tensor-wise path (amax already on the device); no reference op")
     xf = None
     for dt_, name in ((E4M3, "e4m3"), (E5M2, "e5m2")):
         o = [t.view(dt_) for t in outs]
-        ms, mn = time_rotating(lambda i: _cabi.dynamic_scaled_quant(xs[i], dt_, out=o[i]), ns, iters)
-        rms = None
+        t = timed(lambda i: _cabi.dynamic_scaled_quant(xs[i], dt_, out=o[i]), ns, iters)
+        rt = None
         if ref:  # the reference instantiates fp32 input only: time it on float(x) (twice the input bytes)
             if xf is None:
-                xf = [t.float() for t in xs]
-            rms = time_rotating(lambda i: ref.dynamic_scaled_quant(xf[i], dt_), ns, iters)[0]
-        line("cfg2", f"dynamic_scaled_quant->{name}", x.shape, ms, mn,
-             algorithmic_bytes("dynamic_scaled_quant", w.rows, w.cols), rms,
+                xf = [t_.float() for t_ in xs]
+            rt = timed(lambda i: ref.dynamic_scaled_quant(xf[i], dt_), ns, iters)
+        line("cfg2", f"dynamic_scaled_quant->{name}", x.shape, t,
+             algorithmic_bytes("dynamic_scaled_quant", w.rows, w.cols), rt,
              note="compulsory bytes N*(2+1); a two-pass kernel moves N*(2*2+1) unless the re-read hits L2; "
                   "reference kernel timed on fp32 input")
     del xs, outs, xf
@@ -222,9 +243,9 @@ def per_op_table(dev, peak, iters: int):
     xs = [x.clone() for _ in range(ns)]
     ps = [torch.empty(x.shape, dtype=E4M3, device=dev) for _ in range(ns)]
     ss = [torch.empty(x.numel() // 32, dtype=torch.float8_e8m0fnu, device=dev) for _ in range(ns)]
-    ms, mn = time_rotating(lambda i: _cabi.mx_fp8_quantize(xs[i], payload=ps[i], scales=ss[i]), ns, iters)
-    rms = time_rotating(lambda i: ref.mx_fp8_quantize(xs[i], 32, 1, False, E4M3), ns, iters)[0] if ref else None
-    line("cfg3", "mx_fp8_quantize", x.shape, ms, mn, algorithmic_bytes("mx_fp8_quantize", w.rows, w.cols), rms)
+    t = timed(lambda i: _cabi.mx_fp8_quantize(xs[i], payload=ps[i], scales=ss[i]), ns, iters)
+    rt = timed(lambda i: ref.mx_fp8_quantize(xs[i], 32, 1, False, E4M3), ns, iters) if ref else None
+    line("cfg3", "mx_fp8_quantize", x.shape, t, algorithmic_bytes("mx_fp8_quantize", w.rows, w.cols), rt)
     del xs, ps, ss
 
     # cfg4: row-wise dynamic quant bf16 [32768,4096] (no reference op)
@@ -235,9 +256,9 @@ def per_op_table(dev, peak, iters: int):
     ps = [torch.empty(x.shape, dtype=E4M3, device=dev) for _ in range(ns)]
     am = torch.empty(w.rows, 1, dtype=torch.float32, device=dev)
     sc = torch.empty(w.rows, 1, dtype=torch.float32, device=dev)
-    ms, mn = time_rotating(
+    t = timed(
         lambda i: _cabi.dynamic_scaled_quant_rowwise(xs[i], E4M3, out=ps[i], amax_out=am, scale_out=sc), ns, iters)
-    line("cfg4", "dynamic_scaled_quant_rowwise", x.shape, ms, mn,
+    line("cfg4", "dynamic_scaled_quant_rowwise", x.shape, t,
          algorithmic_bytes("dynamic_scaled_quant_rowwise", w.rows, w.cols), None, note="no reference op")
     del xs, ps
     torch.cuda.empty_cache()
@@ -337,6 +358,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="total rows (smaller for profiling captures)")
+    ap.add_argument("--ops-table-only", action="store_true", help="only the cfg1-cfg4 per-op table (profiling captures)")
+    ap.add_argument("--op-iters", type=int, default=0, help="timed launches per op in the per-op table (default max(20, steps))")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -366,6 +389,10 @@ def main():
     from driss_torch_b200.host_pipeline import HostQuantizer
 
     peak, peak_kind = measured_peak()
+    if args.ops_table_only:
+        iters = args.op_iters or max(20, args.steps)
+        print(json.dumps({"ops": per_op_table(dev, peak, iters=iters, warmup=min(3, iters))}), flush=True)
+        return
     chunk_rows = args.rows // TOTAL_CHUNKS
     x = workloads.make_cfg5_shard(rank, world, chunk_rows=chunk_rows, cols=COLS, device=dev)
     rows_local = x.shape[0]
@@ -480,14 +507,19 @@ def main():
         roofline["note"] = ("achieved counts the compulsory N*(2+1) bytes; the tensor-wise dependency makes the kernel "
                             "read its input twice, physical traffic rate is two_pass_GBps")
         roofline["two_pass_GBps"] = dominant["two_pass_GBps"]
-    traffic_file = ROOT / "profiles" / "traffic.json"
-    if traffic_file.exists():
-        try:
-            per_elem = json.loads(traffic_file.read_text()).get(dominant["kernel"], {}).get("dram_bytes_per_element")
-            if per_elem is not None:
-                roofline["traffic"] = int(per_elem * rows_local * COLS)
-        except Exception:
-            pass
+    # DRAM read+write per launch from the ncu capture summarised in
+    # profiles/fused_and_mx_dram_traffic_512MiB.md, scaled to this launch: what the chip keeps out of
+    # DRAM (registers, shared memory, L2) is a constant, not a fraction.
+    n_local = rows_local * COLS
+    if dominant["kernel"] == "dynamic_scaled_quant (fused)":
+        roofline["traffic"] = int(max(3 * n_local, 5 * n_local - 138e6))
+    elif dominant["kernel"] == "mx_fp8_quantize":
+        roofline["traffic"] = int(3.03125 * n_local - min(54e6, 0.25 * n_local))
+    elif dominant["kernel"] == "cast_with_amax":
+        roofline["traffic"] = int(3 * n_local - min(47e6, 0.25 * n_local))
+    elif dominant["kernel"] == "amax":
+        roofline["traffic"] = int(2 * n_local)
+    roofline["traffic_source"] = "ncu dram__bytes_read+write on a 512 MiB case, scaled (profiles/fused_and_mx_dram_traffic_512MiB.md)"
 
     # ---- end to end: host buffers in, host buffers out ------------------------------------------------
     e2e = None
@@ -533,7 +565,7 @@ def main():
     if world == 1 and not args.no_ops_table:
         del x
         torch.cuda.empty_cache()
-        ops = per_op_table(dev, peak, iters=max(20, args.steps))
+        ops = per_op_table(dev, peak, iters=args.op_iters or max(20, args.steps))
 
     if rank == 0:
         out = {

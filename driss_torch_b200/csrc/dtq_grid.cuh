@@ -46,24 +46,44 @@ __device__ __forceinline__ float reduce_partials(const Workspace *ws, float *sme
   return block_max_nonneg(v, smem32, identity);
 }
 
-constexpr unsigned int kSpinLimit = 1u << 23;  // x ~100 ns sleep: gives up after about a second
+constexpr unsigned int kSpinLimit = 1u << 20;  // polls, each an L2 round trip plus a short sleep: gives up after about a second
 
-// Thread 0 waits until the generation word differs from `gen0`; every thread gets the verdict.
-__device__ __forceinline__ bool wait_generation(Workspace *ws, unsigned int gen0, int *flag) {
+// Grid barrier that also reduces a non-negative float maximum, for kernels whose blocks are all
+// co-resident.  `gen0` is the generation word as read by thread 0 BEFORE the block did anything
+// else; its parity picks the counter pair.  Thread 0 folds the block's value into the running
+// maximum, fences, takes a ticket; the last arriver clears the other parity's pair (the previous
+// launch is long over) and bumps the generation for the next launch.  Everybody then waits for
+// the count to reach gridDim.x (bounded spin) and reads the maximum.  Returns false on timeout
+// (status word set, nothing may be assumed about `*result`).
+__device__ __forceinline__ bool grid_max_barrier(Workspace *ws, unsigned int gen0, float block_value, int *flag,
+                                                 float *shared_result, float *result) {
   if (threadIdx.x == 0) {
-    unsigned int spins = 0;
+    const unsigned int slot = gen0 & 1u;
+    atomicMax(&ws->bar_max[slot], __float_as_uint(block_value));
+    __threadfence();
+    const unsigned int ticket = atomicAdd(&ws->bar_count[slot], 1u);
     bool ok = true;
-    while (ld_acquire(&ws->generation) == gen0) {
-      if (++spins > kSpinLimit) {
-        ok = false;
-        atomicExch(&ws->status, DTQ_ERR_TIMEOUT);
-        break;
+    if (ticket == gridDim.x - 1) {
+      ws->bar_count[slot ^ 1u] = 0;
+      ws->bar_max[slot ^ 1u] = 0;
+      atomicAdd(&ws->generation, 1u);
+    } else {
+      unsigned int spins = 0;
+      while (ld_acquire(&ws->bar_count[slot]) != gridDim.x) {
+        if (++spins > kSpinLimit) {
+          ok = false;
+          atomicExch(&ws->status, DTQ_ERR_TIMEOUT);
+          break;
+        }
+        __nanosleep(20);
       }
-      __nanosleep(100);
     }
+    __threadfence();
+    *shared_result = __uint_as_float(ld_acquire(&ws->bar_max[slot]));
     *flag = ok;
   }
   __syncthreads();
+  *result = *shared_result;
   const bool ok = *flag != 0;
   __syncthreads();
   return ok;

@@ -18,7 +18,11 @@ struct alignas(256) Workspace {
   unsigned int generation;  // bumped by the last-arriving block; waiters spin on it (bounded)
   int status;               // sticky: DTQ_ERR_TIMEOUT if a bounded wait ever gave up
   float amax;               // the reduced value of the current launch, valid after the bump
-  unsigned int pad[60];
+  // The fused kernel's grid barrier: arrival count and running maximum (as float bits), one pair
+  // per parity of `generation`; a launch uses the pair of its parity and clears the other.
+  unsigned int bar_count[2];
+  unsigned int bar_max[2];
+  unsigned int pad[56];
   float partials[kMaxGridBlocks];
 };
 

@@ -11,8 +11,8 @@
 // kernel makes as little of that second look as possible come from HBM:
 //   phase 1  each block keeps its FIRST tile in registers and its next few tiles in shared
 //            memory (filled through the registers the max is taken from), then streams the rest;
-//   finish   the last-arriving block reduces the per-block partials, writes amax / scale and
-//            bumps a generation word; the others wait on it with a bounded spin;
+//   finish   every block folds its maximum into one word with an atomic max and takes a ticket;
+//            all wait, with a bounded spin, until the ticket count reaches the grid size;
 //   phase 2  each block converts its streamed tiles newest-first, so the re-read starts with
 //            what L2 still holds (about 50 MB on B200, measured), with the next tile's loads in
 //            flight while the current one is converted and stored; then the tiles it kept in
@@ -64,9 +64,10 @@ namespace {
 #define DTQ_FUSED_KEEP_REGS 1
 #endif
 // 1: the second pass holds two tiles in registers (next tile's loads in flight while the current
-// one is converted); 0: one tile, overlap comes from occupancy alone.
+// one is converted); 0: one tile, overlap comes from the other warps.  Measured on B200: 1 is 1 %
+// faster at 4 GiB, 4 % slower at 128 MiB (register pressure), so 0.
 #ifndef DTQ_FUSED_PIPELINE
-#define DTQ_FUSED_PIPELINE 1
+#define DTQ_FUSED_PIPELINE 0
 #endif
 #ifndef DTQ_DSQ_THREADS
 #define DTQ_DSQ_THREADS 256
@@ -164,11 +165,6 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   __shared__ int flag;
   unsigned int gen0 = 0;
   if (threadIdx.x == 0) gen0 = ld_acquire(&ws->generation);
-#ifdef DTQ_FUSED_TIMING
-  unsigned long long *stamps = reinterpret_cast<unsigned long long *>(ws->pad);
-  auto now = [] { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
-  if (threadIdx.x == 0) atomicMin(&stamps[0], now());
-#endif
 
   const int64_t nchunks = numel / C::kElems;
   constexpr int64_t kTile = int64_t(kFusedThreads) * UNROLL;
@@ -191,9 +187,11 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) C::absmax(a, b, first_tile[u]);
   }
-  for (int64_t k = kRegTiles; k < count; ++k) {
-    uint4 v[UNROLL];
+  for (int64_t k = kRegTiles; k < count; k += 2) {  // two tiles (2 * UNROLL loads) in flight
+    uint4 v[UNROLL], w[UNROLL];
+    const bool second = k + 1 < count;
     load_tile<UNROLL>(v, in, blockIdx.x + k * G, nchunks);
+    if (second) load_tile<UNROLL>(w, in, blockIdx.x + (k + 1) * G, nchunks);
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) C::absmax(a, b, v[u]);
     if (k < kept) {
@@ -201,33 +199,28 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) slot[u * kFusedThreads] = v[u];
     }
+    if (second) {
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) C::absmax(a, b, w[u]);
+      if (k + 1 < kept) {
+        uint4 *slot = kept_smem + (k + 1 - kRegTiles) * kTile + threadIdx.x;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) slot[u * kFusedThreads] = w[u];
+      }
+    }
   }
   if (blockIdx.x == 0 && tail0 + threadIdx.x < numel) a = fmaxf(a, fabsf(C::load_one(in, tail0 + threadIdx.x)));
 
   // finish
-#ifdef DTQ_FUSED_TIMING
-  if (threadIdx.x == 0) { atomicMin(&stamps[1], now()); atomicMax(&stamps[2], now()); }
-#endif
   const float block_value = block_max_nonneg(fmaxf(a, b), smem32, 0.0f);
-  if (publish_and_ticket(ws, block_value, &flag)) {
-    const float total = reduce_partials(ws, smem32, 0.0f);
-    if (threadIdx.x == 0) {
-      ws->amax = total;
-      if (amax_out) *amax_out = total;
-      if (scale_out) *scale_out = static_cast<float>(dsq_scale<OUT>(total));
-      ws->arrivals = 0;
-      __threadfence();
-      atomicAdd(&ws->generation, 1u);
-    }
-    __syncthreads();
-  } else if (!wait_generation(ws, gen0, &flag)) {
-    return;  // status word says why; nothing more is written
+  __shared__ float amax_shared;
+  float amax;
+  if (!grid_max_barrier(ws, gen0, block_value, &flag, &amax_shared, &amax)) return;  // status word says why
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (amax_out) *amax_out = amax;
+    if (scale_out) *scale_out = static_cast<float>(dsq_scale<OUT>(amax));
   }
-  const float amax = ld_relaxed_f32(&ws->amax);
   const DsqScale sd = make_dsq_scale<OUT>(amax);
-#ifdef DTQ_FUSED_TIMING
-  if (threadIdx.x == 0) { atomicMin(&stamps[3], now()); atomicMax(&stamps[4], now()); }
-#endif
 
   // phase 2a: streamed tiles, newest first
 #if DTQ_FUSED_PIPELINE
@@ -262,9 +255,6 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
     store_tile<C, UNROLL>(v, sd, out, blockIdx.x + k * G, nchunks);
   }
   if (kRegTiles && count > 0) store_tile<C, UNROLL>(first_tile, sd, out, blockIdx.x, nchunks);
-#ifdef DTQ_FUSED_TIMING
-  if (threadIdx.x == 0) { atomicMin(&stamps[5], now()); atomicMax(&stamps[6], now()); }
-#endif
   if (blockIdx.x == 0 && tail0 + threadIdx.x < numel)
     out[tail0 + threadIdx.x] = cvt_fp8<OUT>(dsq_mul(sd.sd, C::load_one(in, tail0 + threadIdx.x)));
 }
