@@ -125,6 +125,20 @@ int64_t head_elems(const void *p, int elem_bytes, int64_t numel) {
   return h < numel ? h : numel;
 }
 
+// Arguments already validated; `out` may be any device float (the fused op points it into its
+// workspace when it splits a very large tensor into amax + cast).
+int launch_amax(const void *in, float *out, int64_t numel, int in_dtype, Workspace *ws, const DeviceInfo &dev,
+                cudaStream_t st) {
+  const int eb = in_dtype == DTQ_BF16 ? 2 : 4;
+  const int grid = amax_grid(numel, eb, dev);
+  const int64_t head = head_elems(in, eb, numel);
+  if (in_dtype == DTQ_BF16)
+    amax_kernel<DTQ_BF16, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+  else
+    amax_kernel<DTQ_F32, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+  return cuda_status(cudaGetLastError());
+}
+
 }  // namespace dtq
 
 extern "C" int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype, void *workspace,
@@ -133,19 +147,10 @@ extern "C" int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype,
   if (numel < 0 || !out || (numel > 0 && !in)) return DTQ_ERR_INVALID_ARGUMENT;
   if (in_dtype != DTQ_BF16 && in_dtype != DTQ_F32) return DTQ_ERR_UNSUPPORTED_DTYPE;
   if (!workspace || workspace_bytes < sizeof(Workspace) || !aligned_to(workspace, 256)) return DTQ_ERR_WORKSPACE;
-  const int eb = in_dtype == DTQ_BF16 ? 2 : 4;
-  if (numel > 0 && !aligned_to(in, eb)) return DTQ_ERR_INVALID_ARGUMENT;
+  if (numel > 0 && !aligned_to(in, in_dtype == DTQ_BF16 ? 2 : 4)) return DTQ_ERR_INVALID_ARGUMENT;
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  Workspace *ws = static_cast<Workspace *>(workspace);
-  const int grid = amax_grid(numel, eb, dev);
-  const int64_t head = head_elems(in, eb, numel);
-  if (in_dtype == DTQ_BF16)
-    amax_kernel<DTQ_BF16, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
-  else
-    amax_kernel<DTQ_F32, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
-  return cuda_status(cudaGetLastError());
+  return launch_amax(in, out, numel, in_dtype, static_cast<Workspace *>(workspace), dev, static_cast<cudaStream_t>(stream));
 }
 
 // ---- amax without any caller- or library-allocated scratch -------------------------------------------------

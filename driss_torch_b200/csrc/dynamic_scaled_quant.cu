@@ -35,9 +35,8 @@
 namespace dtq {
 
 // from amax.cu
-template <int IN>
-struct AbsMax;
-int64_t head_elems(const void *p, int elem_bytes, int64_t numel);
+int launch_amax(const void *in, float *out, int64_t numel, int in_dtype, Workspace *ws, const DeviceInfo &dev,
+                cudaStream_t st);
 
 namespace {
 
@@ -66,6 +65,13 @@ namespace {
 // 1: the second pass holds two tiles in registers (next tile's loads in flight while the current
 // one is converted); 0: one tile, overlap comes from the other warps.  Measured on B200: 1 is 1 %
 // faster at 4 GiB, 4 % slower at 128 MiB (register pressure), so 0.
+// Inputs above this many bytes are quantised as amax kernel + cast kernel instead of the single
+// fused launch: what the chip can keep between the two looks (about 140 MB) no longer matters at
+// that size, and the two stream kernels run at higher occupancy than the persistent fused one
+// (measured at 512 MiB: 199 us against 209 us; at 128 MiB the fused launch wins 48 us to 60 us).
+#ifndef DTQ_FUSED_MAX_BYTES
+#define DTQ_FUSED_MAX_BYTES (int64_t(320) << 20)
+#endif
 #ifndef DTQ_FUSED_PIPELINE
 #define DTQ_FUSED_PIPELINE 0
 #endif
@@ -260,14 +266,18 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
 }
 
 // ---- cast phase alone ---------------------------------------------------------------------------------
-template <int IN, int OUT, int UNROLL>
+// BOUNDED: *amax_p is the maximum of this very input (no product can overflow).
+template <int IN, int OUT, int UNROLL, bool BOUNDED>
 __global__ void __launch_bounds__(kThreads, 2048 / kThreads)
 cast_with_amax_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, const float *__restrict__ amax_p,
-                      float *__restrict__ scale_out, int64_t numel) {
-  using C = DsqChunk<IN, OUT>;
+                      float *__restrict__ scale_out, float *__restrict__ amax_out, int64_t numel) {
+  using C = DsqChunk<IN, OUT, BOUNDED>;
   const float amax = fmaxf(*amax_p, 0.0f);
   const DsqScale sd = make_dsq_scale<OUT>(amax);
-  if (scale_out && blockIdx.x == 0 && threadIdx.x == 0) *scale_out = static_cast<float>(sd.sd);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (scale_out) *scale_out = static_cast<float>(sd.sd);
+    if (amax_out) *amax_out = amax;
+  }
   const int64_t nchunks = numel / C::kElems;
   constexpr int64_t kTile = int64_t(kThreads) * UNROLL;
   for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
@@ -370,7 +380,16 @@ int launch_fused(const void *in, void *out, float *amax_out, float *scale_out, i
                  const DeviceInfo &dev, cudaStream_t st) {
   using C = DsqChunk<IN, OUT>;
   uint8_t *o = static_cast<uint8_t *>(out);
-  if (aligned_to(in, 16) && aligned_to(out, C::kOutAlign) && dev.cooperative) {
+  const bool vector_ok = aligned_to(in, 16) && aligned_to(out, C::kOutAlign);
+  if (vector_ok && numel * C::kElemBytes > DTQ_FUSED_MAX_BYTES) {
+    if (int e = launch_amax(in, &ws->amax, numel, IN, ws, dev, st)) return e;
+    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * DTQ_DSQ_UNROLL);
+    const int grid = balanced_grid(tiles, int64_t(dev.sm_count) * DTQ_CAST_BLOCKS_PER_SM);
+    cast_with_amax_stream<IN, OUT, DTQ_DSQ_UNROLL, true><<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in), o,
+                                                                                   &ws->amax, scale_out, amax_out, numel);
+    return cuda_status(cudaGetLastError());
+  }
+  if (vector_ok && dev.cooperative) {
     static FusedPlan cache[64];
     static std::atomic<int> ready[64];
     auto kernel = dsq_fused_kernel<IN, OUT, DTQ_DSQ_UNROLL>;
@@ -408,8 +427,8 @@ int launch_cast(const void *in, void *out, const float *amax, float *scale_out, 
   if (aligned_to(in, 16) && aligned_to(out, C::kOutAlign)) {
     const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * DTQ_DSQ_UNROLL);
     const int grid = balanced_grid(tiles, max_grid);
-    cast_with_amax_stream<IN, OUT, DTQ_DSQ_UNROLL><<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in), o, amax,
-                                                                             scale_out, numel);
+    cast_with_amax_stream<IN, OUT, DTQ_DSQ_UNROLL, false><<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in), o,
+                                                                                    amax, scale_out, nullptr, numel);
   } else {
     const int64_t blocks = ceil_div64(numel, kThreads);
     const int grid = static_cast<int>(blocks < 1 ? 1 : (blocks < max_grid ? blocks : max_grid));

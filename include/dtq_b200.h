@@ -98,7 +98,9 @@ int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype, void *work
 int dtq_amax_static_scratch(const void *in, float *out, int64_t numel, int in_dtype, void *stream);
 
 /*
- * Fused tensor-wise dynamic quantisation in ONE launch:
+ * Fused tensor-wise dynamic quantisation in ONE launch (inputs above 320 MiB, where nothing
+ * can stay on chip between the two looks at the data, are issued as an amax launch followed
+ * by a cast launch on the same stream instead):
  *   amax = max |in| (>= 0);  scale_d = fp8_max / ((double)amax + 1e-12);
  *   out[i] = fp8_satfinite((float)(scale_d * (double)in[i])).
  * amax_out / scale_out (one fp32 each, nullable) receive amax and

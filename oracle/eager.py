@@ -74,7 +74,7 @@ def mx_fp8_quantize_eager(a: torch.Tensor):
     e = torch.where(be == 0, torch.where(bits == 0, -128, -126), e)
     E = e.amax(dim=2, keepdim=True)
     biased = (E - 8 + 127).clamp(0, 255)
-    inv = torch.ldexp(torch.ones(biased.shape, dtype=torch.float32), 127 - biased)
+    inv = torch.ldexp(torch.ones(biased.shape, dtype=torch.float32, device=biased.device), 127 - biased)
     p = (x * inv).clamp(min=-448.0, max=448.0).to(torch.float8_e4m3fn).reshape(M, N)
     scales = biased.clamp(max=254).to(torch.uint8).reshape(-1).view(torch.float8_e8m0fnu)
     return p, scales

@@ -1,0 +1,105 @@
+"""Full-size checks (GPU) at the benchmark configurations, where the CPU oracle would take too
+long: the CUDA kernels against the tensor-level eager forms of the same arithmetic evaluated
+with stock PyTorch ops on the GPU (an independent implementation), plus size-independent
+properties: chunked == whole, a checksum of checksums, dequantisation error bounds."""
+import pytest
+import torch
+
+from conftest import as_bytes
+from driss_torch_b200 import workloads
+from oracle import eager
+from oracle import quant_oracle as qo
+
+pytestmark = pytest.mark.gpu
+E4M3, E5M2 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+def _same(a, b, what):
+    a8, b8 = a.view(torch.uint8), b.view(torch.uint8)
+    if not torch.equal(a8, b8):
+        raise AssertionError(f"{what}: {(a8 != b8).sum().item()} of {a8.numel()} bytes differ")
+
+
+def test_cfg1_saturated_cast_full_size():
+    import driss_torch_b200 as dt
+
+    x = workloads.make_cfg1(device="cuda")
+    scale = workloads.tensor_scale(x, E4M3)
+    got = dt.saturated_cast(x, scale, E4M3)
+    _same(got, eager.saturated_cast_kernel_faithful(x, scale, E4M3), "cfg1 vs eager (bf16 scale)")
+    rows = slice(1000, 1064)
+    _same(got[rows].cpu(), qo.saturated_cast(x[rows].cpu(), scale.item(), E4M3), "cfg1 rows vs oracle")
+
+
+@pytest.mark.parametrize("fp8_dtype", [E4M3, E5M2])
+def test_cfg2_amax_and_fused_full_size(fp8_dtype):
+    import driss_torch_b200 as dt
+
+    x = workloads.make_cfg2(device="cuda")
+    amax = dt.amax(x)
+    assert amax.item() == x.abs().max().float().item()
+    p, am, sc = dt.dynamic_scaled_quant_with_scale(x, fp8_dtype)
+    assert am.item() == amax.item()
+    _same(p, eager.dynamic_scaled_quant_eager(x, fp8_dtype), "cfg2 fused vs eager (fp64)")
+    _same(dt.dynamic_scaled_quant(x, fp8_dtype), p, "with and without extra outputs")
+    p2, sc2 = dt.cast_with_amax(x, amax, fp8_dtype)
+    _same(p2, p, "amax + cast vs fused")
+    assert sc2.item() == sc.item()
+    rows = slice(4000, 4032)
+    want, _ = qo.cast_with_amax(x[rows].cpu(), amax.item(), fp8_dtype)
+    _same(p[rows].cpu(), want, "cfg2 rows vs oracle")
+
+
+def test_cfg3_mx_full_size():
+    import driss_torch_b200 as dt
+
+    x = workloads.make_cfg3(device="cuda")
+    p, s = dt.mx_fp8_quantize(x)
+    ep, es = eager.mx_fp8_quantize_eager(x)
+    _same(p, ep, "cfg3 payload vs eager")
+    _same(s, es, "cfg3 scales vs eager")
+    assert not p.float().isnan().any()
+    # dequantised value within half an e4m3 step of the scaled input
+    scale = torch.ldexp(torch.ones((), device="cuda"), s.view(torch.uint8).to(torch.int32) - 127).view(x.shape[0], -1, 1)
+    deq = p.float().view(x.shape[0], -1, 32) * scale
+    err = (deq - x.float().view(x.shape[0], -1, 32)).abs()
+    assert (err <= scale * 16.0 + 1e-30).all()  # largest e4m3 step below 256 is 32
+    rows = slice(9000, 9016)
+    wp, ws_ = qo.mx_fp8_quantize(x[rows].cpu())
+    _same(p[rows].cpu(), wp, "cfg3 rows vs oracle")
+
+
+def test_cfg4_rowwise_full_size():
+    import driss_torch_b200 as dt
+
+    x = workloads.make_cfg4(device="cuda")
+    p, am, sc = dt.dynamic_scaled_quant_rowwise(x, E4M3)
+    ep, eam, esc = eager.dynamic_scaled_quant_rowwise_eager(x, E4M3)
+    _same(p, ep, "cfg4 payload vs eager (fp64)")
+    assert torch.equal(am, eam) and torch.equal(sc, esc)
+    # every row uses its full range: the row maximum maps to +-448
+    assert (p.float().abs().amax(dim=1) == 448.0).all()
+
+
+def test_large_input_split_path_and_chunk_invariance():
+    # 384 MiB: above the size where the fused op issues amax + cast launches instead of its
+    # single launch; the result must not depend on that, nor on how the rows are chunked.
+    import driss_torch_b200 as dt
+    from driss_torch_b200 import _cabi
+
+    x = torch.cat([workloads.make_cfg5_chunk(c, rows=3072, device="cuda") for c in range(8)])
+    assert x.numel() * 2 > 320 << 20
+    p, am, sc = dt.dynamic_scaled_quant_with_scale(x, E4M3)
+    assert am.item() == x.abs().max().float().item()
+    _same(p, eager.dynamic_scaled_quant_eager(x, E4M3), "split path vs eager (fp64)")
+    parts = [dt.cast_with_amax(x[i * 3072:(i + 1) * 3072], am, E4M3)[0] for i in range(8)]
+    _same(torch.cat(parts), p, "chunked vs whole")
+    mx_p, mx_s = dt.mx_fp8_quantize(x)
+    mx_parts = [dt.mx_fp8_quantize(x[i * 3072:(i + 1) * 3072]) for i in range(8)]
+    _same(torch.cat([q[0] for q in mx_parts]), mx_p, "mx chunked vs whole")
+    _same(torch.cat([q[1] for q in mx_parts]), mx_s, "mx scales chunked vs whole")
+    # checksum of checksums
+    total = sum(int(q.view(torch.uint8).sum(dtype=torch.int64)) for q in parts)
+    assert total == int(p.view(torch.uint8).sum(dtype=torch.int64))
+    assert _cabi.workspace_status(_cabi.workspace()) == 0
+    dt.check_device_status()
