@@ -358,6 +358,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--rows", type=int, default=TOTAL_ROWS, help="total rows (smaller for profiling captures)")
+    ap.add_argument("--exchange", choices=["auto", "p2p", "nccl"], default="auto",
+                    help="N > 1: how the per-GPU maxima meet: inside the one fused launch over NVLink peer memory (p2p), "
+                         "or an NCCL all-reduce between an amax launch and a cast launch (nccl); auto = p2p for shards up to 1.5 GiB "
+                         "(measured: the single persistent launch wins there, two stream launches win above)")
     ap.add_argument("--ops-table-only", action="store_true", help="only the cfg1-cfg4 per-op table (profiling captures)")
     ap.add_argument("--op-iters", type=int, default=0, help="timed launches per op in the per-op table (default max(20, steps))")
     args = ap.parse_args()
@@ -406,9 +410,33 @@ def main():
     # At N == 1 the exchange disappears; amax + cast are then exactly the two launches that
     # dtq_dynamic_scaled_quant itself issues for an input this large (above 320 MiB it does not use
     # its single fused launch, see csrc/dynamic_scaled_quant.cu), timed separately here.
-    names = ["amax", "cast_with_amax", "mx_fp8_quantize"] if world == 1 else \
-            ["amax", "all_reduce(max) [NCCL]", "cast_with_amax", "mx_fp8_quantize"]
-    my_launches_per_step = 3
+    exchange, peer_ptrs, exchange_note = "none", None, None
+    if world > 1:
+        exchange = args.exchange
+        if exchange == "auto":
+            exchange = "p2p" if rows_local * COLS * 2 <= 1.5 * 2**30 else "nccl"
+        if exchange == "p2p":
+            try:
+                from driss_torch_b200.sharded import ShardedQuantizer
+
+                sq = ShardedQuantizer(fused_exchange=True, device=dev)
+                peer_ptrs = sq._exchange["ptrs"]
+            except Exception as exc:  # symmetric memory unavailable on this box: fall back, and say so
+                exchange, exchange_note = "nccl", f"p2p exchange unavailable ({type(exc).__name__}: {exc}); used NCCL"
+            ok = torch.tensor([1 if exchange == "p2p" else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
+                exchange = "nccl"
+    if exchange == "p2p":
+        names = ["dynamic_scaled_quant_p2p (amax + NVLink exchange + cast, one launch)", "mx_fp8_quantize"]
+        my_launches_per_step = 2
+    elif exchange == "nccl":
+        names = ["amax", "all_reduce(max) [NCCL]", "cast_with_amax", "mx_fp8_quantize"]
+        my_launches_per_step = 3
+    else:
+        names = ["amax", "cast_with_amax", "mx_fp8_quantize"]
+        my_launches_per_step = 3
+    epoch = [0]
 
     def step(events=None):
         marks = []
@@ -420,13 +448,19 @@ def main():
                 marks.append(e)
 
         mark()
-        _cabi.amax(x, out=amax, ws=ws)
-        mark()
-        if world > 1:
-            dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+        if exchange == "p2p":
+            epoch[0] += 1
+            _cabi.dynamic_scaled_quant_p2p(x, E4M3, peer_ptrs, rank, epoch[0], out=payload, amax_out=amax,
+                                           scale_out=scale, ws=ws)
             mark()
-        _cabi.cast_with_amax(x, amax, E4M3, out=payload, scale_out=scale)
-        mark()
+        else:
+            _cabi.amax(x, out=amax, ws=ws)
+            mark()
+            if world > 1:
+                dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+                mark()
+            _cabi.cast_with_amax(x, amax, E4M3, out=payload, scale_out=scale)
+            mark()
         _cabi.mx_fp8_quantize(x, payload=mx_payload, scales=mx_scales)
         mark()
         if events is not None:
@@ -487,7 +521,7 @@ def main():
         if "NCCL" in name:
             kernels.append({"kernel": name, "ms": round(ms, 4), "bytes": 4})
             continue
-        op = name
+        op = "dynamic_scaled_quant" if name.startswith("dynamic_scaled_quant_p2p") else name
         nbytes = algorithmic_bytes(op, rows_local, COLS)
         gbs = nbytes / (ms * 1e-3) / 1e9
         k = {"kernel": name, "ms": round(ms, 4), "algorithmic_bytes_per_launch": nbytes, "GBps": round(gbs, 1),
@@ -498,8 +532,8 @@ def main():
     roofline = {"bound": "hbm", "kernel": dominant["kernel"], "achieved": dominant["GBps"], "peak": peak,
                 "unit": "GB/s", "frac": round(dominant["GBps"] / peak, 4), "peak_kind": f"of {peak_kind}",
                 "traffic": None, "frac_of_nominal_8TBps": dominant["frac_of_nominal_8TBps"]}
-    tw_ms = sum(k["ms"] for k in mine if k["kernel"] in ("amax", "cast_with_amax"))
-    roofline["note"] = ("tensor-wise quant = amax + cast launches: together %.4f ms for %d compulsory bytes N*(2+1) "
+    tw_ms = sum(k["ms"] for k in mine if not k["kernel"].startswith("mx"))
+    roofline["note"] = ("tensor-wise quant (amax and cast, as one or two launches): together %.4f ms for %d compulsory bytes N*(2+1) "
                         "(%.1f GB/s) and N*(2*2+1) moved (%.1f GB/s); the global-max dependency forces the second read "
                         "of an input this much larger than L2" % (
                             tw_ms, algorithmic_bytes("dynamic_scaled_quant", rows_local, COLS),
@@ -509,7 +543,9 @@ def main():
     # profiles/fused_and_mx_dram_traffic_512MiB.md, scaled to this launch: what the chip keeps out of
     # DRAM (registers, shared memory, L2) is a constant, not a fraction.
     n_local = rows_local * COLS
-    if dominant["kernel"] == "mx_fp8_quantize":
+    if dominant["kernel"].startswith("dynamic_scaled_quant_p2p"):
+        roofline["traffic"] = int(max(3 * n_local, 5 * n_local - 138e6))
+    elif dominant["kernel"] == "mx_fp8_quantize":
         roofline["traffic"] = int(3.03125 * n_local - min(54e6, 0.25 * n_local))
     elif dominant["kernel"] == "cast_with_amax":
         roofline["traffic"] = int(3 * n_local - min(47e6, 0.25 * n_local))
@@ -571,7 +607,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"cfg5: bf16 [{total_rows},{COLS}] row-sharded over {world} GPU(s); tensor-wise e4m3 "
                                    "quant (amax -> max all-reduce -> cast) + MX block-32 cast",
-                       "rows_per_gpu": rows_local, "l2": "inputs larger than L2 (no flush needed)",
+                       "rows_per_gpu": rows_local, "exchange": exchange, "l2": "inputs larger than L2 (no flush needed)",
                        "timing": "CUDA events on the launch stream, max over ranks"},
             "bytes_per_step": tw_bytes + mx_bytes,
             "frac_of_measured_peak": round(value / (peak * world), 4),
@@ -580,6 +616,8 @@ def main():
             "gpu_launches": my_launches_per_step * args.steps,
             "device_status": status, "output_checksums": check.tolist(),
         }
+        if exchange_note:
+            out["config"]["exchange_note"] = exchange_note
         if e2e is not None:
             out["e2e"] = e2e
         if ops is not None:

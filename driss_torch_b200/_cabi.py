@@ -30,6 +30,9 @@ SIGNATURES = {
     "dtq_amax": ([_vp, _vp, _i64, _i32, _vp, _sz, _vp], _i32),
     "dtq_amax_static_scratch": ([_vp, _vp, _i64, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp, _sz, _vp], _i32),
+    "dtq_p2p_exchange_bytes": ([], _sz),
+    "dtq_dynamic_scaled_quant_p2p": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp, _sz, _vp, _i32, _i32, C.c_uint32,
+                                      C.c_uint32, _vp], _i32),
     "dtq_cast_with_amax": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant_rowwise": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
@@ -129,6 +132,22 @@ def dynamic_scaled_quant(x, out_dtype, out=None, amax_out=None, scale_out=None, 
         load().dtq_dynamic_scaled_quant(x.data_ptr(), out.data_ptr(), _ptr(amax_out), _ptr(scale_out), x.numel(),
                                         IN_CODE[x.dtype], OUT_CODE[out_dtype], ws.data_ptr(), ws.numel(), _stream()),
         "dtq_dynamic_scaled_quant",
+    )
+    return out
+
+
+def dynamic_scaled_quant_p2p(x, out_dtype, peer_ptrs, rank, epoch, out=None, amax_out=None, scale_out=None, ws=None,
+                             spin_limit=0):
+    """One launch per GPU of a row-sharded tensor; ``peer_ptrs[r]`` addresses rank r's exchange buffer."""
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
+    ws = workspace(x.device) if ws is None else ws
+    world = len(peer_ptrs)
+    ptrs = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
+    check(
+        load().dtq_dynamic_scaled_quant_p2p(x.data_ptr(), out.data_ptr(), _ptr(amax_out), _ptr(scale_out), x.numel(),
+                                            IN_CODE[x.dtype], OUT_CODE[out_dtype], ws.data_ptr(), ws.numel(), ptrs,
+                                            rank, world, epoch, spin_limit, _stream()),
+        "dtq_dynamic_scaled_quant_p2p",
     )
     return out
 

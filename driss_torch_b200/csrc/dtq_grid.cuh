@@ -89,4 +89,111 @@ __device__ __forceinline__ bool grid_max_barrier(Workspace *ws, unsigned int gen
   return ok;
 }
 
+// ---- the same barrier with an exchange across GPUs in its serial section -------------------------
+// Every rank (one process per GPU, same launch on each) owns a small exchange buffer that all
+// peers can address over NVLink: kPeerParities x kMaxPeers 64-bit slots.  The last block to arrive
+// at the local barrier stores {epoch, local maximum} into its slot of EVERY rank's buffer
+// (st.release.sys, plain peer stores) and then reads its own buffer until all `world` slots carry
+// this launch's epoch (ld.acquire.sys, bounded spin).  The slot parity alternates with the epoch,
+// so a fast peer's next launch can never overwrite a value a slow rank has not read yet (a rank
+// cannot get two launches ahead: it needs this rank's next value first).  Nothing is ever reset.
+constexpr int kMaxPeers = 16;
+constexpr int kPeerParities = 2;
+
+struct PeerExchange {
+  unsigned long long *buffer[kMaxPeers];  // entry r: rank r's exchange buffer as mapped on this device
+  int rank, world;
+  unsigned int epoch;       // same on every rank for the same launch, increasing by one per launch
+  unsigned int spin_limit;  // polls before a wait gives up
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// As grid_max_barrier, but the value every block leaves with is the maximum over all ranks.
+// Waiting blocks watch the local count reach gridDim.x + 1: the last arriver adds the extra one
+// after the exchange, when ws->amax holds the global value.
+__device__ __forceinline__ bool grid_max_barrier_exchange(Workspace *ws, unsigned int gen0, float block_value,
+                                                          const PeerExchange &px, int *flag, float *shared_result,
+                                                          float *result) {
+  if (threadIdx.x < 32) {  // warp 0; lane 0 runs the local protocol, lanes < world the exchange
+    const unsigned int slot = gen0 & 1u;
+    const int lane = threadIdx.x;
+    unsigned int ticket = 0;
+    if (lane == 0) {
+      atomicMax(&ws->bar_max[slot], __float_as_uint(block_value));
+      __threadfence();
+      ticket = atomicAdd(&ws->bar_count[slot], 1u);
+    }
+    ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+    bool ok = true;
+    if (ticket == gridDim.x - 1) {
+      unsigned int local_bits = 0;
+      if (lane == 0) {
+        __threadfence();
+        local_bits = ld_acquire(&ws->bar_max[slot]);
+      }
+      local_bits = __shfl_sync(0xFFFFFFFFu, local_bits, 0);
+      const int parity = px.epoch & 1u;
+      unsigned int global_bits = 0;
+      if (lane < px.world) {
+        st_release_sys(px.buffer[lane] + parity * kMaxPeers + px.rank,
+                       (static_cast<unsigned long long>(px.epoch) << 32) | local_bits);
+        const unsigned long long *mine = px.buffer[px.rank] + parity * kMaxPeers + lane;
+        unsigned int spins = 0;
+        unsigned long long v = ld_acquire_sys(mine);
+        while (static_cast<unsigned int>(v >> 32) != px.epoch) {
+          if (++spins > px.spin_limit) {
+            ok = false;
+            break;
+          }
+          __nanosleep(40);
+          v = ld_acquire_sys(mine);
+        }
+        global_bits = static_cast<unsigned int>(v);
+      }
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      global_bits = __reduce_max_sync(0xFFFFFFFFu, global_bits);  // non-negative floats order like their bits
+      if (lane == 0) {
+        if (!ok) atomicExch(&ws->status, DTQ_ERR_TIMEOUT);
+        ws->amax = ok ? __uint_as_float(global_bits) : 0.0f;
+        ws->bar_count[slot ^ 1u] = 0;
+        ws->bar_max[slot ^ 1u] = 0;
+        atomicAdd(&ws->generation, 1u);
+        __threadfence();
+        // release the local waiters; on failure with a count they recognise as "gave up"
+        atomicAdd(&ws->bar_count[slot], ok ? 1u : 2u);
+      }
+    } else if (lane == 0) {
+      unsigned int spins = 0;
+      unsigned int c = ld_acquire(&ws->bar_count[slot]);
+      while (c <= gridDim.x) {
+        if (++spins > kSpinLimit + px.spin_limit) {
+          atomicExch(&ws->status, DTQ_ERR_TIMEOUT);
+          break;
+        }
+        __nanosleep(20);
+        c = ld_acquire(&ws->bar_count[slot]);
+      }
+      ok = c == gridDim.x + 1;
+    }
+    if (lane == 0) {
+      __threadfence();
+      *shared_result = ld_relaxed_f32(&ws->amax);
+      *flag = ok;
+    }
+  }
+  __syncthreads();
+  *result = *shared_result;
+  const bool ok = *flag != 0;
+  __syncthreads();
+  return ok;
+}
+
 }  // namespace dtq

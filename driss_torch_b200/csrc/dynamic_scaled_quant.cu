@@ -161,10 +161,12 @@ __device__ __forceinline__ void store_tile(const uint4 (&v)[UNROLL], const DsqSc
   }
 }
 
-template <int IN, int OUT, int UNROLL>
+// P2P: the tensor is row-sharded over several GPUs running this same launch; the barrier between
+// the phases also exchanges the per-GPU maxima through peer memory (see grid_max_barrier_exchange).
+template <int IN, int OUT, int UNROLL, bool P2P>
 __global__ void __launch_bounds__(kFusedThreads, DTQ_FUSED_BLOCKS_PER_SM)
 dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float *__restrict__ amax_out,
-                 float *__restrict__ scale_out, int64_t numel, Workspace *ws, int smem_tiles) {
+                 float *__restrict__ scale_out, int64_t numel, Workspace *ws, int smem_tiles, PeerExchange px) {
   using C = DsqChunk<IN, OUT, true>;
   extern __shared__ uint4 kept_smem[];  // [smem_tiles][UNROLL][kFusedThreads]
   __shared__ float smem32[32];
@@ -221,7 +223,11 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   const float block_value = block_max_nonneg(fmaxf(a, b), smem32, 0.0f);
   __shared__ float amax_shared;
   float amax;
-  if (!grid_max_barrier(ws, gen0, block_value, &flag, &amax_shared, &amax)) return;  // status word says why
+  if constexpr (P2P) {
+    if (!grid_max_barrier_exchange(ws, gen0, block_value, px, &flag, &amax_shared, &amax)) return;
+  } else {
+    if (!grid_max_barrier(ws, gen0, block_value, &flag, &amax_shared, &amax)) return;  // status word says why
+  }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     if (amax_out) *amax_out = amax;
     if (scale_out) *scale_out = static_cast<float>(dsq_scale<OUT>(amax));
@@ -375,6 +381,34 @@ int fused_plan(Kernel kernel, const DeviceInfo &dev, FusedPlan *cache, std::atom
   return DTQ_OK;
 }
 
+// The single persistent launch (optionally with the cross-GPU exchange in its barrier).
+template <int IN, int OUT, bool P2P>
+int launch_fused_kernel(const void *in, void *out, float *amax_out, float *scale_out, int64_t numel, Workspace *ws,
+                        const DeviceInfo &dev, const PeerExchange &px, cudaStream_t st) {
+  using C = DsqChunk<IN, OUT>;
+  static FusedPlan cache[64];
+  static std::atomic<int> ready[64];
+  auto kernel = dsq_fused_kernel<IN, OUT, DTQ_DSQ_UNROLL, P2P>;
+  FusedPlan plan;
+  if (int e = fused_plan(kernel, dev, cache, ready, &plan)) return e;
+  const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kFusedThreads) * DTQ_DSQ_UNROLL);
+  const int grid = balanced_grid(tiles, plan.max_grid);
+  const uint4 *in4 = static_cast<const uint4 *>(in);
+  uint8_t *o = static_cast<uint8_t *>(out);
+  int smem_tiles = plan.smem_tiles;
+  PeerExchange exchange = px;
+  const size_t dyn = size_t(smem_tiles) * kFusedThreads * DTQ_DSQ_UNROLL * 16;
+#if DTQ_DSQ_COOP
+  void *args[] = {&in4, &o, &amax_out, &scale_out, &numel, &ws, &smem_tiles, &exchange};
+  DTQ_CUDA_TRY(
+      cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kernel), dim3(grid), dim3(kFusedThreads), args, dyn, st));
+  return DTQ_OK;
+#else
+  kernel<<<grid, kFusedThreads, dyn, st>>>(in4, o, amax_out, scale_out, numel, ws, smem_tiles, exchange);
+  return cuda_status(cudaGetLastError());
+#endif
+}
+
 template <int IN, int OUT>
 int launch_fused(const void *in, void *out, float *amax_out, float *scale_out, int64_t numel, Workspace *ws,
                  const DeviceInfo &dev, cudaStream_t st) {
@@ -389,27 +423,8 @@ int launch_fused(const void *in, void *out, float *amax_out, float *scale_out, i
                                                                                    &ws->amax, scale_out, amax_out, numel);
     return cuda_status(cudaGetLastError());
   }
-  if (vector_ok && dev.cooperative) {
-    static FusedPlan cache[64];
-    static std::atomic<int> ready[64];
-    auto kernel = dsq_fused_kernel<IN, OUT, DTQ_DSQ_UNROLL>;
-    FusedPlan plan;
-    if (int e = fused_plan(kernel, dev, cache, ready, &plan)) return e;
-    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kFusedThreads) * DTQ_DSQ_UNROLL);
-    const int grid = balanced_grid(tiles, plan.max_grid);
-    const uint4 *in4 = static_cast<const uint4 *>(in);
-    int smem_tiles = plan.smem_tiles;
-    const size_t dyn = size_t(smem_tiles) * kFusedThreads * DTQ_DSQ_UNROLL * 16;
-#if DTQ_DSQ_COOP
-    void *args[] = {&in4, &o, &amax_out, &scale_out, &numel, &ws, &smem_tiles};
-    DTQ_CUDA_TRY(
-        cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kernel), dim3(grid), dim3(kFusedThreads), args, dyn, st));
-    return DTQ_OK;
-#else
-    kernel<<<grid, kFusedThreads, dyn, st>>>(in4, o, amax_out, scale_out, numel, ws, smem_tiles);
-    return cuda_status(cudaGetLastError());
-#endif
-  }
+  if (vector_ok && dev.cooperative)
+    return launch_fused_kernel<IN, OUT, false>(in, out, amax_out, scale_out, numel, ws, dev, PeerExchange{}, st);
   const int64_t blocks = ceil_div64(numel, kThreads);
   const int64_t max_grid = int64_t(dev.sm_count) * 8;
   const int grid = static_cast<int>(blocks < 1 ? 1 : (blocks < max_grid ? blocks : max_grid));
@@ -464,6 +479,43 @@ extern "C" int dtq_dynamic_scaled_quant(const void *in, void *out, float *amax_o
                : launch_fused<DTQ_BF16, DTQ_E5M2>(in, out, amax_out, scale_out, numel, ws, dev, st);
   return out_dtype == DTQ_E4M3 ? launch_fused<DTQ_F32, DTQ_E4M3>(in, out, amax_out, scale_out, numel, ws, dev, st)
                                : launch_fused<DTQ_F32, DTQ_E5M2>(in, out, amax_out, scale_out, numel, ws, dev, st);
+}
+
+extern "C" size_t dtq_p2p_exchange_bytes(void) { return sizeof(unsigned long long) * dtq::kPeerParities * dtq::kMaxPeers; }
+
+extern "C" int dtq_dynamic_scaled_quant_p2p(const void *in, void *out, float *amax_out, float *scale_out, int64_t numel,
+                                            int in_dtype, int out_dtype, void *workspace, size_t workspace_bytes,
+                                            void *const *peer_exchange, int rank, int world, uint32_t epoch,
+                                            uint32_t spin_limit, void *stream) {
+  using namespace dtq;
+  if (numel < 0 || (numel > 0 && (!in || !out)) || !peer_exchange) return DTQ_ERR_INVALID_ARGUMENT;
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return DTQ_ERR_INVALID_ARGUMENT;
+  if (int e = check_dtypes(in_dtype, out_dtype)) return e;
+  if (!workspace || workspace_bytes < sizeof(Workspace) || !aligned_to(workspace, 256)) return DTQ_ERR_WORKSPACE;
+  // the exchange lives in the vector kernel: every rank must take it, so alignment is a requirement here
+  const int out_align = in_dtype == DTQ_BF16 ? 8 : 4;
+  if (!aligned_to(in, 16) || !aligned_to(out, out_align)) return DTQ_ERR_INVALID_ARGUMENT;
+  DeviceInfo dev;
+  if (int e = current_device_info(&dev)) return e;
+  if (!dev.cooperative) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorNotSupported);
+  PeerExchange px{};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_exchange[r] || !aligned_to(peer_exchange[r], 8)) return DTQ_ERR_INVALID_ARGUMENT;
+    px.buffer[r] = static_cast<unsigned long long *>(peer_exchange[r]);
+  }
+  px.rank = rank;
+  px.world = world;
+  px.epoch = epoch;
+  px.spin_limit = spin_limit ? spin_limit : kSpinLimit;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Workspace *ws = static_cast<Workspace *>(workspace);
+  if (in_dtype == DTQ_BF16)
+    return out_dtype == DTQ_E4M3
+               ? launch_fused_kernel<DTQ_BF16, DTQ_E4M3, true>(in, out, amax_out, scale_out, numel, ws, dev, px, st)
+               : launch_fused_kernel<DTQ_BF16, DTQ_E5M2, true>(in, out, amax_out, scale_out, numel, ws, dev, px, st);
+  return out_dtype == DTQ_E4M3
+             ? launch_fused_kernel<DTQ_F32, DTQ_E4M3, true>(in, out, amax_out, scale_out, numel, ws, dev, px, st)
+             : launch_fused_kernel<DTQ_F32, DTQ_E5M2, true>(in, out, amax_out, scale_out, numel, ws, dev, px, st);
 }
 
 extern "C" int dtq_cast_with_amax(const void *in, void *out, const float *amax, float *scale_out, int64_t numel,

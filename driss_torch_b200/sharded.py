@@ -49,9 +49,34 @@ class ShardedQuantizer:
     that the host logic can be exercised on CPU ranks with another implementation.
     """
 
-    def __init__(self, group: Optional[dist.ProcessGroup] = None, kernels=None):
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, kernels=None, fused_exchange: bool = False,
+                 device=None):
+        """``fused_exchange=True`` (CUDA ranks of one node only): ``tensorwise`` becomes ONE kernel launch
+        per GPU that exchanges the per-GPU maxima itself through NVLink peer memory instead of calling a
+        collective between an amax launch and a cast launch.  It needs a small symmetric buffer, set up
+        here once (a collective call: construct the quantizer on every rank)."""
         self.group = group
         self.kernels = _CudaKernels() if kernels is None else kernels
+        self._exchange = None
+        if fused_exchange:
+            self._setup_exchange(device)
+
+    def _setup_exchange(self, device) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _cabi
+
+        if not dist.is_initialized():
+            raise RuntimeError("fused_exchange needs an initialised process group (one process per GPU)")
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        nwords = _cabi.load().dtq_p2p_exchange_bytes() // 8
+        buf = symm_mem.empty(nwords, dtype=torch.int64, device=device)
+        buf.zero_()
+        group = self.group if self.group is not None else dist.group.WORLD
+        handle = symm_mem.rendezvous(buf, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)  # every rank's buffer is zero before anybody's first launch
+        self._exchange = dict(buffer=buf, handle=handle, ptrs=[int(p) for p in handle.buffer_ptrs], epoch=0)
 
     @property
     def world_size(self) -> int:
@@ -76,10 +101,25 @@ class ShardedQuantizer:
         Returns ``(payload_shard, amax[1], scale[1])``; amax and scale are global.  A single rank
         needs no exchange and takes the fused single-launch op.
         """
+        if self._exchange is not None:
+            return self._tensorwise_fused_exchange(shard, dtype)
         if self.world_size == 1:
             return self.kernels.dynamic_scaled_quant_with_scale(shard, dtype)
         amax = self.global_amax(shard)
         payload, scale = self.kernels.cast_with_amax(shard, amax, dtype)
+        return payload, amax, scale
+
+    def _tensorwise_fused_exchange(self, shard: torch.Tensor, dtype: torch.dtype):
+        from . import _cabi
+
+        ex = self._exchange
+        ex["epoch"] += 1  # the same sequence on every rank: all ranks make the same calls
+        if not shard.is_contiguous():
+            raise ValueError("the shard must be contiguous")
+        amax = torch.empty(1, dtype=torch.float32, device=shard.device)
+        scale = torch.empty(1, dtype=torch.float32, device=shard.device)
+        payload = _cabi.dynamic_scaled_quant_p2p(shard, dtype, ex["ptrs"], self.rank, ex["epoch"], amax_out=amax,
+                                                 scale_out=scale)
         return payload, amax, scale
 
     def mx(self, shard: torch.Tensor):

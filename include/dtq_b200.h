@@ -113,6 +113,29 @@ int dtq_dynamic_scaled_quant(const void *in, void *out, float *amax_out, float *
                              size_t workspace_bytes, void *stream);
 
 /*
+ * dtq_dynamic_scaled_quant for a tensor that is row-sharded over the GPUs of one node, one
+ * process per GPU, every rank making this same call on its shard: ONE launch per GPU whose
+ * grid barrier also exchanges the per-GPU maxima through peer-addressable memory (plain
+ * st.release.sys / ld.acquire.sys over NVLink; no collective library call, no second launch),
+ * so every rank quantises with the global amax.  Output is bit-identical to the single-GPU
+ * result on the concatenated tensor.
+ *   peer_exchange[r] = rank r's exchange buffer (dtq_p2p_exchange_bytes() bytes, zero-filled
+ *                      once, 8-byte aligned) as addressable from THIS device, r < world <= 16;
+ *   epoch            = 1, 2, 3, ... : the same value on every rank for the same call;
+ *   spin_limit       = polls before the wait for the peers gives up (0 = default, about 1 s);
+ *                      a rank that never arrives makes the others return with
+ *                      DTQ_ERR_TIMEOUT in the workspace status word instead of hanging
+ *                      (re-initialise the workspace afterwards).
+ * `in` must be 16-byte and `out` 8-byte (bf16) / 4-byte (fp32) aligned.  No reference counterpart
+ * (the reference has no multi-GPU path); arithmetic as dtq_dynamic_scaled_quant.
+ */
+size_t dtq_p2p_exchange_bytes(void);
+int dtq_dynamic_scaled_quant_p2p(const void *in, void *out, float *amax_out, float *scale_out,
+                                 int64_t numel, int in_dtype, int out_dtype, void *workspace,
+                                 size_t workspace_bytes, void *const *peer_exchange, int rank, int world,
+                                 uint32_t epoch, uint32_t spin_limit, void *stream);
+
+/*
  * Cast phase alone, for an amax that already exists on the device (a sharded
  * tensor after its max all-reduce): same arithmetic as the second half of
  * dtq_dynamic_scaled_quant (src/dynamic_scaled_quant.cu:111-117).

@@ -61,8 +61,19 @@ def _worker(rank, world, port, outdir):
         payload, amax, scale = q.tensorwise(shard, E4M3)
         mx_p, mx_s = q.mx(shard)
         torch.cuda.synchronize()
+        # the same through ONE launch per GPU that exchanges the maxima itself over peer memory;
+        # several calls in a row (the exchange slots alternate with the call count), the last one on
+        # different data so that a stale value from an earlier call would show
+        qf = dt.ShardedQuantizer(fused_exchange=True)
+        for _ in range(3):
+            f_payload, f_amax, f_scale = qf.tensorwise(shard, E4M3)
+        shard2 = (shard.float() * 0.5).to(torch.bfloat16)
+        f2_payload, f2_amax, _ = qf.tensorwise(shard2, torch.float8_e5m2)
+        torch.cuda.synchronize()
         dt.check_device_status()
-        torch.save(dict(payload=as_bytes(payload), amax=amax.cpu(), scale=scale.cpu(), mx_p=as_bytes(mx_p), mx_s=as_bytes(mx_s)),
+        torch.save(dict(payload=as_bytes(payload), amax=amax.cpu(), scale=scale.cpu(), mx_p=as_bytes(mx_p), mx_s=as_bytes(mx_s),
+                        f_payload=as_bytes(f_payload), f_amax=f_amax.cpu(), f_scale=f_scale.cpu(),
+                        f2_payload=as_bytes(f2_payload), f2_amax=f2_amax.cpu()),
                    os.path.join(outdir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -82,3 +93,45 @@ def test_ranks_over_nccl_equal_the_single_process_result():
     for p in parts:
         assert p["amax"].view(torch.int32).item() == want_amax.view(torch.int32).item()
         assert p["scale"].view(torch.int32).item() == want_scale.view(torch.int32).item()
+        assert p["f_amax"].view(torch.int32).item() == want_amax.view(torch.int32).item()
+        assert p["f_scale"].view(torch.int32).item() == want_scale.view(torch.int32).item()
+    assert torch.equal(torch.cat([p["f_payload"] for p in parts]), as_bytes(want)), "fused exchange payload"
+    half = (full.float() * 0.5).to(torch.bfloat16)
+    want2, want2_amax, _ = qo.dynamic_scaled_quant(half, torch.float8_e5m2)
+    assert torch.equal(torch.cat([p["f2_payload"] for p in parts]), as_bytes(want2)), "fused exchange, second tensor"
+    assert all(p["f2_amax"].item() == want2_amax.item() for p in parts)
+
+
+def test_fused_exchange_single_rank_and_missing_peer_timeout():
+    # world 1: the exchange degenerates to a store and a load on the rank's own buffer.
+    # world 2 with a peer that never writes: the bounded wait gives up, the launch returns, the
+    # workspace reports DTQ_ERR_TIMEOUT (5) and the context stays usable.
+    from driss_torch_b200 import _cabi
+
+    lib = _cabi.load()
+    x = workloads.make_cfg2(rows=512, cols=1024)
+    want, want_amax, want_scale = qo.dynamic_scaled_quant(x, E4M3)
+    xd = x.cuda()
+    mine = torch.zeros(lib.dtq_p2p_exchange_bytes() // 8, dtype=torch.int64, device="cuda")
+    amax, scale = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    for epoch in (1, 2, 3):
+        got = _cabi.dynamic_scaled_quant_p2p(xd, E4M3, [mine.data_ptr()], 0, epoch, amax_out=amax, scale_out=scale)
+        assert torch.equal(as_bytes(got), as_bytes(want))
+        assert amax.item() == want_amax.item() and scale.item() == want_scale.item()
+
+    silent_peer = torch.zeros_like(mine)
+    ws = torch.empty(lib.dtq_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    _cabi.check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), stream), "init")
+    out = torch.full(x.shape, 0x5A, dtype=torch.uint8, device="cuda")
+    _cabi.dynamic_scaled_quant_p2p(xd, E4M3, [mine.data_ptr(), silent_peer.data_ptr()], 0, 4, out=out.view(E4M3), ws=ws,
+                                   spin_limit=2000)
+    torch.cuda.synchronize()  # returns: nothing hangs
+    assert _cabi.workspace_status(ws) == 5
+    assert (out == 0x5A).all()  # no payload is written without a global maximum
+    # the rank's own value did reach the peer's buffer (what a live peer would have read)
+    assert (silent_peer.cpu() != 0).sum().item() == 1
+    # a fresh workspace and the ordinary op still work
+    _cabi.check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), stream), "init")
+    assert torch.equal(as_bytes(_cabi.dynamic_scaled_quant(xd, E4M3, ws=ws)), as_bytes(want))
+    assert _cabi.workspace_status(ws) == 0
