@@ -540,7 +540,7 @@ def main():
                             algorithmic_bytes("dynamic_scaled_quant", rows_local, COLS) / (tw_ms * 1e-3) / 1e9,
                             rows_local * COLS * 5 / (tw_ms * 1e-3) / 1e9))
     # DRAM read+write per launch from the ncu capture summarised in
-    # profiles/fused_and_mx_dram_traffic_512MiB.md, scaled to this launch: what the chip keeps out of
+    # profiles/step_kernels_dram_traffic_512MiB.md, scaled to this launch: what the chip keeps out of
     # DRAM (registers, shared memory, L2) is a constant, not a fraction.
     n_local = rows_local * COLS
     if dominant["kernel"].startswith("dynamic_scaled_quant_p2p"):
@@ -548,10 +548,10 @@ def main():
     elif dominant["kernel"] == "mx_fp8_quantize":
         roofline["traffic"] = int(3.03125 * n_local - min(54e6, 0.25 * n_local))
     elif dominant["kernel"] == "cast_with_amax":
-        roofline["traffic"] = int(3 * n_local - min(47e6, 0.25 * n_local))
+        roofline["traffic"] = int(3 * n_local - min(34e6, 0.25 * n_local))
     elif dominant["kernel"] == "amax":
         roofline["traffic"] = int(2 * n_local)
-    roofline["traffic_source"] = "ncu dram__bytes_read+write on a 512 MiB case, scaled (profiles/fused_and_mx_dram_traffic_512MiB.md)"
+    roofline["traffic_source"] = "ncu dram__bytes_read+write on a 512 MiB case, scaled (profiles/step_kernels_dram_traffic_512MiB.md)"
 
     # ---- end to end: host buffers in, host buffers out ------------------------------------------------
     e2e = None

@@ -11,7 +11,7 @@
 // Arithmetic (identical to the reference): e_i = ceil(log2 |x_i|) from the exponent field
 // (+1 if the mantissa is non-zero; zero -> -128, subnormal -> -126); E = max e_i;
 // biased = clamp(E - 8 + 127, 0, 255); scale = 2^(biased-127) (0.0 for biased == 0, +inf for
-// 255); payload = e4m3_satfinite(x * rcp(scale)); scale byte = ue8m0(scale) rounded up,
+// 255); payload = e4m3_satfinite(x * (1/scale)); scale byte = ue8m0(scale) rounded up,
 // saturating (255 -> 0xFE).  e is monotone in |x|, so the block max is taken on the raw
 // 15-bit magnitudes with packed 16-bit integer max.
 #include "dtq_device.cuh"
@@ -42,8 +42,20 @@ __device__ __forceinline__ int block_biased_exponent(uint32_t mag) {
   return min(255, max(0, e - 8 + 127));
 }
 
+// 1 / scale for scale = 2^(biased-127), as the reference's rcp.rn gives it: exact for every power
+// of two (2^-127 is the subnormal 0x00400000), +inf for scale 0 (biased 0), 0 for scale +inf
+// (biased 255).  Built from the exponent instead of running the reciprocal sequence.
+__device__ __forceinline__ float inverse_scale(int biased) {
+  const int e = 254 - biased;  // exponent field of the reciprocal
+  uint32_t bits = static_cast<uint32_t>(e) << 23;
+  if (e <= 0) bits = e == 0 ? 0x00400000u : 0u;
+  if (biased == 0) bits = 0x7F800000u;
+  return __uint_as_float(bits);
+}
+
 __device__ __forceinline__ uint32_t mx_pair(uint32_t w, float inv) {
-  return cvt_fp8x2<DTQ_E4M3>(__fmul_rn(bf16_lo(w), inv), __fmul_rn(bf16_hi(w), inv));
+  const float2 p = __fmul2_rn(make_float2(bf16_lo(w), bf16_hi(w)), make_float2(inv, inv));
+  return cvt_fp8x2<DTQ_E4M3>(p.x, p.y);
 }
 
 __device__ __forceinline__ uint2 mx_payload(uint4 v, float inv) {
@@ -55,7 +67,7 @@ __device__ __forceinline__ uint2 mx_payload(uint4 v, float inv) {
 
 // nchunks = numel / 8 is a multiple of 4.  A warp owns kUnroll consecutive 512-byte rows of
 // chunks; a CTA tile is kThreads * kUnroll chunks.
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2048 / kThreads)
 mx_stream_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
                  int64_t nchunks) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -76,7 +88,7 @@ mx_stream_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, ui
       mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
       const int biased = block_biased_exponent(mag);
       const float scale = __int_as_float(biased << 23);
-      const float inv = __frcp_rn(scale);
+      const float inv = inverse_scale(biased);
       const int64_t c = warp_first + u * 32 + lane;
       if (c < nchunks) stg_stream(payload + c * 8, mx_payload(v[u], inv));
       if ((lane & 3) == u) my_scale_byte = cvt_ue8m0(scale);
