@@ -324,6 +324,8 @@ def run_reference_arm(args, rank: int):
         return
     from oracle import quant_oracle as qo
 
+    # torchrun pins OMP_NUM_THREADS=1 for its children; this arm is meant to use every host core
+    qo.set_num_threads(os.cpu_count() or 1)
     sample_rows = 8192
     x = cpu_sample(sample_rows)
     for _ in range(args.warmup):
@@ -338,7 +340,10 @@ def run_reference_arm(args, rank: int):
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt_ * 1e3, 3), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16->fp8 (f64 scale arithmetic)", "data": "synthetic",
-        "config": {"workload": "cfg5 sample: tensor-wise e4m3 quant + MX block-32 cast", "sample": sample},
+        "config": {"workload": f"cfg5: bf16 [{TOTAL_ROWS},{COLS}] row-sharded over {args.gpus} GPU(s); tensor-wise e4m3 "
+                               "quant (amax -> max all-reduce -> cast) + MX block-32 cast",
+                   "sample": sample, "what_runs": "CPU restatement of the reference kernels (oracle/quant_oracle.c, "
+                   "OpenMP); the reference itself is CUDA-only and has no CPU implementation"},
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": qo.num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
