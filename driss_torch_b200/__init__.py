@@ -7,7 +7,7 @@ Drop-in for the quantization part of ``driss_torch`` (driss_torch/__init__.py:20
 Importing loads ``lib/libdriss_torch.so`` (the ``TORCH_LIBRARY(DrissTorch)``
 registration, which pulls in the CUDA kernels in ``lib/libdtq_b200.so``) and the
 fake-tensor implementations.  There is no CPU implementation and no fallback: if the
-libraries have not been built (``python -m driss_torch_b200.build``) the import fails.
+libraries have not been built (``python driss_torch_b200/build.py``) the import fails.
 """
 from __future__ import annotations
 
@@ -22,7 +22,7 @@ kernels_lib_path = _LIB_DIR / "libdtq_b200.so"
 if not lib_path.exists() or not kernels_lib_path.exists():
     raise ImportError(
         f"{lib_path.name} / {kernels_lib_path.name} not found in {_LIB_DIR}: build them with "
-        "`python -m driss_torch_b200.build` (needs nvcc with sm_100a support); there is no fallback path"
+        "`python driss_torch_b200/build.py` (needs nvcc with sm_100a support); there is no fallback path"
     )
 
 torch.ops.load_library(str(lib_path))
@@ -97,6 +97,12 @@ def cast_with_amax(inpt: Tensor, amax_value: Tensor, dtype: torch.dtype) -> tupl
     return ops.cast_with_amax(inpt, amax_value, dtype)
 
 
+def mx_fp8_quantize_blocked(input: Tensor) -> tuple[Tensor, Tensor]:
+    """``mx_fp8_quantize`` with the E8M0 scales already in the blocked (128x4-atom) layout that the MX
+    GEMM ``mx_fp8_bf16`` expects, i.e. without the separate ``to_blocked`` pass; zero in the padding."""
+    return ops.mx_fp8_quantize_blocked(input)
+
+
 def check_device_status() -> None:
     """Synchronises and raises if a kernel's bounded device-side wait ever gave up."""
     ops.check_device_status()
@@ -113,6 +119,7 @@ __all__ = [
     "dynamic_scaled_quant_with_scale",
     "dynamic_scaled_quant_rowwise",
     "cast_with_amax",
+    "mx_fp8_quantize_blocked",
     "check_device_status",
     "ShardedQuantizer",
 ]

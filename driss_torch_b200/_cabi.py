@@ -36,6 +36,8 @@ SIGNATURES = {
     "dtq_cast_with_amax": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant_rowwise": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
+    "dtq_mx_blocked_scale_bytes": ([_i64, _i64], _sz),
+    "dtq_mx_fp8_quantize_blocked": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
 }
 
 _lib = None
@@ -46,7 +48,7 @@ def load() -> C.CDLL:
     global _lib
     if _lib is None:
         if not LIB_PATH.exists():
-            raise ImportError(f"{LIB_PATH} not built: run `python -m driss_torch_b200.build`")
+            raise ImportError(f"{LIB_PATH} not built: run `python driss_torch_b200/build.py`")
         lib = C.CDLL(str(LIB_PATH))
         for name, (argtypes, restype) in SIGNATURES.items():
             fn = getattr(lib, name)
@@ -179,4 +181,16 @@ def mx_fp8_quantize(x, payload=None, scales=None):
     scales = torch.empty(rows * (cols // 32), dtype=torch.float8_e8m0fnu, device=x.device) if scales is None else scales
     check(load().dtq_mx_fp8_quantize(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, _stream()),
           "dtq_mx_fp8_quantize")
+    return payload, scales
+
+
+def mx_fp8_quantize_blocked(x, payload=None, scales=None):
+    """MX cast with the scales in the blocked layout of the consumer GEMM (zero-filled padding)."""
+    rows, cols = x.shape
+    payload = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device) if payload is None else payload
+    if scales is None:
+        nbytes = load().dtq_mx_blocked_scale_bytes(rows, cols)
+        scales = torch.zeros(nbytes, dtype=torch.uint8, device=x.device).view(torch.float8_e8m0fnu)
+    check(load().dtq_mx_fp8_quantize_blocked(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, _stream()),
+          "dtq_mx_fp8_quantize_blocked")
     return payload, scales

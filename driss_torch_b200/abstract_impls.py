@@ -47,3 +47,10 @@ def dynamic_scaled_quant_rowwise_meta(x: torch.Tensor, dtype: torch.dtype):
 @register_fake("DrissTorch::cast_with_amax")
 def cast_with_amax_meta(x: torch.Tensor, amax: torch.Tensor, dtype: torch.dtype):
     return torch.empty_like(x, dtype=dtype), torch.empty(1, dtype=torch.float32, device=x.device)
+
+
+@register_fake("DrissTorch::mx_fp8_quantize_blocked")
+def mx_fp8_quantize_blocked_meta(x: torch.Tensor):
+    m, n = x.shape
+    nbytes = ((m + 127) // 128) * ((n // 32 + 3) // 4) * 512
+    return torch.empty_like(x, dtype=torch.float8_e4m3fn), torch.empty(nbytes, dtype=torch.float8_e8m0fnu, device=x.device)

@@ -5,7 +5,7 @@
 * ``lib/libdriss_torch.so`` -- ``register_ops.cpp``: the ``TORCH_LIBRARY(DrissTorch)``
   registration that binds the C ABI into the PyTorch dispatcher, built with g++.
 
-``python -m driss_torch_b200.build`` builds both; objects are rebuilt only when a
+``python driss_torch_b200/build.py`` builds both; objects are rebuilt only when a
 source or header is newer.  The reference builds one ``libdriss_torch.so`` through
 scikit-build/CMake with the same architecture flags (CMakeLists.txt:25-27).
 """

@@ -65,11 +65,27 @@ __device__ __forceinline__ uint2 mx_payload(uint4 v, float inv) {
   return r;
 }
 
+// Where the scale of MX block `blk` (row-major index over [rows, kblocks]) goes.
+// Row-major: scales[blk], the reference's layout (src/mx_cast.cu:199,210-211).
+// Blocked: the layout the reference's MX GEMM consumes (src/mx_fp8_bf16.cu:97-110, CUTLASS
+// Sm1xxBlockScaledConfig::tile_atom_to_shape_SFA; the reference gets there through a separate
+// `to_blocked` pass, test/test_mx.py:28-32): 128-row x 4-k-block atoms of 512 bytes, atoms ordered
+// k-block-major within a 128-row band; inside an atom row r, k-block c sit at
+// (r % 32) * 16 + (r / 32) * 4 + c.
+template <bool BLOCKED>
+__device__ __forceinline__ int64_t scale_offset(int64_t blk, int64_t kblocks, int64_t katoms) {
+  if constexpr (!BLOCKED) return blk;
+  const int64_t r = blk / kblocks, c = blk - r * kblocks;
+  const int64_t atom = (r >> 7) * katoms + (c >> 2);
+  return atom * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3);
+}
+
 // nchunks = numel / 8 is a multiple of 4.  A warp owns kUnroll consecutive 512-byte rows of
 // chunks; a CTA tile is kThreads * kUnroll chunks.
+template <bool BLOCKED>
 __global__ void __launch_bounds__(kThreads, 2048 / kThreads)
 mx_stream_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
-                 int64_t nchunks) {
+                 int64_t nchunks, int64_t kblocks, int64_t katoms) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int64_t kTile = int64_t(kThreads) * kUnroll;
   for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
@@ -95,14 +111,15 @@ mx_stream_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, ui
     }
     // lane = 4*k + j holds the scale of block (u = j, quad k): block index u*8 + k in the warp's span.
     const int64_t blk = warp_first / 4 + (lane & 3) * 8 + (lane >> 2);
-    if (blk * 4 < nchunks) scales[blk] = static_cast<uint8_t>(my_scale_byte);
+    if (blk * 4 < nchunks) scales[scale_offset<BLOCKED>(blk, kblocks, katoms)] = static_cast<uint8_t>(my_scale_byte);
   }
 }
 
 // Any alignment: one thread per MX block.
+template <bool BLOCKED>
 __global__ void __launch_bounds__(kThreads)
 mx_scalar_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
-                 int64_t nblocks) {
+                 int64_t nblocks, int64_t kblocks, int64_t katoms) {
   for (int64_t b = int64_t(blockIdx.x) * kThreads + threadIdx.x; b < nblocks; b += int64_t(gridDim.x) * kThreads) {
     const uint16_t *x = in + b * 32;
     uint32_t mag = 0;
@@ -112,16 +129,17 @@ mx_scalar_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload,
     const float inv = __frcp_rn(scale);
     for (int i = 0; i < 32; ++i)
       payload[b * 32 + i] = cvt_fp8<DTQ_E4M3>(__fmul_rn(__uint_as_float(uint32_t(x[i]) << 16), inv));
-    scales[b] = cvt_ue8m0(scale);
+    scales[scale_offset<BLOCKED>(b, kblocks, katoms)] = cvt_ue8m0(scale);
   }
 }
 
 }  // namespace
 }  // namespace dtq
 
-extern "C" int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, int64_t rows, int64_t cols,
-                                   void *stream) {
-  using namespace dtq;
+namespace dtq {
+namespace {
+template <bool BLOCKED>
+int launch_mx(const void *in_bf16, void *payload, void *scales_e8m0, int64_t rows, int64_t cols, cudaStream_t st) {
   if (rows < 0 || cols < 0) return DTQ_ERR_INVALID_ARGUMENT;
   if (cols % 32 != 0) return DTQ_ERR_SHAPE;
   const int64_t numel = rows * cols;
@@ -129,19 +147,38 @@ extern "C" int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *sca
   if (!in_bf16 || !payload || !scales_e8m0 || !aligned_to(in_bf16, 2)) return DTQ_ERR_INVALID_ARGUMENT;
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t kblocks = cols / 32, katoms = (kblocks + 3) / 4;
   const int64_t max_grid = int64_t(dev.sm_count) * DTQ_MX_BLOCKS_PER_SM;
   if (aligned_to(in_bf16, 16) && aligned_to(payload, 8)) {
     const int64_t nchunks = numel / 8;
     const int64_t tiles = ceil_div64(nchunks, int64_t(kThreads) * kUnroll);
     const int grid = balanced_grid(tiles, max_grid);
-    mx_stream_kernel<<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in_bf16), static_cast<uint8_t *>(payload),
-                                                static_cast<uint8_t *>(scales_e8m0), nchunks);
+    mx_stream_kernel<BLOCKED><<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in_bf16),
+                                                         static_cast<uint8_t *>(payload),
+                                                         static_cast<uint8_t *>(scales_e8m0), nchunks, kblocks, katoms);
   } else {
     const int64_t blocks = ceil_div64(numel / 32, kThreads);
     const int grid = static_cast<int>(blocks < max_grid ? blocks : max_grid);
-    mx_scalar_kernel<<<grid, kThreads, 0, st>>>(static_cast<const uint16_t *>(in_bf16), static_cast<uint8_t *>(payload),
-                                                static_cast<uint8_t *>(scales_e8m0), numel / 32);
+    mx_scalar_kernel<BLOCKED><<<grid, kThreads, 0, st>>>(static_cast<const uint16_t *>(in_bf16),
+                                                         static_cast<uint8_t *>(payload),
+                                                         static_cast<uint8_t *>(scales_e8m0), numel / 32, kblocks, katoms);
   }
   return cuda_status(cudaGetLastError());
+}
+}  // namespace
+}  // namespace dtq
+
+extern "C" int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, int64_t rows, int64_t cols,
+                                   void *stream) {
+  return dtq::launch_mx<false>(in_bf16, payload, scales_e8m0, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t dtq_mx_blocked_scale_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return static_cast<size_t>((rows + 127) / 128) * static_cast<size_t>((cols / 32 + 3) / 4) * 512;
+}
+
+extern "C" int dtq_mx_fp8_quantize_blocked(const void *in_bf16, void *payload, void *scales_blocked, int64_t rows,
+                                           int64_t cols, void *stream) {
+  return dtq::launch_mx<true>(in_bf16, payload, scales_blocked, rows, cols, static_cast<cudaStream_t>(stream));
 }

@@ -168,6 +168,27 @@ std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize(at::Tensor input, int64_t blo
 
 // ---- additions ---------------------------------------------------------------------------------------
 
+// MX cast whose scales come out in the blocked layout of the MX GEMM (1-D e8m0 tensor of
+// 512 * ceil(M/128) * ceil(N/128) bytes, zero in the padding).
+std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize_blocked(at::Tensor input) {
+  TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D");
+  TORCH_CHECK(input.scalar_type() == at::kBFloat16, "Input tensor must be bfloat16, but got ", input.dtype());
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(n % 32 == 0, "The last dimension must be a multiple of the block size 32, but got ", n);
+  at::Tensor out = at::empty_like(input, input.options().dtype(at::kFloat8_e4m3fn));
+  const int64_t nbytes = static_cast<int64_t>(dtq_mx_blocked_scale_bytes(m, n));
+  const bool padded = m % 128 != 0 || (n / 32) % 4 != 0;
+  at::Tensor scale = padded ? at::zeros({nbytes}, input.options().dtype(at::kByte)).view(at::kFloat8_e8m0fnu)
+                            : at::empty({nbytes}, input.options().dtype(at::kFloat8_e8m0fnu));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_mx_fp8_quantize_blocked(input.data_ptr(), out.data_ptr(), scale.data_ptr(), m, n, stream.stream()),
+               "mx_fp8_quantize_blocked");
+  return {out, scale};
+}
+
 std::tuple<at::Tensor, at::Tensor, at::Tensor> dynamic_scaled_quant_rowwise(const at::Tensor &input,
                                                                              at::ScalarType dtype) {
   check_fp8(dtype);
@@ -228,6 +249,8 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("dynamic_scaled_quant_rowwise", c10::DispatchKey::CUDA, TORCH_FN(dynamic_scaled_quant_rowwise));
   m.def("cast_with_amax(Tensor input, Tensor amax, ScalarType dtype) -> (Tensor, Tensor)");
   m.impl("cast_with_amax", c10::DispatchKey::CUDA, TORCH_FN(cast_with_amax));
+  m.def("mx_fp8_quantize_blocked(Tensor input) -> (Tensor, Tensor)");
+  m.impl("mx_fp8_quantize_blocked", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_blocked));
   m.def("check_device_status() -> ()");
   m.impl("check_device_status", c10::DispatchKey::CompositeExplicitAutograd, TORCH_FN(check_device_status));
 }

@@ -167,6 +167,21 @@ int dtq_dynamic_scaled_quant_rowwise(const void *in, void *out, float *amax_out,
 int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, int64_t rows,
                         int64_t cols, void *stream);
 
+/*
+ * As dtq_mx_fp8_quantize, but the scales are written directly in the blocked layout that the
+ * reference's MX GEMM (mx_fp8_bf16, src/mx_fp8_bf16.cu:97-110,197-205) hands to CUTLASS
+ * (Sm1xxBlockScaledConfig::tile_atom_to_shape_SFA): 128-row x 4-block atoms of 512 bytes,
+ * k-major atom order; row r, block c of an atom at (r % 32) * 16 + (r / 32) * 4 + c.  The
+ * reference reaches that layout with a separate re-layout pass over the row-major scales
+ * (`to_blocked`, test/test_mx.py:28-32); emitting it here saves that pass.
+ * `scales_blocked` holds dtq_mx_blocked_scale_bytes(rows, cols) bytes; bytes that belong to
+ * padding rows / blocks (rows % 128, (cols/32) % 4) are not written: zero the buffer first if
+ * the shape is not a multiple of (128, 128).
+ */
+size_t dtq_mx_blocked_scale_bytes(int64_t rows, int64_t cols);
+int dtq_mx_fp8_quantize_blocked(const void *in_bf16, void *payload, void *scales_blocked, int64_t rows,
+                                int64_t cols, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -191,3 +191,21 @@ def f32_to_bf16_array(vals: np.ndarray, header: bool = False) -> np.ndarray:
     fn = header_lib().hdr_f32_to_bf16_array if header else lib().oracle_f32_to_bf16_array
     fn(vals.ctypes.data, out.ctypes.data, vals.size)
     return out
+
+
+def blocked_scale_offsets(rows: int, kblocks: int) -> np.ndarray:
+    """Offset of scale (r, c) in the blocked layout of the reference's MX GEMM
+    (src/mx_fp8_bf16.cu:97-110; CUTLASS Sm1xxBlockScaledConfig): 128 x 4 atoms of 512 bytes, k-major
+    atom order, (r % 32) * 16 + (r % 128 // 32) * 4 + c % 4 inside an atom.  Shape [rows, kblocks]."""
+    r = np.arange(rows, dtype=np.int64)[:, None]
+    c = np.arange(kblocks, dtype=np.int64)[None, :]
+    katoms = (kblocks + 3) // 4
+    return ((r // 128) * katoms + c // 4) * 512 + (r % 32) * 16 + (r % 128 // 32) * 4 + c % 4
+
+
+def to_blocked(scales_row_major: torch.Tensor, rows: int, kblocks: int) -> torch.Tensor:
+    """Row-major [rows * kblocks] scale bytes -> blocked layout (uint8, zero padding)."""
+    off = blocked_scale_offsets(rows, kblocks)
+    out = np.zeros(((rows + 127) // 128) * ((kblocks + 3) // 4) * 512, dtype=np.uint8)
+    out[off.ravel()] = scales_row_major.view(torch.uint8).numpy().ravel()
+    return torch.from_numpy(out)

@@ -198,3 +198,45 @@ def test_rowwise_op_cfg4_slice_and_zero_rows():
     e_p, e_am, e_sc = eager.dynamic_scaled_quant_rowwise_eager(a, torch.float8_e4m3fn)
     assert_fp8_equal(e_p, want, torch.float8_e4m3fn, "rowwise eager")
     assert _bits(e_am) == _bits(want_amax) and _bits(e_sc) == _bits(want_scale)
+
+
+def test_ops_capture_into_a_cuda_graph_and_replay():
+    # The C ABI neither allocates nor synchronises, so a whole quantisation step can be captured
+    # once and replayed on new data in the same buffers.
+    from driss_torch_b200 import _cabi
+
+    E4M3 = torch.float8_e4m3fn
+    x = workloads.make_cfg2(rows=1024, cols=2048).cuda()
+    x2 = workloads.make_cfg3(rows=1024, cols=2048)
+    out = torch.empty(x.shape, dtype=E4M3, device="cuda")
+    fused = torch.empty_like(out)
+    mx_p = torch.empty_like(out)
+    mx_s = torch.empty(x.numel() // 32, dtype=torch.float8_e8m0fnu, device="cuda")
+    amax, scale = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ws = _cabi.workspace()  # created (and the kernels' one-time set-up done) before the capture
+        for _ in range(2):
+            _cabi.amax(x, out=amax, ws=ws)
+            _cabi.cast_with_amax(x, amax, E4M3, out=out, scale_out=scale)
+            _cabi.dynamic_scaled_quant(x, E4M3, out=fused, ws=ws)
+            _cabi.mx_fp8_quantize(x, payload=mx_p, scales=mx_s)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        _cabi.amax(x, out=amax, ws=ws)
+        _cabi.cast_with_amax(x, amax, E4M3, out=out, scale_out=scale)
+        _cabi.dynamic_scaled_quant(x, E4M3, out=fused, ws=ws)
+        _cabi.mx_fp8_quantize(x, payload=mx_p, scales=mx_s)
+    x.copy_(x2)  # new data, same buffers
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    want, want_amax, want_scale = qo.dynamic_scaled_quant(x2, E4M3)
+    assert_fp8_equal(out, want, E4M3, "graph: amax + cast")
+    assert_fp8_equal(fused, want, E4M3, "graph: fused")
+    assert _bits(amax) == _bits(want_amax) and _bits(scale) == _bits(want_scale)
+    wp, ws_ = qo.mx_fp8_quantize(x2)
+    assert_fp8_equal(mx_p, wp, E4M3, "graph: mx payload")
+    assert torch.equal(mx_s.view(torch.uint8).cpu(), ws_.view(torch.uint8))
+    assert _cabi.workspace_status(ws) == 0

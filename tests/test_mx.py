@@ -143,3 +143,54 @@ def test_errors_and_compile():
     p, s = fn(a)
     p0, s0 = dt.mx_fp8_quantize(a)
     assert torch.equal(as_bytes(p), as_bytes(p0)) and torch.equal(as_bytes(s), as_bytes(s0))
+
+
+# ---- scales in the blocked layout of the MX GEMM ------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(128, 128), (256, 256), (384, 4096), (129, 256), (133, 512), (64, 96),
+                                       (1, 32), (1000, 2080), (8192, 8192)])
+def test_blocked_scales_are_the_row_major_scales_rearranged(rows, cols):
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg3(rows=rows, cols=cols)
+    p, s = dt.mx_fp8_quantize_blocked(a.cuda())
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    assert_fp8_equal(p, want_p, E4M3, "payload")
+    want_blocked = qo.to_blocked(want_s, rows, cols // 32)
+    assert s.dtype == torch.float8_e8m0fnu and s.numel() == want_blocked.numel()
+    assert torch.equal(as_bytes(s), want_blocked)
+
+
+def test_blocked_layout_matches_the_cutlass_layout_function():
+    # the index map the kernel uses, against CUTLASS's own tile_atom_to_shape_SFA evaluated on the
+    # host by oracle/cute_sf_layout.cpp (built on demand from the CUTLASS headers vendored in the image)
+    import subprocess
+    import sysconfig
+    from pathlib import Path
+
+    import numpy as np
+
+    from driss_torch_b200 import _cabi
+
+    root = Path(__file__).resolve().parents[1]
+    cutlass = Path(sysconfig.get_paths()["purelib"]) / "flashinfer" / "data" / "cutlass" / "include"
+    if not (cutlass / "cutlass" / "detail" / "sm100_blockscaled_layout.hpp").exists():
+        pytest.skip("no CUTLASS headers in this image")
+    exe = root / "oracle" / "_build" / "cute_sf_layout"
+    src = root / "oracle" / "cute_sf_layout.cpp"
+    if not exe.exists() or exe.stat().st_mtime < src.stat().st_mtime:
+        exe.parent.mkdir(exist_ok=True)
+        subprocess.check_call(["g++", "-std=c++17", "-O1", f"-I{cutlass}", "-I/usr/local/cuda/include", str(src), "-o", str(exe)])
+    for rows, cols in ((128, 128), (256, 1024), (133, 512), (384, 4096)):
+        lines = subprocess.check_output([str(exe), str(rows), str(cols)], text=True).split("\n")
+        cosize = int(lines[0].split()[1])
+        table = np.array([[int(v) for v in ln.split()] for ln in lines[1:] if ln], dtype=np.int64)
+        mine = qo.blocked_scale_offsets(rows, cols // 32)
+        assert np.array_equal(mine[table[:, 0], table[:, 1]], table[:, 2]), (rows, cols)
+        assert cosize <= _cabi.load().dtq_mx_blocked_scale_bytes(rows, cols)
+        # and the kernel itself: scale (r, c) is found at that offset
+        a = workloads.make_cfg3(rows=rows, cols=cols)
+        _, s = _cabi.mx_fp8_quantize_blocked(a.cuda())
+        _, row_major = qo.mx_fp8_quantize(a)
+        got = as_bytes(s).numpy()[table[:, 2]]
+        assert np.array_equal(got, row_major.view(torch.uint8).numpy()[table[:, 0] * (cols // 32) + table[:, 1]])
