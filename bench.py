@@ -246,7 +246,16 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
     t = timed(lambda i: _cabi.mx_fp8_quantize(xs[i], payload=ps[i], scales=ss[i]), ns, iters)
     rt = timed(lambda i: ref.mx_fp8_quantize(xs[i], 32, 1, False, E4M3), ns, iters) if ref else None
     line("cfg3", "mx_fp8_quantize", x.shape, t, algorithmic_bytes("mx_fp8_quantize", w.rows, w.cols), rt)
-    del xs, ps, ss
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    t = timed(lambda i: _cabi.mx_fp8_quantize_tma(xs[i], payload=ps[i], scales=ss[i], status=status), ns, iters)
+    line("cfg3", "mx_fp8_quantize (TMA-staged variant)", x.shape, t, algorithmic_bytes("mx_fp8_quantize", w.rows, w.cols),
+         None, note=f"same outputs through a cp.async.bulk + mbarrier shared-memory ring; status {int(status.item())}")
+    sb = [torch.empty(_cabi.load().dtq_mx_blocked_scale_bytes(w.rows, w.cols), dtype=torch.uint8, device=dev)
+          .view(torch.float8_e8m0fnu) for _ in range(ns)]
+    t = timed(lambda i: _cabi.mx_fp8_quantize_blocked(xs[i], payload=ps[i], scales=sb[i]), ns, iters)
+    line("cfg3", "mx_fp8_quantize_blocked", x.shape, t, algorithmic_bytes("mx_fp8_quantize", w.rows, w.cols), None,
+         note="scales written in the MX GEMM's blocked layout (the reference needs a separate to_blocked pass)")
+    del xs, ps, ss, sb
 
     # cfg4: row-wise dynamic quant bf16 [32768,4096] (no reference op)
     w = workloads.WORKLOADS["cfg4"]

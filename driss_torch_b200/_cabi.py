@@ -36,6 +36,7 @@ SIGNATURES = {
     "dtq_cast_with_amax": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant_rowwise": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
+    "dtq_mx_fp8_quantize_tma": ([_vp, _vp, _vp, _i64, _i64, _vp, _vp], _i32),
     "dtq_mx_blocked_scale_bytes": ([_i64, _i64], _sz),
     "dtq_mx_fp8_quantize_blocked": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
 }
@@ -194,3 +195,14 @@ def mx_fp8_quantize_blocked(x, payload=None, scales=None):
     check(load().dtq_mx_fp8_quantize_blocked(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, _stream()),
           "dtq_mx_fp8_quantize_blocked")
     return payload, scales
+
+
+def mx_fp8_quantize_tma(x, payload=None, scales=None, status=None):
+    """The shared-memory-staged (TMA bulk copy) variant of the MX cast; same outputs."""
+    rows, cols = x.shape
+    payload = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device) if payload is None else payload
+    scales = torch.empty(rows * (cols // 32), dtype=torch.float8_e8m0fnu, device=x.device) if scales is None else scales
+    status = torch.zeros(1, dtype=torch.int32, device=x.device) if status is None else status
+    check(load().dtq_mx_fp8_quantize_tma(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols,
+                                         status.data_ptr(), _stream()), "dtq_mx_fp8_quantize_tma")
+    return payload, scales, status

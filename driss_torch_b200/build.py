@@ -35,6 +35,7 @@ KERNEL_SOURCES = [
     "dynamic_scaled_quant.cu",
     "rowwise_quant.cu",
     "mx_cast.cu",
+    "mx_cast_tma.cu",
 ]
 
 NVCC_FLAGS = [

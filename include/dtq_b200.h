@@ -168,6 +168,19 @@ int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, i
                         int64_t cols, void *stream);
 
 /*
+ * dtq_mx_fp8_quantize through shared memory: same outputs, but the input is staged by the bulk
+ * asynchronous copy engine (TMA, cp.async.bulk + mbarrier ring) for a persistent grid of
+ * producer/consumer CTAs instead of being loaded straight into registers.  Kept as a measured
+ * alternative (the register path is the default because it is faster on B200 at every size
+ * measured).  Needs 16-byte aligned input, 8-byte aligned payload, and `status_dev`, one int in
+ * device memory (zero it once): a bounded wait that gives up stores DTQ_ERR_TIMEOUT there.
+ * Replaces the same reference code as dtq_mx_fp8_quantize (src/mx_cast.cu:96-161), whose kernel
+ * also stages its tile in shared memory.
+ */
+int dtq_mx_fp8_quantize_tma(const void *in_bf16, void *payload, void *scales_e8m0, int64_t rows,
+                            int64_t cols, int *status_dev, void *stream);
+
+/*
  * As dtq_mx_fp8_quantize, but the scales are written directly in the blocked layout that the
  * reference's MX GEMM (mx_fp8_bf16, src/mx_fp8_bf16.cu:97-110,197-205) hands to CUTLASS
  * (Sm1xxBlockScaledConfig::tile_atom_to_shape_SFA): 128-row x 4-block atoms of 512 bytes,

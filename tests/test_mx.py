@@ -194,3 +194,38 @@ def test_blocked_layout_matches_the_cutlass_layout_function():
         _, row_major = qo.mx_fp8_quantize(a)
         got = as_bytes(s).numpy()[table[:, 2]]
         assert np.array_equal(got, row_major.view(torch.uint8).numpy()[table[:, 0] * (cols // 32) + table[:, 1]])
+
+
+# ---- the shared-memory-staged (TMA bulk copy) variant ---------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(1, 32), (3, 96), (128, 128), (77, 2048), (1000, 2080), (4096, 8192), (5, 4128)])
+def test_tma_staged_variant_gives_the_same_bytes(rows, cols):
+    from driss_torch_b200 import _cabi
+
+    a = workloads.make_cfg3(rows=rows, cols=cols)
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    n = a.numel()
+    pbuf = torch.full((n + 256,), 0x5A, dtype=torch.uint8, device="cuda")
+    sbuf = torch.full((n // 32 + 256,), 0x5A, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        _cabi.mx_fp8_quantize_tma(a.cuda(), payload=pbuf[:n].view(E4M3).view(rows, cols),
+                                  scales=sbuf[: n // 32].view(torch.float8_e8m0fnu), status=status)
+    assert status.item() == 0
+    assert_fp8_equal(pbuf[:n].view(E4M3).view(rows, cols), want_p, E4M3, "tma payload")
+    assert torch.equal(sbuf[: n // 32].cpu(), as_bytes(want_s))
+    assert (pbuf[n:] == 0x5A).all() and (sbuf[n // 32 :] == 0x5A).all()
+
+
+def test_tma_staged_variant_on_patterns_and_degenerate_blocks():
+    from driss_torch_b200 import _cabi
+
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    zeros = torch.zeros(128, 64)
+    zeros[:, 32:] = 2.0**-121
+    for a in (bits.view(64, 1024), zeros.to(torch.bfloat16)):
+        want_p, want_s = qo.mx_fp8_quantize(a)
+        p, s, status = _cabi.mx_fp8_quantize_tma(a.cuda())
+        assert status.item() == 0
+        assert_fp8_equal(p, want_p, E4M3, "tma payload")
+        assert torch.equal(as_bytes(s), as_bytes(want_s))
