@@ -255,7 +255,19 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
     t = timed(lambda i: _cabi.mx_fp8_quantize_blocked(xs[i], payload=ps[i], scales=sb[i]), ns, iters)
     line("cfg3", "mx_fp8_quantize_blocked", x.shape, t, algorithmic_bytes("mx_fp8_quantize", w.rows, w.cols), None,
          note="scales written in the MX GEMM's blocked layout (the reference needs a separate to_blocked pass)")
-    del xs, ps, ss, sb
+    pt = [torch.empty(w.cols, w.rows, dtype=E4M3, device=dev) for _ in range(ns)]
+    st = [torch.empty(x.numel() // 32, dtype=torch.float8_e8m0fnu, device=dev) for _ in range(ns)]
+    dual_bytes = x.numel() * 2 + 2 * (x.numel() + x.numel() // 32)
+    t = timed(lambda i: _cabi.mx_fp8_quantize_dual(xs[i], ps[i], ss[i], pt[i], st[i]), ns, iters)
+
+    def two_casts(i):
+        _cabi.mx_fp8_quantize(xs[i], payload=ps[i], scales=ss[i])
+        _cabi.mx_fp8_quantize(xs[i].t().contiguous(), payload=pt[i], scales=st[i])
+
+    t2 = timed(two_casts, ns, iters)
+    line("cfg3", "mx_fp8_quantize_dual (x and x^T from one read)", x.shape, t, dual_bytes, None,
+         note=f"same four outputs by cast + torch transpose + cast: {t2[0] * 1e3:.1f} us")
+    del xs, ps, ss, sb, pt, st
 
     # cfg4: row-wise dynamic quant bf16 [32768,4096] (no reference op)
     w = workloads.WORKLOADS["cfg4"]

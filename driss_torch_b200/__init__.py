@@ -97,6 +97,13 @@ def cast_with_amax(inpt: Tensor, amax_value: Tensor, dtype: torch.dtype) -> tupl
     return ops.cast_with_amax(inpt, amax_value, dtype)
 
 
+def mx_fp8_quantize_dual(input: Tensor) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """``(p, s, p_t, s_t)`` with ``(p, s) == mx_fp8_quantize(x)`` and
+    ``(p_t, s_t) == mx_fp8_quantize(x.t().contiguous())``, from a single read of ``x``
+    (both dimensions multiples of 32)."""
+    return ops.mx_fp8_quantize_dual(input)
+
+
 def mx_fp8_quantize_blocked(input: Tensor) -> tuple[Tensor, Tensor]:
     """``mx_fp8_quantize`` with the E8M0 scales already in the blocked (128x4-atom) layout that the MX
     GEMM ``mx_fp8_bf16`` expects, i.e. without the separate ``to_blocked`` pass; zero in the padding."""
@@ -119,6 +126,7 @@ __all__ = [
     "dynamic_scaled_quant_with_scale",
     "dynamic_scaled_quant_rowwise",
     "cast_with_amax",
+    "mx_fp8_quantize_dual",
     "mx_fp8_quantize_blocked",
     "check_device_status",
     "ShardedQuantizer",

@@ -36,6 +36,7 @@ SIGNATURES = {
     "dtq_cast_with_amax": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant_rowwise": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
+    "dtq_mx_fp8_quantize_dual": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp], _i32),
     "dtq_mx_fp8_quantize_tma": ([_vp, _vp, _vp, _i64, _i64, _vp, _vp], _i32),
     "dtq_mx_blocked_scale_bytes": ([_i64, _i64], _sz),
     "dtq_mx_fp8_quantize_blocked": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
@@ -206,3 +207,16 @@ def mx_fp8_quantize_tma(x, payload=None, scales=None, status=None):
     check(load().dtq_mx_fp8_quantize_tma(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols,
                                          status.data_ptr(), _stream()), "dtq_mx_fp8_quantize_tma")
     return payload, scales, status
+
+
+def mx_fp8_quantize_dual(x, payload=None, scales=None, payload_t=None, scales_t=None):
+    """MX cast of x and of its transpose from one read of x."""
+    rows, cols = x.shape
+    e4m3, e8m0 = torch.float8_e4m3fn, torch.float8_e8m0fnu
+    payload = torch.empty(rows, cols, dtype=e4m3, device=x.device) if payload is None else payload
+    scales = torch.empty(rows * (cols // 32), dtype=e8m0, device=x.device) if scales is None else scales
+    payload_t = torch.empty(cols, rows, dtype=e4m3, device=x.device) if payload_t is None else payload_t
+    scales_t = torch.empty(cols * (rows // 32), dtype=e8m0, device=x.device) if scales_t is None else scales_t
+    check(load().dtq_mx_fp8_quantize_dual(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), payload_t.data_ptr(),
+                                          scales_t.data_ptr(), rows, cols, _stream()), "dtq_mx_fp8_quantize_dual")
+    return payload, scales, payload_t, scales_t

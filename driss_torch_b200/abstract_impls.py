@@ -54,3 +54,11 @@ def mx_fp8_quantize_blocked_meta(x: torch.Tensor):
     m, n = x.shape
     nbytes = ((m + 127) // 128) * ((n // 32 + 3) // 4) * 512
     return torch.empty_like(x, dtype=torch.float8_e4m3fn), torch.empty(nbytes, dtype=torch.float8_e8m0fnu, device=x.device)
+
+
+@register_fake("DrissTorch::mx_fp8_quantize_dual")
+def mx_fp8_quantize_dual_meta(x: torch.Tensor):
+    m, n = x.shape
+    e4m3, e8m0 = torch.float8_e4m3fn, torch.float8_e8m0fnu
+    return (torch.empty((m, n), dtype=e4m3, device=x.device), torch.empty(m * (n // 32), dtype=e8m0, device=x.device),
+            torch.empty((n, m), dtype=e4m3, device=x.device), torch.empty(n * (m // 32), dtype=e8m0, device=x.device))

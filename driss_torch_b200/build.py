@@ -36,6 +36,7 @@ KERNEL_SOURCES = [
     "rowwise_quant.cu",
     "mx_cast.cu",
     "mx_cast_tma.cu",
+    "mx_cast_dual.cu",
 ]
 
 NVCC_FLAGS = [

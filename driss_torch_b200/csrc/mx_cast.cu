@@ -14,8 +14,8 @@
 // 255); payload = e4m3_satfinite(x * (1/scale)); scale byte = ue8m0(scale) rounded up,
 // saturating (255 -> 0xFE).  e is monotone in |x|, so the block max is taken on the raw
 // 15-bit magnitudes with packed 16-bit integer max.
-#include "dtq_device.cuh"
 #include "dtq_host.h"
+#include "mx_common.cuh"
 
 namespace dtq {
 namespace {
@@ -26,44 +26,6 @@ namespace {
 #endif
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;  // tied to the scale-byte mapping below: lane&3 picks the iteration
-
-// Largest 15-bit magnitude among the eight bf16 of a chunk.
-__device__ __forceinline__ uint32_t chunk_absmax_bits(uint4 v) {
-  const uint32_t m = __vmaxu2(__vmaxu2(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu),
-                              __vmaxu2(v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu));
-  return max(m & 0xFFFFu, m >> 16);
-}
-
-// Biased exponent of the block scale from the block's largest magnitude bits.
-__device__ __forceinline__ int block_biased_exponent(uint32_t mag) {
-  const int be = static_cast<int>(mag >> 7);
-  int e = be - 127 + ((mag & 0x7Fu) != 0);
-  if (be == 0) e = (mag == 0) ? -128 : -126;
-  return min(255, max(0, e - 8 + 127));
-}
-
-// 1 / scale for scale = 2^(biased-127), as the reference's rcp.rn gives it: exact for every power
-// of two (2^-127 is the subnormal 0x00400000), +inf for scale 0 (biased 0), 0 for scale +inf
-// (biased 255).  Built from the exponent instead of running the reciprocal sequence.
-__device__ __forceinline__ float inverse_scale(int biased) {
-  const int e = 254 - biased;  // exponent field of the reciprocal
-  uint32_t bits = static_cast<uint32_t>(e) << 23;
-  if (e <= 0) bits = e == 0 ? 0x00400000u : 0u;
-  if (biased == 0) bits = 0x7F800000u;
-  return __uint_as_float(bits);
-}
-
-__device__ __forceinline__ uint32_t mx_pair(uint32_t w, float inv) {
-  const float2 p = __fmul2_rn(make_float2(bf16_lo(w), bf16_hi(w)), make_float2(inv, inv));
-  return cvt_fp8x2<DTQ_E4M3>(p.x, p.y);
-}
-
-__device__ __forceinline__ uint2 mx_payload(uint4 v, float inv) {
-  uint2 r;
-  r.x = mx_pair(v.x, inv) | (mx_pair(v.y, inv) << 16);
-  r.y = mx_pair(v.z, inv) | (mx_pair(v.w, inv) << 16);
-  return r;
-}
 
 // Where the scale of MX block `blk` (row-major index over [rows, kblocks]) goes.
 // Row-major: scales[blk], the reference's layout (src/mx_cast.cu:199,210-211).

@@ -1,0 +1,134 @@
+// mx_fp8_quantize in both orientations from ONE read of the input.
+//
+// Training with MX operands needs a matrix quantised along its last dimension for one GEMM and
+// its transpose quantised along ITS last dimension (blocks down the columns of the original) for
+// the other.  The reference declares `axis` / `transpose` on mx_fp8_quantize but ignores them
+// (src/mx_cast.cu:168-171), so a caller has to transpose and cast a second time: two more
+// passes over the data.  This kernel produces, from a contiguous bf16 [M, N] input,
+//   payload   [M, N], scales   [M * N/32]   == mx_fp8_quantize(x)                  and
+//   payload_t [N, M], scales_t [N * M/32]   == mx_fp8_quantize(x.t().contiguous())
+// byte for byte, reading x once: 2 + 2 * (1 + 1/32) bytes per element instead of 2 * (3 + 1/32)
+// plus the transpose.
+//
+// A CTA owns a 128 x 128 tile, so every global access is at least a full 128-byte line in both
+// orientations.  Row direction: as in the stream kernel -- each lane loads 16 bytes, four lanes
+// share an MX block, results go out from registers; the chunk is also parked in shared memory
+// (32 KiB, 4-word groups XOR-swizzled by the 16-row group so that both phases are free of bank
+// conflicts).  Column direction: a lane owns two neighbouring columns x 16 rows (sixteen 32-bit
+// shared loads), lanes l and l^1 together hold one MX block of each column; the eight lanes of a
+// column pair write 128 contiguous bytes of a row of the transposed payload.
+// CTAs are numbered so that eight row tiles of one column tile run back to back, then the next
+// column tile: the 4-byte scale fragments that neighbouring tiles add to one 32-byte sector of
+// either scale array arrive close together in time.
+#include "dtq_host.h"
+#include "mx_common.cuh"
+
+namespace dtq {
+namespace {
+
+constexpr int kTile = 128;          // rows and columns of a CTA tile
+constexpr int kTileWords = kTile / 2;  // 32-bit words (bf16 pairs) per tile row
+constexpr int kThreadsDual = 256;
+constexpr int kRowPasses = kTile / 16;  // a pass of 8 warps covers 16 rows (2 per warp)
+constexpr int kGroupRowTiles = 8;
+
+__global__ void __launch_bounds__(kThreadsDual)
+mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
+               uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows, int64_t cols,
+               int64_t row_tiles, int64_t col_tiles) {
+  __shared__ __align__(16) uint32_t tile[kTile][kTileWords];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  // grouped numbering: groups of kGroupRowTiles row tiles; inside a group row tiles vary fastest
+  const int64_t pid = blockIdx.x;
+  const int64_t per_group = kGroupRowTiles * col_tiles;
+  const int64_t first_row_tile = (pid / per_group) * kGroupRowTiles;
+  const int64_t group_rows = min(row_tiles - first_row_tile, int64_t(kGroupRowTiles));
+  const int64_t in_group = pid % per_group;
+  const int64_t row0 = (first_row_tile + in_group % group_rows) * kTile;
+  const int64_t col0 = (in_group / group_rows) * kTile;
+  const int64_t kblocks = cols / 32;
+
+  // ---- row direction: in pass p warp w owns tile rows 16p + 2w and + 1; lane l the columns 8(l&15) .. +7
+  const int chunk = lane & 15;
+  const int64_t c = col0 + chunk * 8;
+  const bool col_live = c < cols;  // cols % 32 == 0, so a quad of lanes is live or dead as a whole
+  uint4 v[kRowPasses];
+#pragma unroll
+  for (int p = 0; p < kRowPasses; ++p) {
+    const int64_t r = row0 + p * 16 + warp * 2 + (lane >> 4);
+    v[p] = (col_live && r < rows) ? ldg_stream(in + r * cols + c) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int p = 0; p < kRowPasses; ++p) {
+    const int rt = p * 16 + warp * 2 + (lane >> 4);  // rt >> 4 == p: the 16-row group of this row
+    const int64_t r = row0 + rt;
+    *reinterpret_cast<uint4 *>(&tile[rt][(chunk * 4) ^ (p << 2)]) = v[p];
+    uint32_t mag = chunk_absmax_bits(v[p]);
+    mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 1));
+    mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
+    const int biased = block_biased_exponent(mag);
+    if (col_live && r < rows) {
+      stg_stream(payload + r * cols + c, mx_payload(v[p], inverse_scale(biased)));
+      if ((lane & 3) == 0) scales[r * kblocks + (c >> 5)] = mx_scale_byte(biased);
+    }
+  }
+  __syncthreads();
+
+  // ---- column direction: lane = 8 * q + g: 16-row group g of the tile, column pair 4 * warp + q (+ 32 per pass)
+  const int g = lane & 7, q = lane >> 3;
+  const int64_t r_first = row0 + g * 16;
+  const bool rows_live = r_first < rows;  // rows % 32 == 0: lanes g and g^1 are live or dead together
+  const int64_t row_blocks = rows / 32;
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    const int word = pass * 32 + warp * 4 + q;
+    const int64_t col_a = col0 + word * 2;  // and col_a + 1; cols is even, so both or neither exist
+    uint32_t w[16];
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      w[i] = tile[g * 16 + i][word ^ (g << 2)];
+      m = __vmaxu2(m, w[i] & 0x7FFF7FFFu);
+    }
+    m = __vmaxu2(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    const int biased_a = block_biased_exponent(m & 0xFFFFu), biased_b = block_biased_exponent(m >> 16);
+    const float inv_a = inverse_scale(biased_a), inv_b = inverse_scale(biased_b);
+    uint32_t a[8], b[8];  // two consecutive rows of one column per word, as e4m3 byte pairs
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a[i] = mx_pair(__byte_perm(w[2 * i], w[2 * i + 1], 0x5410), inv_a);
+      b[i] = mx_pair(__byte_perm(w[2 * i], w[2 * i + 1], 0x7632), inv_b);
+    }
+    if (rows_live && col_a < cols) {
+      uint8_t *dst = payload_t + col_a * rows + r_first;  // 16 consecutive bytes of row col_a of the transpose
+      stg_stream(dst, make_uint4(a[0] | (a[1] << 16), a[2] | (a[3] << 16), a[4] | (a[5] << 16), a[6] | (a[7] << 16)));
+      stg_stream(dst + rows, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
+      if ((g & 1) == 0) {
+        uint8_t *sdst = scales_t + col_a * row_blocks + (r_first >> 5);
+        sdst[0] = mx_scale_byte(biased_a);
+        sdst[row_blocks] = mx_scale_byte(biased_b);
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace dtq
+
+extern "C" int dtq_mx_fp8_quantize_dual(const void *in_bf16, void *payload, void *scales_e8m0, void *payload_t,
+                                        void *scales_t_e8m0, int64_t rows, int64_t cols, void *stream) {
+  using namespace dtq;
+  if (rows < 0 || cols < 0) return DTQ_ERR_INVALID_ARGUMENT;
+  if (cols % 32 != 0 || rows % 32 != 0) return DTQ_ERR_SHAPE;
+  if (rows == 0 || cols == 0) return DTQ_OK;
+  if (!in_bf16 || !payload || !scales_e8m0 || !payload_t || !scales_t_e8m0) return DTQ_ERR_INVALID_ARGUMENT;
+  // 16-byte loads of the input, 8-byte stores of the payload, 16-byte stores of the transposed payload
+  if (!aligned_to(in_bf16, 16) || !aligned_to(payload, 8) || !aligned_to(payload_t, 16)) return DTQ_ERR_INVALID_ARGUMENT;
+  const int64_t row_tiles = ceil_div64(rows, kTile), col_tiles = ceil_div64(cols, kTile);
+  if (row_tiles > 0x7FFFFFFFLL / col_tiles) return DTQ_ERR_TOO_LARGE;  // grid.x
+  mx_dual_kernel<<<static_cast<unsigned>(row_tiles * col_tiles), kThreadsDual, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t *>(in_bf16), static_cast<uint8_t *>(payload), static_cast<uint8_t *>(scales_e8m0),
+      static_cast<uint8_t *>(payload_t), static_cast<uint8_t *>(scales_t_e8m0), rows, cols, row_tiles, col_tiles);
+  return cuda_status(cudaGetLastError());
+}

@@ -11,8 +11,8 @@
 // entry point uses it.
 #include <atomic>
 
-#include "dtq_device.cuh"
 #include "dtq_host.h"
+#include "mx_common.cuh"
 
 namespace dtq {
 namespace {
@@ -65,29 +65,6 @@ __device__ __forceinline__ void bulk_load(void *dst_smem, const void *src_gmem, 
                    smem_u32(dst_smem)),
                "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
-}
-
-__device__ __forceinline__ uint32_t chunk_absmax_bits(uint4 v) {
-  const uint32_t m = __vmaxu2(__vmaxu2(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu),
-                              __vmaxu2(v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu));
-  return max(m & 0xFFFFu, m >> 16);
-}
-__device__ __forceinline__ int block_biased_exponent(uint32_t mag) {
-  const int be = static_cast<int>(mag >> 7);
-  int e = be - 127 + ((mag & 0x7Fu) != 0);
-  if (be == 0) e = (mag == 0) ? -128 : -126;
-  return min(255, max(0, e - 8 + 127));
-}
-__device__ __forceinline__ float inverse_scale(int biased) {
-  const int e = 254 - biased;
-  uint32_t bits = static_cast<uint32_t>(e) << 23;
-  if (e <= 0) bits = e == 0 ? 0x00400000u : 0u;
-  if (biased == 0) bits = 0x7F800000u;
-  return __uint_as_float(bits);
-}
-__device__ __forceinline__ uint32_t mx_pair(uint32_t w, float inv) {
-  const float2 p = __fmul2_rn(make_float2(bf16_lo(w), bf16_hi(w)), make_float2(inv, inv));
-  return cvt_fp8x2<DTQ_E4M3>(p.x, p.y);
 }
 
 struct __align__(128) TmaSmem {

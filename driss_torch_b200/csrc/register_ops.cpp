@@ -168,6 +168,26 @@ std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize(at::Tensor input, int64_t blo
 
 // ---- additions ---------------------------------------------------------------------------------------
 
+// MX cast of the input and of its transpose from one read of the input.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> mx_fp8_quantize_dual(at::Tensor input) {
+  TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D");
+  TORCH_CHECK(input.scalar_type() == at::kBFloat16, "Input tensor must be bfloat16, but got ", input.dtype());
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(m % 32 == 0 && n % 32 == 0, "Both dimensions must be multiples of the block size 32, but got ", m, " x ", n);
+  auto fp8 = input.options().dtype(at::kFloat8_e4m3fn);
+  auto e8m0 = input.options().dtype(at::kFloat8_e8m0fnu);
+  at::Tensor out = at::empty({m, n}, fp8), out_t = at::empty({n, m}, fp8);
+  at::Tensor scale = at::empty({m * (n / 32)}, e8m0), scale_t = at::empty({n * (m / 32)}, e8m0);
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_mx_fp8_quantize_dual(input.data_ptr(), out.data_ptr(), scale.data_ptr(), out_t.data_ptr(),
+                                        scale_t.data_ptr(), m, n, stream.stream()),
+               "mx_fp8_quantize_dual");
+  return {out, scale, out_t, scale_t};
+}
+
 // MX cast whose scales come out in the blocked layout of the MX GEMM (1-D e8m0 tensor of
 // 512 * ceil(M/128) * ceil(N/128) bytes, zero in the padding).
 std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize_blocked(at::Tensor input) {
@@ -249,6 +269,8 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("dynamic_scaled_quant_rowwise", c10::DispatchKey::CUDA, TORCH_FN(dynamic_scaled_quant_rowwise));
   m.def("cast_with_amax(Tensor input, Tensor amax, ScalarType dtype) -> (Tensor, Tensor)");
   m.impl("cast_with_amax", c10::DispatchKey::CUDA, TORCH_FN(cast_with_amax));
+  m.def("mx_fp8_quantize_dual(Tensor input) -> (Tensor, Tensor, Tensor, Tensor)");
+  m.impl("mx_fp8_quantize_dual", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_dual));
   m.def("mx_fp8_quantize_blocked(Tensor input) -> (Tensor, Tensor)");
   m.impl("mx_fp8_quantize_blocked", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_blocked));
   m.def("check_device_status() -> ()");

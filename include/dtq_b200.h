@@ -168,6 +168,18 @@ int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, i
                         int64_t cols, void *stream);
 
 /*
+ * Both orientations from one read of a contiguous bf16 [rows, cols] matrix (rows % 32 == 0,
+ * cols % 32 == 0):
+ *   payload   [rows, cols], scales   [rows * cols/32]  = dtq_mx_fp8_quantize(x)
+ *   payload_t [cols, rows], scales_t [cols * rows/32]  = dtq_mx_fp8_quantize(transpose(x))
+ * byte for byte.  The reference declares `axis` and `transpose` on its op but ignores them
+ * (src/mx_cast.cu:168-171); getting the second operand there takes a transpose and a second
+ * cast.  `in` 16-byte, `payload` 8-byte, `payload_t` 16-byte aligned.
+ */
+int dtq_mx_fp8_quantize_dual(const void *in_bf16, void *payload, void *scales_e8m0, void *payload_t,
+                             void *scales_t_e8m0, int64_t rows, int64_t cols, void *stream);
+
+/*
  * dtq_mx_fp8_quantize through shared memory: same outputs, but the input is staged by the bulk
  * asynchronous copy engine (TMA, cp.async.bulk + mbarrier ring) for a persistent grid of
  * producer/consumer CTAs instead of being loaded straight into registers.  Kept as a measured

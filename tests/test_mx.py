@@ -229,3 +229,47 @@ def test_tma_staged_variant_on_patterns_and_degenerate_blocks():
         assert status.item() == 0
         assert_fp8_equal(p, want_p, E4M3, "tma payload")
         assert torch.equal(as_bytes(s), as_bytes(want_s))
+
+
+# ---- both orientations from one read --------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(32, 32), (64, 256), (96, 288), (32, 8224), (1024, 512), (4096, 4096), (160, 96), (1184, 448), (2048, 32), (32, 2048)])
+def test_dual_equals_cast_of_the_matrix_and_of_its_transpose(rows, cols):
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg3(rows=rows, cols=cols)
+    ad = a.cuda()
+    p, s, p_t, s_t = dt.mx_fp8_quantize_dual(ad)
+    assert p.shape == (rows, cols) and p_t.shape == (cols, rows)
+    assert s.shape == (rows * cols // 32,) and s_t.shape == (cols * rows // 32,)
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    want_pt, want_st = qo.mx_fp8_quantize(a.t().contiguous())
+    assert_fp8_equal(p, want_p, E4M3, "payload")
+    assert torch.equal(as_bytes(s), as_bytes(want_s))
+    assert_fp8_equal(p_t, want_pt, E4M3, "transposed payload")
+    assert torch.equal(as_bytes(s_t), as_bytes(want_st))
+    # and against the single-orientation op on the GPU
+    q, qs = dt.mx_fp8_quantize(ad.t().contiguous())
+    assert torch.equal(as_bytes(p_t), as_bytes(q)) and torch.equal(as_bytes(s_t), as_bytes(qs))
+
+
+def test_dual_on_every_bf16_pattern_and_degenerate_blocks_and_errors():
+    import driss_torch_b200 as dt
+
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    g = torch.Generator().manual_seed(2)
+    zeros = torch.zeros(128, 64)
+    zeros[:, 32:] = 2.0**-121
+    zeros[64:, :] = 0.0
+    for a in (bits.view(256, 256), bits[torch.randperm(65536, generator=g)].view(64, 1024), zeros.to(torch.bfloat16)):
+        p, s, p_t, s_t = dt.mx_fp8_quantize_dual(a.cuda())
+        want_p, want_s = qo.mx_fp8_quantize(a)
+        want_pt, want_st = qo.mx_fp8_quantize(a.t().contiguous())
+        assert_fp8_equal(p, want_p, E4M3, "payload")
+        assert_fp8_equal(p_t, want_pt, E4M3, "transposed payload")
+        assert torch.equal(as_bytes(s), as_bytes(want_s)) and torch.equal(as_bytes(s_t), as_bytes(want_st))
+    a = torch.zeros(48, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        dt.mx_fp8_quantize_dual(a)  # rows not a multiple of 32
+    with pytest.raises(RuntimeError):
+        dt.mx_fp8_quantize_dual(torch.zeros(64, 64, device="cuda"))  # not bf16
