@@ -65,11 +65,10 @@ mx_stream_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, ui
       mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 1));
       mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
       const int biased = block_biased_exponent(mag);
-      const float scale = __int_as_float(biased << 23);
       const float inv = inverse_scale(biased);
       const int64_t c = warp_first + u * 32 + lane;
       if (c < nchunks) stg_stream(payload + c * 8, mx_payload(v[u], inv));
-      if ((lane & 3) == u) my_scale_byte = cvt_ue8m0(scale);
+      if ((lane & 3) == u) my_scale_byte = mx_scale_byte(biased);
     }
     // lane = 4*k + j holds the scale of block (u = j, quad k): block index u*8 + k in the warp's span.
     const int64_t blk = warp_first / 4 + (lane & 3) * 8 + (lane >> 2);

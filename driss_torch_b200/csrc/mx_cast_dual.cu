@@ -30,34 +30,29 @@ constexpr int kTile = 128;          // rows and columns of a CTA tile
 constexpr int kTileWords = kTile / 2;  // 32-bit words (bf16 pairs) per tile row
 constexpr int kThreadsDual = 256;
 constexpr int kRowPasses = kTile / 16;  // a pass of 8 warps covers 16 rows (2 per warp)
-constexpr int kGroupRowTiles = 8;
+#ifndef DTQ_DUAL_GROUP
+#define DTQ_DUAL_GROUP 8
+#endif
+constexpr int kGroupRowTiles = DTQ_DUAL_GROUP;
 
-__global__ void __launch_bounds__(kThreadsDual)
-mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
-               uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows, int64_t cols,
-               int64_t row_tiles, int64_t col_tiles) {
-  __shared__ __align__(16) uint32_t tile[kTile][kTileWords];
+// One tile.  FULL: the tile lies inside the matrix, no access is predicated.
+template <bool FULL>
+__device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], const uint16_t *__restrict__ in,
+                                          uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
+                                          uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows,
+                                          int64_t cols, int64_t row0, int64_t col0) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-
-  // grouped numbering: groups of kGroupRowTiles row tiles; inside a group row tiles vary fastest
-  const int64_t pid = blockIdx.x;
-  const int64_t per_group = kGroupRowTiles * col_tiles;
-  const int64_t first_row_tile = (pid / per_group) * kGroupRowTiles;
-  const int64_t group_rows = min(row_tiles - first_row_tile, int64_t(kGroupRowTiles));
-  const int64_t in_group = pid % per_group;
-  const int64_t row0 = (first_row_tile + in_group % group_rows) * kTile;
-  const int64_t col0 = (in_group / group_rows) * kTile;
   const int64_t kblocks = cols / 32;
 
   // ---- row direction: in pass p warp w owns tile rows 16p + 2w and + 1; lane l the columns 8(l&15) .. +7
   const int chunk = lane & 15;
   const int64_t c = col0 + chunk * 8;
-  const bool col_live = c < cols;  // cols % 32 == 0, so a quad of lanes is live or dead as a whole
+  const bool col_live = FULL || c < cols;  // cols % 32 == 0, so a quad of lanes is live or dead as a whole
   uint4 v[kRowPasses];
 #pragma unroll
   for (int p = 0; p < kRowPasses; ++p) {
     const int64_t r = row0 + p * 16 + warp * 2 + (lane >> 4);
-    v[p] = (col_live && r < rows) ? ldg_stream(in + r * cols + c) : make_uint4(0, 0, 0, 0);
+    v[p] = (FULL || (col_live && r < rows)) ? ldg_stream(in + r * cols + c) : make_uint4(0, 0, 0, 0);
   }
 #pragma unroll
   for (int p = 0; p < kRowPasses; ++p) {
@@ -68,7 +63,7 @@ mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, u
     mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 1));
     mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
     const int biased = block_biased_exponent(mag);
-    if (col_live && r < rows) {
+    if (FULL || (col_live && r < rows)) {
       stg_stream(payload + r * cols + c, mx_payload(v[p], inverse_scale(biased)));
       if ((lane & 3) == 0) scales[r * kblocks + (c >> 5)] = mx_scale_byte(biased);
     }
@@ -78,7 +73,7 @@ mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, u
   // ---- column direction: lane = 8 * q + g: 16-row group g of the tile, column pair 4 * warp + q (+ 32 per pass)
   const int g = lane & 7, q = lane >> 3;
   const int64_t r_first = row0 + g * 16;
-  const bool rows_live = r_first < rows;  // rows % 32 == 0: lanes g and g^1 are live or dead together
+  const bool rows_live = FULL || r_first < rows;  // rows % 32 == 0: lanes g and g^1 are live or dead together
   const int64_t row_blocks = rows / 32;
 #pragma unroll
   for (int pass = 0; pass < 2; ++pass) {
@@ -89,9 +84,9 @@ mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, u
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       w[i] = tile[g * 16 + i][word ^ (g << 2)];
-      m = __vmaxu2(m, w[i] & 0x7FFF7FFFu);
+      m = packed_mag_max(m, w[i] & 0x7FFF7FFFu);
     }
-    m = __vmaxu2(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+    m = packed_mag_max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
     const int biased_a = block_biased_exponent(m & 0xFFFFu), biased_b = block_biased_exponent(m >> 16);
     const float inv_a = inverse_scale(biased_a), inv_b = inverse_scale(biased_b);
     uint32_t a[8], b[8];  // two consecutive rows of one column per word, as e4m3 byte pairs
@@ -100,7 +95,7 @@ mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, u
       a[i] = mx_pair(__byte_perm(w[2 * i], w[2 * i + 1], 0x5410), inv_a);
       b[i] = mx_pair(__byte_perm(w[2 * i], w[2 * i + 1], 0x7632), inv_b);
     }
-    if (rows_live && col_a < cols) {
+    if (FULL || (rows_live && col_a < cols)) {
       uint8_t *dst = payload_t + col_a * rows + r_first;  // 16 consecutive bytes of row col_a of the transpose
       stg_stream(dst, make_uint4(a[0] | (a[1] << 16), a[2] | (a[3] << 16), a[4] | (a[5] << 16), a[6] | (a[7] << 16)));
       stg_stream(dst + rows, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
@@ -111,6 +106,28 @@ mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, u
       }
     }
   }
+}
+
+#ifndef DTQ_DUAL_MIN_BLOCKS
+#define DTQ_DUAL_MIN_BLOCKS 4
+#endif
+__global__ void __launch_bounds__(kThreadsDual, DTQ_DUAL_MIN_BLOCKS)
+mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
+               uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows, int64_t cols,
+               int64_t row_tiles, int64_t col_tiles) {
+  __shared__ __align__(16) uint32_t tile[kTile][kTileWords];
+  // grouped numbering: groups of kGroupRowTiles row tiles; inside a group row tiles vary fastest
+  const int64_t pid = blockIdx.x;
+  const int64_t per_group = kGroupRowTiles * col_tiles;
+  const int64_t first_row_tile = (pid / per_group) * kGroupRowTiles;
+  const int64_t group_rows = min(row_tiles - first_row_tile, int64_t(kGroupRowTiles));
+  const int64_t in_group = pid % per_group;
+  const int64_t row0 = (first_row_tile + in_group % group_rows) * kTile;
+  const int64_t col0 = (in_group / group_rows) * kTile;
+  if (row0 + kTile <= rows && col0 + kTile <= cols)
+    dual_tile<true>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
+  else
+    dual_tile<false>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
 }
 
 }  // namespace

@@ -136,7 +136,6 @@ mx_tma_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8
       mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 1));
       mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
       const int biased = block_biased_exponent(mag);
-      const float scale = __int_as_float(biased << 23);
       const float inv = inverse_scale(biased);
       if (c < nchunks) {
         uint2 r;
@@ -144,7 +143,7 @@ mx_tma_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8
         r.y = mx_pair(v[u].z, inv) | (mx_pair(v[u].w, inv) << 16);
         stg_stream(payload + c * 8, r);
       }
-      if ((lane & 3) == u) my_scale_byte = cvt_ue8m0(scale);
+      if ((lane & 3) == u) my_scale_byte = mx_scale_byte(biased);
     }
     const int64_t blk = warp_first / 4 + (lane & 3) * 8 + (lane >> 2);
     if (blk * 4 < nchunks) scales[blk] = static_cast<uint8_t>(my_scale_byte);

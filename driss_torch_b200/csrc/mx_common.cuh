@@ -6,33 +6,39 @@
 
 namespace dtq {
 
+// Per-half maximum of two words of packed 15-bit bf16 magnitudes (sign bits clear): one bf16x2
+// max.  NaN-propagating, so a NaN (the largest magnitudes when read as integers) still wins; it
+// comes out as the canonical 0x7FFF, which has the exponent field and the non-zero mantissa of
+// every other NaN, hence the same block exponent.
+__device__ __forceinline__ uint32_t packed_mag_max(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // Largest 15-bit magnitude among the eight bf16 of a 16-byte chunk.
 __device__ __forceinline__ uint32_t chunk_absmax_bits(uint4 v) {
-  const uint32_t m = __vmaxu2(__vmaxu2(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu),
-                              __vmaxu2(v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu));
+  const uint32_t m = packed_mag_max(packed_mag_max(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu),
+                                    packed_mag_max(v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu));
   return max(m & 0xFFFFu, m >> 16);
 }
 
-// Biased exponent of the block scale from the block's largest magnitude bits:
+// Biased exponent of the block scale from the block's largest magnitude bits.  The reference:
 // e = ceil(log2 |x|) from the exponent field (+1 if the mantissa is non-zero; zero -> -128,
-// subnormal -> -126), biased = clamp(e - 8 + 127, 0, 255).  e is monotone in |x|, so taking the
+// subnormal -> -126), biased = clamp(e - 8 + 127, 0, 255); e is monotone in |x|, so taking the
 // maximum of the raw magnitudes first gives the same block exponent as the maximum of the e_i.
+// Here: (mag + 0x7F) >> 7 = exponent field + (mantissa != 0), so biased = that - 8 clamped at 0.
+// For the exponent field 0 (zero and subnormals) both forms are negative before the clamp, and
+// the upper clamp never acts: mag <= 0x7FFF gives at most 248.
 __device__ __forceinline__ int block_biased_exponent(uint32_t mag) {
-  const int be = static_cast<int>(mag >> 7);
-  int e = be - 127 + ((mag & 0x7Fu) != 0);
-  if (be == 0) e = (mag == 0) ? -128 : -126;
-  return min(255, max(0, e - 8 + 127));
+  return max(0, static_cast<int>((mag + 0x7Fu) >> 7) - 8);
 }
 
-// 1 / scale for scale = 2^(biased-127), as the reference's rcp.rn gives it: exact for every power
-// of two (2^-127 is the subnormal 0x00400000), +inf for scale 0 (biased 0), 0 for scale +inf
-// (biased 255).  Built from the exponent instead of running the reciprocal sequence.
+// 1 / scale for scale = 2^(biased-127), as the reference's rcp.rn gives it: the exact power of
+// two (a normal number, since biased <= 248), and +inf for scale 0 (biased 0).  Built from the
+// exponent instead of running the reciprocal sequence.
 __device__ __forceinline__ float inverse_scale(int biased) {
-  const int e = 254 - biased;  // exponent field of the reciprocal
-  uint32_t bits = static_cast<uint32_t>(e) << 23;
-  if (e <= 0) bits = e == 0 ? 0x00400000u : 0u;
-  if (biased == 0) bits = 0x7F800000u;
-  return __uint_as_float(bits);
+  return __uint_as_float(biased == 0 ? 0x7F800000u : static_cast<uint32_t>(254 - biased) << 23);
 }
 
 // Two packed bf16 -> two e4m3 bytes of x * inv.
@@ -48,7 +54,9 @@ __device__ __forceinline__ uint2 mx_payload(uint4 v, float inv) {
   return r;
 }
 
-// The scale byte: cvt.rp.satfinite.ue8m0 of 2^(biased-127) = biased, with 255 (+inf) clamped to 0xFE.
-__device__ __forceinline__ uint8_t mx_scale_byte(int biased) { return cvt_ue8m0(__int_as_float(biased << 23)); }
+// The scale byte.  The reference converts 2^(biased-127) with cvt.rp.satfinite.ue8m0x2.f32; for a
+// power of two in range that is the exponent field itself, 0.0 (biased 0) gives 0, and the
+// saturating case (biased 255) cannot occur (biased <= 248).
+__device__ __forceinline__ uint8_t mx_scale_byte(int biased) { return static_cast<uint8_t>(biased); }
 
 }  // namespace dtq
