@@ -52,6 +52,18 @@ def saturated_cast(
     return ops.saturated_cast(x, scale, out_dtype, transpose)
 
 
+def saturated_cast_transposed(x: Tensor, scale: Tensor, out_dtype: torch.dtype) -> Tensor:
+    """``saturated_cast(x.t().contiguous(), scale, out_dtype)`` without the separate transpose:
+    a contiguous ``[cols, rows]`` tensor.  (The reference declares ``transpose`` on
+    ``saturated_cast`` but asserts it off, driss_torch/__init__.py:24-38.)"""
+    return ops.saturated_cast_transposed(x, scale, out_dtype)
+
+
+def saturated_cast_dual(x: Tensor, scale: Tensor, out_dtype: torch.dtype) -> tuple[Tensor, Tensor]:
+    """``(saturated_cast(x), saturated_cast(x.t().contiguous()))`` from a single read of ``x``."""
+    return ops.saturated_cast_dual(x, scale, out_dtype)
+
+
 def amax(x: Tensor) -> Tensor:
     """``max(abs(x))`` as an fp32 tensor of shape [1]."""
     return ops.amax(x)
@@ -126,6 +138,8 @@ __all__ = [
     "dynamic_scaled_quant_with_scale",
     "dynamic_scaled_quant_rowwise",
     "cast_with_amax",
+    "saturated_cast_transposed",
+    "saturated_cast_dual",
     "mx_fp8_quantize_dual",
     "mx_fp8_quantize_blocked",
     "check_device_status",

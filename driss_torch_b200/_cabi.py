@@ -27,6 +27,7 @@ SIGNATURES = {
     "dtq_workspace_init": ([_vp, _sz, _vp], _i32),
     "dtq_workspace_status": ([_vp, _vp, _vp], _i32),
     "dtq_saturated_cast": ([_vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
+    "dtq_saturated_cast_transposed": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_amax": ([_vp, _vp, _i64, _i32, _vp, _sz, _vp], _i32),
     "dtq_amax_static_scratch": ([_vp, _vp, _i64, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp, _sz, _vp], _i32),
@@ -220,3 +221,15 @@ def mx_fp8_quantize_dual(x, payload=None, scales=None, payload_t=None, scales_t=
     check(load().dtq_mx_fp8_quantize_dual(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), payload_t.data_ptr(),
                                           scales_t.data_ptr(), rows, cols, _stream()), "dtq_mx_fp8_quantize_dual")
     return payload, scales, payload_t, scales_t
+
+
+def saturated_cast_transposed(x, scale, out_dtype, out_t=None, out=None, both=False):
+    """The cast of x transposed ([cols, rows]); with ``both`` (or ``out``) also the cast of x itself."""
+    rows, cols = x.shape
+    out_t = torch.empty(cols, rows, dtype=out_dtype, device=x.device) if out_t is None else out_t
+    if both and out is None:
+        out = torch.empty(rows, cols, dtype=out_dtype, device=x.device)
+    check(load().dtq_saturated_cast_transposed(x.data_ptr(), out.data_ptr() if out is not None else None, out_t.data_ptr(),
+                                               scale.data_ptr(), rows, cols, IN_CODE[x.dtype], OUT_CODE[out_dtype],
+                                               _stream()), "dtq_saturated_cast_transposed")
+    return (out, out_t) if out is not None else out_t

@@ -62,3 +62,14 @@ def mx_fp8_quantize_dual_meta(x: torch.Tensor):
     e4m3, e8m0 = torch.float8_e4m3fn, torch.float8_e8m0fnu
     return (torch.empty((m, n), dtype=e4m3, device=x.device), torch.empty(m * (n // 32), dtype=e8m0, device=x.device),
             torch.empty((n, m), dtype=e4m3, device=x.device), torch.empty(n * (m // 32), dtype=e8m0, device=x.device))
+
+
+@register_fake("DrissTorch::saturated_cast_transposed")
+def saturated_cast_transposed_meta(x: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype):
+    return torch.empty((x.shape[1], x.shape[0]), dtype=dtype, device=x.device)
+
+
+@register_fake("DrissTorch::saturated_cast_dual")
+def saturated_cast_dual_meta(x: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype):
+    return (torch.empty(tuple(x.shape), dtype=dtype, device=x.device),
+            torch.empty((x.shape[1], x.shape[0]), dtype=dtype, device=x.device))

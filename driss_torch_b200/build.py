@@ -31,6 +31,7 @@ NVCC = str(CUDA_HOME / "bin" / "nvcc")
 KERNEL_SOURCES = [
     "common.cu",
     "saturated_cast.cu",
+    "saturated_cast_t.cu",
     "amax.cu",
     "dynamic_scaled_quant.cu",
     "rowwise_quant.cu",

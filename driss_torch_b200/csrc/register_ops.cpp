@@ -98,6 +98,36 @@ at::Tensor saturated_cast(const at::Tensor &input, const at::Tensor &scale, at::
   return out;
 }
 
+// The cast of input.t() as a contiguous [cols, rows] tensor and, with `both`, also the cast of input.
+std::tuple<at::Tensor, at::Tensor> cast_transposed(const at::Tensor &input, const at::Tensor &scale,
+                                                   at::ScalarType dtype, bool both, const char *what) {
+  check_fp8(dtype);
+  check_input(input);
+  TORCH_CHECK(scale.scalar_type() == at::kFloat, "Scale tensor must be of type Float, but got ", scale.dtype());
+  TORCH_CHECK(scale.numel() == 1, "Scale tensor must be a scalar, but got ", scale.numel());
+  TORCH_CHECK(scale.is_cuda() && scale.device() == input.device(), "Scale tensor must live on the input's device");
+  const at::Tensor x = input.contiguous();
+  const int64_t rows = x.size(0), cols = x.size(1);
+  at::Tensor out_t = at::empty({cols, rows}, x.options().dtype(dtype));
+  at::Tensor out = both ? at::empty({rows, cols}, x.options().dtype(dtype)) : at::Tensor();
+  c10::cuda::CUDAGuard guard(x.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_saturated_cast_transposed(x.data_ptr(), both ? out.data_ptr() : nullptr, out_t.data_ptr(),
+                                             scale.data_ptr<float>(), rows, cols, in_code(x.scalar_type()),
+                                             out_code(dtype), stream.stream()),
+               what);
+  return {out, out_t};
+}
+
+at::Tensor saturated_cast_transposed(const at::Tensor &input, const at::Tensor &scale, at::ScalarType dtype) {
+  return std::get<1>(cast_transposed(input, scale, dtype, false, "saturated_cast_transposed"));
+}
+
+std::tuple<at::Tensor, at::Tensor> saturated_cast_dual(const at::Tensor &input, const at::Tensor &scale,
+                                                       at::ScalarType dtype) {
+  return cast_transposed(input, scale, dtype, true, "saturated_cast_dual");
+}
+
 at::Tensor amax(const at::Tensor &input) {
   check_input(input);
   // max is order independent, so any dense layout can be reduced over its storage.
@@ -269,6 +299,10 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("dynamic_scaled_quant_rowwise", c10::DispatchKey::CUDA, TORCH_FN(dynamic_scaled_quant_rowwise));
   m.def("cast_with_amax(Tensor input, Tensor amax, ScalarType dtype) -> (Tensor, Tensor)");
   m.impl("cast_with_amax", c10::DispatchKey::CUDA, TORCH_FN(cast_with_amax));
+  m.def("saturated_cast_transposed(Tensor input, Tensor scale, ScalarType dtype) -> Tensor");
+  m.impl("saturated_cast_transposed", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast_transposed));
+  m.def("saturated_cast_dual(Tensor input, Tensor scale, ScalarType dtype) -> (Tensor, Tensor)");
+  m.impl("saturated_cast_dual", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast_dual));
   m.def("mx_fp8_quantize_dual(Tensor input) -> (Tensor, Tensor, Tensor, Tensor)");
   m.impl("mx_fp8_quantize_dual", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_dual));
   m.def("mx_fp8_quantize_blocked(Tensor input) -> (Tensor, Tensor)");

@@ -71,6 +71,20 @@ int dtq_saturated_cast(const void *in, void *out, const float *scale, int64_t nu
                        int out_dtype, void *stream);
 
 /*
+ * The cast with the output transposed, or in both orientations from one read of a
+ * contiguous [rows, cols] input:
+ *   out_t [cols, rows] = dtq_saturated_cast(transpose(in))   always written
+ *   out   [rows, cols] = dtq_saturated_cast(in)              written unless `out` is NULL
+ * Same arithmetic as dtq_saturated_cast, bit for bit.  Any shape; the tiled fast path needs
+ * rows % 16 == 0, cols % 8 == 0 (bf16) or % 4 == 0 (fp32), `in` and `out_t` 16-byte and `out`
+ * 8-byte aligned.  The reference declares `transpose` on saturated_cast but its wrapper asserts
+ * it off (driss_torch/__init__.py:24-38) and the CUDA side only uses the flag to choose a kernel
+ * (src/saturated_cast.cu:168-181).
+ */
+int dtq_saturated_cast_transposed(const void *in, void *out, void *out_t, const float *scale, int64_t rows,
+                                  int64_t cols, int in_dtype, int out_dtype, void *stream);
+
+/*
  * out[0] = max_i |in[i]| as fp32 (-inf for numel == 0; NaNs are dropped), one
  * launch, no pre-initialised output.
  * Replaces driss_torch::amax and amax_kernel: src/amax.cu:50-80, :82-119.

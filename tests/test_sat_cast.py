@@ -171,3 +171,47 @@ def test_compile_fullgraph_uses_fake_impl():
     s = workloads.tensor_scale(a, torch.float8_e4m3fn)
     fn = torch.compile(dt.saturated_cast, fullgraph=True, backend="aot_eager")
     assert_fp8_equal(fn(a, s, torch.float8_e4m3fn), dt.saturated_cast(a, s, torch.float8_e4m3fn))
+
+
+# ---- transposed output / both orientations from one read -----------------------------------------------
+
+T_SHAPES = [(128, 128), (256, 64), (16, 8), (48, 200), (144, 1032), (4096, 512), (1040, 4104),  # tiled path
+            (3, 7), (64, 17), (33, 512), (512, 4097), (1, 1), (100, 36)]                         # byte-tile path
+
+
+@pytest.mark.parametrize("shape", T_SHAPES, ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("fp8_dtype", FP8_DTYPES)
+@pytest.mark.parametrize("in_dtype", IN_DTYPES)
+def test_transposed_and_dual_outputs(shape, in_dtype, fp8_dtype):
+    import driss_torch_b200 as dt
+
+    a = _input(shape[0], shape[1], in_dtype, seed=shape[0] * 31 + shape[1])
+    scale = workloads.tensor_scale(a, fp8_dtype)
+    a[0, 0] = float("inf")  # saturates
+    a[-1, -1] = -1e30       # saturates
+    a[shape[0] // 2, shape[1] // 2] = float("nan")
+    want = qo.saturated_cast(a, scale.item(), fp8_dtype)
+    ad, sd = a.cuda(), scale.cuda()
+    out_t = dt.saturated_cast_transposed(ad, sd, fp8_dtype)
+    assert out_t.shape == (shape[1], shape[0]) and out_t.is_contiguous() and out_t.dtype == fp8_dtype
+    assert_fp8_equal(out_t, want.t().contiguous(), fp8_dtype, "transposed")
+    out, out_t2 = dt.saturated_cast_dual(ad, sd, fp8_dtype)
+    assert out.shape == tuple(shape) and out.is_contiguous()
+    assert_fp8_equal(out, want, fp8_dtype, "dual: row-major")
+    assert_fp8_equal(out_t2, want.t().contiguous(), fp8_dtype, "dual: transposed")
+    # a non-contiguous input is made contiguous first
+    out_v = dt.saturated_cast_transposed(ad.t(), sd, fp8_dtype)
+    assert_fp8_equal(out_v, want, fp8_dtype, "transposed view in")
+
+
+def test_transposed_on_every_bf16_pattern():
+    import driss_torch_b200 as dt
+
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).view(256, 256)
+    for fp8_dtype in FP8_DTYPES:
+        for s in (1.0, 0.37, 448.0):
+            scale = torch.tensor([s])
+            want = qo.saturated_cast(bits, s, fp8_dtype)
+            out, out_t = dt.saturated_cast_dual(bits.cuda(), scale.cuda(), fp8_dtype)
+            assert_fp8_equal(out, want, fp8_dtype, "row-major")
+            assert_fp8_equal(out_t, want.t().contiguous(), fp8_dtype, "transposed")
