@@ -206,7 +206,20 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
     t = timed(lambda i: _cabi.saturated_cast(xs[i], scale, E4M3, out=outs[i]), ns, iters)
     rt = timed(lambda i: ref.saturated_cast(xs[i], scale, E4M3, False), ns, iters) if ref else None
     line("cfg1", "saturated_cast", x.shape, t, algorithmic_bytes("saturated_cast", w.rows, w.cols), rt)
-    del xs, outs
+    outs_t = [torch.empty(w.cols, w.rows, dtype=E4M3, device=dev) for _ in range(ns)]
+    t = timed(lambda i: _cabi.saturated_cast_transposed(xs[i], scale, E4M3, out_t=outs_t[i]), ns, iters)
+    line("cfg1", "saturated_cast_transposed", x.shape, t, algorithmic_bytes("saturated_cast", w.rows, w.cols), None,
+         note="output [cols, rows]; the reference declares the flag but does not implement it")
+    t = timed(lambda i: _cabi.saturated_cast_transposed(xs[i], scale, E4M3, out_t=outs_t[i], out=outs[i]), ns, iters)
+
+    def cast_twice(i):
+        _cabi.saturated_cast(xs[i], scale, E4M3, out=outs[i])
+        _cabi.saturated_cast(xs[i].t().contiguous(), scale, E4M3, out=outs_t[i])
+
+    t2 = timed(cast_twice, ns, iters)
+    line("cfg1", "saturated_cast_dual (x and x^T from one read)", x.shape, t, x.numel() * 4 + 4, None,
+         note=f"same two outputs by cast + torch transpose + cast: {t2[0] * 1e3:.1f} us")
+    del xs, outs, outs_t
 
     # cfg2: amax + fused dynamic_scaled_quant bf16 [8192,8192], e4m3 and e5m2
     w = workloads.WORKLOADS["cfg2"]
