@@ -268,6 +268,14 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
     t = timed(lambda i: _cabi.mx_fp8_quantize_blocked(xs[i], payload=ps[i], scales=sb[i]), ns, iters)
     line("cfg3", "mx_fp8_quantize_blocked", x.shape, t, algorithmic_bytes("mx_fp8_quantize", w.rows, w.cols), None,
          note="scales written in the MX GEMM's blocked layout (the reference needs a separate to_blocked pass)")
+    t = timed(lambda i: _cabi.mx_quantize(xs[i], E5M2, payload=ps[i].view(E5M2), scales=ss[i]), ns, iters)
+    line("cfg3", "mx_fp8_quantize -> e5m2 payload", x.shape, t, algorithmic_bytes("mx_fp8_quantize", w.rows, w.cols), None,
+         note="the reference accepts fp8_type=e5m2 but writes e4m3; same scale rule with e5m2's largest exponent")
+    p4 = [torch.empty(w.rows, w.cols // 2, dtype=torch.uint8, device=dev) for _ in range(ns)]
+    t = timed(lambda i: _cabi.mx_quantize(xs[i], "e2m1", payload=p4[i], scales=ss[i]), ns, iters)
+    line("cfg3", "mx_fp4_quantize (e2m1, two per byte)", x.shape, t, x.numel() * 2 + x.numel() // 2 + x.numel() // 32, None,
+         note="producer for the operands of the reference's mx_fp4_bf16, which has none")
+    del p4
     pt = [torch.empty(w.cols, w.rows, dtype=E4M3, device=dev) for _ in range(ns)]
     st = [torch.empty(x.numel() // 32, dtype=torch.float8_e8m0fnu, device=dev) for _ in range(ns)]
     dual_bytes = x.numel() * 2 + 2 * (x.numel() + x.numel() // 32)

@@ -81,7 +81,11 @@ def mx_fp8_quantize(
     transpose: bool = False,
     ScalarType: torch.dtype = torch.float8_e4m3fn,
 ) -> tuple[Tensor, Tensor]:
-    """bf16 [M, N] -> (e4m3 payload [M, N], E8M0 scales [M * N / 32]), blocks of 32 along N."""
+    """[M, N] -> (fp8 payload [M, N], E8M0 scales [M * N / 32]), blocks of 32 along N.
+
+    bf16 input with e4m3 payload is the reference's kernel, bit for bit.  fp16 / fp32 inputs and
+    ``ScalarType=torch.float8_e5m2`` (which the reference accepts but computes as bf16 -> e4m3) use
+    the same scale rule with the format's own largest exponent (15 for e5m2)."""
     return ops.mx_fp8_quantize(input, block_size, axis, transpose, ScalarType)
 
 
@@ -107,6 +111,13 @@ def dynamic_scaled_quant_rowwise(inpt: Tensor, dtype: torch.dtype) -> tuple[Tens
 def cast_with_amax(inpt: Tensor, amax_value: Tensor, dtype: torch.dtype) -> tuple[Tensor, Tensor]:
     """The cast phase of ``dynamic_scaled_quant`` for a given device-resident amax; returns (payload, scale)."""
     return ops.cast_with_amax(inpt, amax_value, dtype)
+
+
+def mx_fp4_quantize(input: Tensor) -> tuple[Tensor, Tensor]:
+    """MXFP4: ``(uint8 [M, N/2], E8M0 scales [M * N / 32])``; e2m1 values packed two per byte, the
+    lower index in the low nibble -- the operands of the reference's ``mx_fp4_bf16``, which has no
+    producer kernel there.  Same scale rule as ``mx_fp8_quantize`` with e2m1's largest exponent 2."""
+    return ops.mx_fp4_quantize(input)
 
 
 def mx_fp8_quantize_dual(input: Tensor) -> tuple[Tensor, Tensor, Tensor, Tensor]:
@@ -140,6 +151,7 @@ __all__ = [
     "cast_with_amax",
     "saturated_cast_transposed",
     "saturated_cast_dual",
+    "mx_fp4_quantize",
     "mx_fp8_quantize_dual",
     "mx_fp8_quantize_blocked",
     "check_device_status",

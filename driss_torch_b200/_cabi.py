@@ -37,6 +37,7 @@ SIGNATURES = {
     "dtq_cast_with_amax": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant_rowwise": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
+    "dtq_mx_quantize": ([_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize_dual": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp], _i32),
     "dtq_mx_fp8_quantize_tma": ([_vp, _vp, _vp, _i64, _i64, _vp, _vp], _i32),
     "dtq_mx_blocked_scale_bytes": ([_i64, _i64], _sz),
@@ -233,3 +234,20 @@ def saturated_cast_transposed(x, scale, out_dtype, out_t=None, out=None, both=Fa
                                                scale.data_ptr(), rows, cols, IN_CODE[x.dtype], OUT_CODE[out_dtype],
                                                _stream()), "dtq_saturated_cast_transposed")
     return (out, out_t) if out is not None else out_t
+
+
+MX_IN_CODE = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}
+MX_FMT_CODE = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1, torch.float4_e2m1fn_x2: 2, "e2m1": 2}
+
+
+def mx_quantize(x, elem, payload=None, scales=None):
+    """MX block-32 cast of bf16 / fp16 / fp32 to e4m3 / e5m2 (payload [M, N]) or e2m1 (uint8 [M, N/2])."""
+    rows, cols = x.shape
+    fmt = MX_FMT_CODE[elem]
+    if payload is None:
+        payload = (torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device) if fmt == 2
+                   else torch.empty(rows, cols, dtype=elem, device=x.device))
+    scales = torch.empty(rows * (cols // 32), dtype=torch.float8_e8m0fnu, device=x.device) if scales is None else scales
+    check(load().dtq_mx_quantize(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, MX_IN_CODE[x.dtype], fmt,
+                                 _stream()), "dtq_mx_quantize")
+    return payload, scales

@@ -73,3 +73,10 @@ def saturated_cast_transposed_meta(x: torch.Tensor, scale: torch.Tensor, dtype: 
 def saturated_cast_dual_meta(x: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype):
     return (torch.empty(tuple(x.shape), dtype=dtype, device=x.device),
             torch.empty((x.shape[1], x.shape[0]), dtype=dtype, device=x.device))
+
+
+@register_fake("DrissTorch::mx_fp4_quantize")
+def mx_fp4_quantize_meta(x: torch.Tensor):
+    m, n = x.shape
+    return (torch.empty((m, n // 2), dtype=torch.uint8, device=x.device),
+            torch.empty(m * (n // 32), dtype=torch.float8_e8m0fnu, device=x.device))

@@ -38,6 +38,7 @@ KERNEL_SOURCES = [
     "mx_cast.cu",
     "mx_cast_tma.cu",
     "mx_cast_dual.cu",
+    "mx_cast_formats.cu",
 ]
 
 NVCC_FLAGS = [

@@ -173,30 +173,63 @@ at::Tensor dynamic_scaled_quant(const at::Tensor &input, at::ScalarType dtype) {
   return out;
 }
 
+int mx_in_code(at::ScalarType t) { return t == at::kBFloat16 ? DTQ_BF16 : (t == at::kHalf ? DTQ_F16 : DTQ_F32); }
+
 std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize(at::Tensor input, int64_t block_size, int64_t axis, bool transpose,
                                                    c10::ScalarType fp8_type) {
   TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
   TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
   TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D");
-  // The reference accepts more here and then ignores it (it always reads bf16, blocks of 32 along
-  // the last dimension, and writes e4m3); those combinations are rejected instead of mis-computed.
-  TORCH_CHECK(input.scalar_type() == at::kBFloat16, "Input tensor must be bfloat16, but got ", input.dtype());
+  // The reference accepts fp16 / fp32 inputs and fp8_type = e5m2 and then computes bf16 -> e4m3 on the
+  // bytes it was given; here they are computed with the same scale rule for the asked format.  What
+  // the reference ignores and no kernel here implements is rejected instead of mis-computed.
+  const auto in_type = input.scalar_type();
+  TORCH_CHECK(in_type == at::kBFloat16 || in_type == at::kHalf || in_type == at::kFloat,
+              "Input tensor must be bfloat16, float16 or float32, but got ", input.dtype());
   TORCH_CHECK(block_size == 32, "Block size must be 32, but got ", block_size);
   TORCH_CHECK(axis == 1 || axis == -1, "Blocks run along the last dimension (axis=1), but got axis=", axis);
-  TORCH_CHECK(!transpose, "transpose=True is not supported");
-  TORCH_CHECK(fp8_type == at::kFloat8_e4m3fn, "FP8 type must be Float8_e4m3fn");
+  TORCH_CHECK(!transpose, "transpose=True is not supported (see mx_fp8_quantize_dual)");
+  TORCH_CHECK(fp8_type == at::kFloat8_e4m3fn || fp8_type == at::kFloat8_e5m2,
+              "FP8 type must be Float8_e4m3fn or Float8_e5m2");
   const int64_t m = input.size(0), n = input.size(1);
   TORCH_CHECK(n % 32 == 0, "The last dimension must be a multiple of the block size 32, but got ", n);
   at::Tensor out = at::empty_like(input, input.options().dtype(fp8_type));
   at::Tensor scale = at::empty({m * (n / 32)}, input.options().dtype(at::kFloat8_e8m0fnu));
   c10::cuda::CUDAGuard guard(input.device());
   auto stream = c10::cuda::getCurrentCUDAStream();
-  check_status(dtq_mx_fp8_quantize(input.data_ptr(), out.data_ptr(), scale.data_ptr(), m, n, stream.stream()),
-               "mx_fp8_quantize");
+  if (in_type == at::kBFloat16 && fp8_type == at::kFloat8_e4m3fn) {
+    check_status(dtq_mx_fp8_quantize(input.data_ptr(), out.data_ptr(), scale.data_ptr(), m, n, stream.stream()),
+                 "mx_fp8_quantize");
+  } else {
+    check_status(dtq_mx_quantize(input.data_ptr(), out.data_ptr(), scale.data_ptr(), m, n, mx_in_code(in_type),
+                                 out_code(fp8_type), stream.stream()),
+                 "mx_fp8_quantize");
+  }
   return {out, scale};
 }
 
 // ---- additions ---------------------------------------------------------------------------------------
+
+// MXFP4: e2m1 payload packed two per byte ([M, N/2] uint8, lower index in the low nibble: the operand
+// layout of the reference's mx_fp4_bf16, which reads K as a.size(1) * 2) + E8M0 scales.
+std::tuple<at::Tensor, at::Tensor> mx_fp4_quantize(at::Tensor input) {
+  TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D");
+  const auto in_type = input.scalar_type();
+  TORCH_CHECK(in_type == at::kBFloat16 || in_type == at::kHalf || in_type == at::kFloat,
+              "Input tensor must be bfloat16, float16 or float32, but got ", input.dtype());
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(n % 32 == 0, "The last dimension must be a multiple of the block size 32, but got ", n);
+  at::Tensor out = at::empty({m, n / 2}, input.options().dtype(at::kByte));
+  at::Tensor scale = at::empty({m * (n / 32)}, input.options().dtype(at::kFloat8_e8m0fnu));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_mx_quantize(input.data_ptr(), out.data_ptr(), scale.data_ptr(), m, n, mx_in_code(in_type), DTQ_E2M1,
+                               stream.stream()),
+               "mx_fp4_quantize");
+  return {out, scale};
+}
 
 // MX cast of the input and of its transpose from one read of the input.
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> mx_fp8_quantize_dual(at::Tensor input) {
@@ -303,6 +336,8 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("saturated_cast_transposed", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast_transposed));
   m.def("saturated_cast_dual(Tensor input, Tensor scale, ScalarType dtype) -> (Tensor, Tensor)");
   m.impl("saturated_cast_dual", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast_dual));
+  m.def("mx_fp4_quantize(Tensor input) -> (Tensor, Tensor)");
+  m.impl("mx_fp4_quantize", c10::DispatchKey::CUDA, TORCH_FN(mx_fp4_quantize));
   m.def("mx_fp8_quantize_dual(Tensor input) -> (Tensor, Tensor, Tensor, Tensor)");
   m.impl("mx_fp8_quantize_dual", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_dual));
   m.def("mx_fp8_quantize_blocked(Tensor input) -> (Tensor, Tensor)");

@@ -27,8 +27,10 @@ extern "C" {
 /* element types */
 #define DTQ_BF16 0
 #define DTQ_F32 1
+#define DTQ_F16 2 /* dtq_mx_quantize only */
 #define DTQ_E4M3 0 /* float8_e4m3fn */
 #define DTQ_E5M2 1 /* float8_e5m2   */
+#define DTQ_E2M1 2 /* float4_e2m1fn, two per byte, lower index in the low nibble; dtq_mx_quantize only */
 
 /* status codes */
 #define DTQ_OK 0
@@ -180,6 +182,22 @@ int dtq_dynamic_scaled_quant_rowwise(const void *in, void *out, float *amax_out,
  */
 int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, int64_t rows,
                         int64_t cols, void *stream);
+
+/*
+ * MX block-32 quantisation for every input type and element format the reference's schema names:
+ * in_dtype DTQ_BF16 / DTQ_F16 / DTQ_F32, elem_format DTQ_E4M3 / DTQ_E5M2 / DTQ_E2M1.
+ * The reference accepts fp8_type = e5m2 and fp16 / fp32 inputs but computes bf16 -> e4m3 on the
+ * bytes it was given (src/mx_cast.cu:148,175-184,204), and has no producer for the MXFP4 operands
+ * of mx_fp4_bf16 (src/mx_fp8_bf16.cu:243-271).  Scale rule: the reference's (src/mx_cast.cu:44-86)
+ * with its constant 8 replaced by the format's largest exponent (8 / 15 / 2):
+ * biased = clamp(max_i ceil(log2|x_i|) - EMAX + 127, 0, 255), payload = cvt_satfinite(x * 2^(127-biased)),
+ * scale byte = biased; blocks that are all zero or tiny give scale byte 0 and NaN (fp8) or +6 (e2m1)
+ * payloads, as in the reference.  For DTQ_BF16 / DTQ_E4M3 the result equals dtq_mx_fp8_quantize's.
+ * payload: rows*cols bytes (fp8) or rows*cols/2 bytes (e2m1); scales: rows*cols/32 bytes, row-major.
+ * cols % 32 == 0; `in` 16-byte aligned, `payload` aligned to 8 bytes.
+ */
+int dtq_mx_quantize(const void *in, void *payload, void *scales_e8m0, int64_t rows, int64_t cols, int in_dtype,
+                    int elem_format, void *stream);
 
 /*
  * Both orientations from one read of a contiguous bf16 [rows, cols] matrix (rows % 32 == 0,

@@ -10,6 +10,7 @@
 #include <cstring>
 
 #include <cuda_bf16.h>
+#include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
 static inline __nv_fp8_interpretation_t kind_of(int k) { return k == 0 ? __NV_E4M3 : __NV_E5M2; }
@@ -41,6 +42,15 @@ uint16_t hdr_bf16_mul(uint16_t a, uint16_t b) {
   uint16_t u;
   std::memcpy(&u, &p, 2);
   return u;
+}
+
+uint8_t hdr_f32_to_fp4(float f) { return __nv_cvt_float_to_fp4(f, __NV_E2M1, cudaRoundNearest); }
+
+uint8_t hdr_f32x2_to_fp4x2(float lo, float hi) {
+  float2 v;
+  v.x = lo;
+  v.y = hi;
+  return static_cast<uint8_t>(__nv_cvt_float2_to_fp4x2(v, __NV_E2M1, cudaRoundNearest));
 }
 
 uint8_t hdr_f32_to_e8m0(float f) {

@@ -236,6 +236,78 @@ void oracle_mx_fp8_quantize(const uint16_t *in, uint8_t *payload, uint8_t *scale
   }
 }
 
+/* ---- MX block-32 quantisation for the other element formats and input types.
+ * The reference's scale rule (src/mx_cast.cu:44-86) with its constant 8 (the
+ * exponent of e4m3's largest power of two, :72) replaced by the element
+ * format's: 15 for e5m2, 2 for e2m1.  No reference kernel computes these (the
+ * reference accepts the arguments and runs the bf16 -> e4m3 arithmetic,
+ * :148,175-184,204), so no reference test pins them; the conversions are pinned
+ * against the CUDA toolkit's header functions, and in_dtype bf16 / e4m3 must
+ * reproduce oracle_mx_fp8_quantize. */
+static float f16_to_f32(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  const int be = (h >> 10) & 0x1F;
+  const uint32_t man = h & 0x3FFu;
+  if (be == 0x1F) return bits_f32(sign | 0x7F800000u | (man << 13));
+  if (be == 0) return (sign ? -1.0f : 1.0f) * (float)ldexp((double)man, -24);
+  return bits_f32(sign | ((uint32_t)(be - 15 + 127) << 23) | (man << 13));
+}
+
+/* cvt.rn.satfinite.e2m1x2.f32 per element (what __nv_cvt_float_to_fp4 does): values
+ * 0, 0.5, 1, 1.5, 2, 3, 4, 6 with a sign bit; nearest-even; above 6 (infinities too)
+ * -> 6; NaN -> +6 (the format has no NaN). */
+static uint8_t f32_to_e2m1_sat(float x) {
+  if (isnan(x)) return 0x7;
+  const uint8_t sign = signbit(x) ? 0x8 : 0;
+  const double a = fabs((double)x);
+  if (a > 6.0) return sign | 0x7;
+  if (a == 0.0) return sign;
+  int e;
+  (void)frexp(a, &e);
+  int fl = e - 1;
+  if (fl < 0) fl = 0; /* smallest normal exponent: 2^0; below it the step is 0.5 */
+  double q = ldexp(1.0, fl - 1);
+  long n = (long)rint(a / q); /* in [0, 4] */
+  if (n == 4) { n = 2; fl += 1; }
+  uint8_t code = (n < 2) ? (uint8_t)n : (uint8_t)(((fl + 1) << 1) | (n - 2));
+  return sign | code;
+}
+uint8_t oracle_f32_to_e2m1(float f) { return f32_to_e2m1_sat(f); }
+float oracle_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+
+/* in_dtype: 0 bf16, 1 fp32, 2 fp16.  fmt: 0 e4m3, 1 e5m2, 2 e2m1 (packed two per
+ * byte, lower index in the low nibble). */
+void oracle_mx_quantize(const void *in, int in_dtype, uint8_t *payload, uint8_t *scales, int64_t nblocks, int fmt) {
+  const int emax = fmt == 0 ? 8 : (fmt == 1 ? 15 : 2);
+#pragma omp parallel for schedule(static)
+  for (int64_t b = 0; b < nblocks; ++b) {
+    float x[32];
+    int E = -1000;
+    for (int i = 0; i < 32; ++i) {
+      const int64_t j = b * 32 + i;
+      x[i] = in_dtype == 0 ? bf16_to_f32(((const uint16_t *)in)[j])
+           : in_dtype == 1 ? ((const float *)in)[j] : f16_to_f32(((const uint16_t *)in)[j]);
+      int e = mx_ceil_log2(fabsf(x[i]));
+      if (e > E) E = e;
+    }
+    int biased = E - emax + 127;
+    if (biased < 0) biased = 0;
+    if (biased > 255) biased = 255;
+    const float inv = (biased == 0) ? INFINITY : (biased == 255 ? 0.0f : (float)ldexp(1.0, 127 - biased));
+    for (int i = 0; i < 32; ++i) {
+      volatile float p = x[i] * inv; /* one fp32 rounding (exact unless the product is subnormal) */
+      if (fmt == 2) {
+        const uint8_t nib = f32_to_e2m1_sat(p);
+        uint8_t *dst = payload + (b * 32 + i) / 2;
+        if (i & 1) *dst = (uint8_t)(*dst | (nib << 4)); else *dst = nib;
+      } else {
+        payload[b * 32 + i] = f32_to_fp8_sat(p, fmt);
+      }
+    }
+    scales[b] = (uint8_t)(biased > 254 ? 254 : biased);
+  }
+}
+
 /* Single-value entry points for exhaustive conversion checks. */
 uint16_t oracle_f32_to_bf16(float f) { return f64_to_bf16_rne((double)f); }
 uint16_t oracle_bf16_mul(uint16_t a, uint16_t b) {

@@ -67,6 +67,12 @@ def lib() -> C.CDLL:
         L.oracle_dynamic_scaled_quant_rowwise.restype = None
         L.oracle_mx_fp8_quantize.argtypes = [vp, vp, vp, i64]
         L.oracle_mx_fp8_quantize.restype = None
+        L.oracle_mx_quantize.argtypes = [vp, i32, vp, vp, i64, i32]
+        L.oracle_mx_quantize.restype = None
+        L.oracle_f32_to_e2m1.argtypes = [f32]
+        L.oracle_f32_to_e2m1.restype = C.c_uint8
+        L.oracle_f16_to_f32.argtypes = [C.c_uint16]
+        L.oracle_f16_to_f32.restype = f32
         L.oracle_f32_to_fp8_array.argtypes = [vp, vp, i64, i32]
         L.oracle_bf16_mul_array.argtypes = [vp, C.c_uint16, vp, i64]
         L.oracle_f32_to_bf16_array.argtypes = [vp, vp, i64]
@@ -85,6 +91,10 @@ def header_lib() -> C.CDLL:
         H.hdr_f32_to_fp8_array.argtypes = [vp, vp, i64, i32]
         H.hdr_bf16_mul_array.argtypes = [vp, C.c_uint16, vp, i64]
         H.hdr_f32_to_bf16_array.argtypes = [vp, vp, i64]
+        H.hdr_f32_to_fp4.argtypes = [C.c_float]
+        H.hdr_f32_to_fp4.restype = C.c_uint8
+        H.hdr_f32x2_to_fp4x2.argtypes = [C.c_float, C.c_float]
+        H.hdr_f32x2_to_fp4x2.restype = C.c_uint8
         H.hdr_f32_to_e8m0.argtypes = [C.c_float]
         H.hdr_f32_to_e8m0.restype = C.c_uint8
         H.hdr_bf16_to_fp8.argtypes = [C.c_uint16, i32]
@@ -165,6 +175,22 @@ def mx_fp8_quantize(x: torch.Tensor):
     scales = torch.empty(x.numel() // 32, dtype=torch.uint8)
     lib().oracle_mx_fp8_quantize(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), x.numel() // 32)
     return payload.view(torch.float8_e4m3fn), scales.view(torch.float8_e8m0fnu)
+
+
+MX_IN = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}
+MX_FMT = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1, "e2m1": 2, torch.float4_e2m1fn_x2: 2}
+
+
+def mx_quantize(x: torch.Tensor, elem):
+    """[M, N] bf16 / fp16 / fp32 with N % 32 == 0 -> (payload, e8m0 scales [M * N / 32]); ``elem`` an fp8
+    dtype (payload [M, N]) or "e2m1" (payload uint8 [M, N / 2], lower index in the low nibble)."""
+    assert x.device.type == "cpu" and x.is_contiguous() and x.dtype in MX_IN and x.numel() % 32 == 0
+    fmt = MX_FMT[elem]
+    rows, cols = x.shape
+    payload = torch.zeros((rows, cols // 2) if fmt == 2 else (rows, cols), dtype=torch.uint8)
+    scales = torch.empty(x.numel() // 32, dtype=torch.uint8)
+    lib().oracle_mx_quantize(x.data_ptr(), MX_IN[x.dtype], payload.data_ptr(), scales.data_ptr(), x.numel() // 32, fmt)
+    return (payload if fmt == 2 else payload.view(elem)), scales.view(torch.float8_e8m0fnu)
 
 
 # ---- conversion tables for the exhaustive pins -------------------------------------------------

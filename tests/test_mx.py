@@ -126,11 +126,13 @@ def test_errors_and_compile():
 
     a = torch.rand(128, 64, device="cuda").to(torch.bfloat16)
     for bad in (
-        lambda: dt.mx_fp8_quantize(a.float()),
+        lambda: dt.mx_fp8_quantize(a.double()),
         lambda: dt.mx_fp8_quantize(a, block_size=16),
         lambda: dt.mx_fp8_quantize(a, axis=0),
         lambda: dt.mx_fp8_quantize(a, transpose=True),
-        lambda: dt.mx_fp8_quantize(a, ScalarType=torch.float8_e5m2),
+        lambda: dt.mx_fp8_quantize(a, ScalarType=torch.float16),
+        lambda: dt.mx_fp4_quantize(a[:, :48]),
+        lambda: dt.mx_fp4_quantize(a.double()),
         lambda: dt.mx_fp8_quantize(a[:, :48]),
         lambda: dt.mx_fp8_quantize(a.t()),
         lambda: dt.mx_fp8_quantize(a.view(-1)),
@@ -273,3 +275,99 @@ def test_dual_on_every_bf16_pattern_and_degenerate_blocks_and_errors():
         dt.mx_fp8_quantize_dual(a)  # rows not a multiple of 32
     with pytest.raises(RuntimeError):
         dt.mx_fp8_quantize_dual(torch.zeros(64, 64, device="cuda"))  # not bf16
+
+
+# ---- the other element formats and input types ----------------------------------------------------------
+
+FORMATS = [torch.float8_e4m3fn, torch.float8_e5m2, "e2m1"]
+MX_INPUTS = [torch.bfloat16, torch.float16, torch.float32]
+
+
+def _mx_input(rows, cols, in_dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    mag = torch.exp(3.0 * torch.randn(rows, cols, generator=g))
+    sign = torch.where(torch.rand(rows, cols, generator=g) < 0.5, -1.0, 1.0)
+    x = torch.where(torch.rand(rows, cols, generator=g) < 0.01, torch.zeros(()), mag * sign)
+    return x.to(in_dtype)
+
+
+def _assert_payload(got, want, elem, what):
+    if elem == "e2m1":
+        assert got.dtype == torch.uint8 and torch.equal(got.cpu(), want), what
+    else:
+        assert_fp8_equal(got, want, elem, what)
+
+
+@pytest.mark.parametrize("elem", FORMATS, ids=str)
+@pytest.mark.parametrize("in_dtype", MX_INPUTS, ids=str)
+@pytest.mark.parametrize("shape", [(128, 32), (8, 64), (256, 8192), (33, 96), (2048, 2048)], ids=lambda s: f"{s[0]}x{s[1]}")
+def test_mx_formats_against_the_oracle(shape, in_dtype, elem):
+    from driss_torch_b200 import _cabi
+
+    a = _mx_input(shape[0], shape[1], in_dtype, seed=shape[0] + 7 * shape[1])
+    want_p, want_s = qo.mx_quantize(a, elem)
+    p, s = _cabi.mx_quantize(a.cuda(), elem)
+    _assert_payload(p, want_p, elem, "payload")
+    assert torch.equal(as_bytes(s), as_bytes(want_s)), "scales"
+
+
+@pytest.mark.parametrize("elem", FORMATS, ids=str)
+def test_mx_formats_on_every_16_bit_pattern_and_degenerate_blocks(elem):
+    from driss_torch_b200 import _cabi
+
+    g = torch.Generator().manual_seed(11)
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    shuffled = bits[torch.randperm(65536, generator=g)]
+    for in_dtype in (torch.bfloat16, torch.float16):
+        for b in (bits, shuffled):
+            a = b.view(in_dtype).view(64, 1024)  # sorted: blocks of near-equal magnitude; shuffled: mixed blocks
+            want_p, want_s = qo.mx_quantize(a, elem)
+            p, s = _cabi.mx_quantize(a.cuda(), elem)
+            _assert_payload(p, want_p, elem, f"{in_dtype} payload")
+            assert torch.equal(as_bytes(s), as_bytes(want_s))
+    # fp32: every exponent with a few mantissas, plus zero / subnormal / tiny / huge blocks
+    exps = torch.arange(256, dtype=torch.int32).repeat_interleave(32)
+    mant = torch.tensor([0, 1, 0x400000, 0x7FFFFF], dtype=torch.int32).repeat(2048)
+    sign = (torch.arange(8192, dtype=torch.int32) % 3 == 0).to(torch.int32) << 31
+    a = ((exps << 23) | mant | sign).view(torch.float32).view(64, 128)
+    a2 = a.clone().view(-1)[torch.randperm(8192, generator=g)].view(64, 128)
+    z = torch.zeros(32, 64)
+    z[8:16] = 1e-38
+    z[16:24, ::7] = 3e38
+    for x in (a, a2, z):
+        want_p, want_s = qo.mx_quantize(x.contiguous(), elem)
+        p, s = _cabi.mx_quantize(x.contiguous().cuda(), elem)
+        _assert_payload(p, want_p, elem, "fp32 payload")
+        assert torch.equal(as_bytes(s), as_bytes(want_s))
+
+
+def test_mx_formats_bf16_e4m3_is_the_reference_kernel_and_ops():
+    import driss_torch_b200 as dt
+    from driss_torch_b200 import _cabi
+
+    a = workloads.make_cfg3(rows=512, cols=1024).cuda()
+    p0, s0 = _cabi.mx_fp8_quantize(a)
+    p1, s1 = _cabi.mx_quantize(a, E4M3)
+    assert torch.equal(as_bytes(p0), as_bytes(p1)) and torch.equal(as_bytes(s0), as_bytes(s1))
+    # the ops: e5m2 payload, fp32 / fp16 input, fp4
+    p, s = dt.mx_fp8_quantize(a, ScalarType=torch.float8_e5m2)
+    want_p, want_s = qo.mx_quantize(a.cpu(), torch.float8_e5m2)
+    assert p.dtype == torch.float8_e5m2 and p.shape == a.shape
+    assert_fp8_equal(p, want_p, torch.float8_e5m2, "e5m2 op")
+    assert torch.equal(as_bytes(s), as_bytes(want_s))
+    for in_dtype in (torch.float32, torch.float16):
+        x = a.to(in_dtype)
+        p, s = dt.mx_fp8_quantize(x)
+        want_p, want_s = qo.mx_quantize(x.cpu(), E4M3)
+        assert_fp8_equal(p, want_p, E4M3, f"{in_dtype} op")
+        assert torch.equal(as_bytes(s), as_bytes(want_s))
+    p4, s4 = dt.mx_fp4_quantize(a)
+    want_p, want_s = qo.mx_quantize(a.cpu(), "e2m1")
+    assert p4.dtype == torch.uint8 and p4.shape == (512, 512) and torch.equal(p4.cpu(), want_p)
+    assert torch.equal(as_bytes(s4), as_bytes(want_s))
+    # dequantised fp4 is within half a step of the block scale: |x - q| <= 2^(E-2) * 1 (largest step is 2)
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6])
+    q = torch.stack([lut[(p4.cpu() & 0xF).long()], lut[(p4.cpu() >> 4).long()]], dim=-1).view(512, 1024)
+    scale = torch.exp2(as_bytes(s4).cpu().float() - 127).view(512, 32, 1)
+    err = (q.view(512, 32, 32) * scale - a.cpu().float().view(512, 32, 32)).abs()
+    assert (err <= scale * 1.0 + 1e-30).all()

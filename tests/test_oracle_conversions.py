@@ -121,3 +121,41 @@ def test_bf16_to_fp8_header_path_equals_via_fp32():
             if np.isnan(vals[b]):
                 continue
             assert H.hdr_bf16_to_fp8(int(bits[b]), kind) == mine[b]
+
+
+def test_e2m1_conversion_matches_the_toolkit_header():
+    """The plain-C e2m1 rounding against __nv_cvt_float_to_fp4 (host path of cuda_fp4.hpp), on every
+    bf16-valued float, on a fine sweep around the representable values, and the packing order."""
+    L, H = qo.lib(), qo.header_lib()
+    vals = [float(v) for v in torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).float()]
+    vals += [k / 64.0 for k in range(-512, 513)] + [float("inf"), float("-inf"), 1e-45, -1e-45, 6.0000005, 5.9999995]
+    for v in vals:
+        if v != v:
+            continue  # NaN: compared below
+        assert L.oracle_f32_to_e2m1(v) == H.hdr_f32_to_fp4(v), v
+    assert L.oracle_f32_to_e2m1(float("nan")) == H.hdr_f32_to_fp4(float("nan")) == 0x7
+    assert H.hdr_f32x2_to_fp4x2(1.0, -6.0) == 0xF2  # first element in the low nibble
+
+
+def test_f16_widening_and_mx_formats_reduce_to_the_reference_case():
+    L = qo.lib()
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    want = bits.view(torch.float16).float()
+    got = torch.tensor([L.oracle_f16_to_f32(int(b) & 0xFFFF) for b in bits.tolist()])
+    assert torch.equal(got.view(torch.int32)[~want.isnan()], want.view(torch.int32)[~want.isnan()])
+    assert got[want.isnan()].isnan().all()
+    # bf16 input, e4m3 payload: the generalised function is the reference restatement
+    g = torch.Generator().manual_seed(3)
+    a = bits[torch.randperm(65536, generator=g)].view(torch.bfloat16).view(64, 1024)
+    p0, s0 = qo.mx_fp8_quantize(a)
+    p1, s1 = qo.mx_quantize(a, torch.float8_e4m3fn)
+    assert torch.equal(p0.view(torch.uint8), p1.view(torch.uint8)) and torch.equal(s0.view(torch.uint8), s1.view(torch.uint8))
+    # fp32 input that is bf16-valued gives the same bytes as the bf16 input; e5m2 / e2m1 scale bytes differ
+    # from e4m3's by the difference of the formats' largest exponents wherever no clamp acts
+    p2, s2 = qo.mx_quantize(a.float(), torch.float8_e4m3fn)
+    assert torch.equal(p1.view(torch.uint8), p2.view(torch.uint8)) and torch.equal(s1.view(torch.uint8), s2.view(torch.uint8))
+    _, s5 = qo.mx_quantize(a, torch.float8_e5m2)
+    _, s4 = qo.mx_quantize(a, "e2m1")
+    e4, e5, e2 = (t.view(torch.uint8).int() for t in (s1, s5, s4))
+    ok = (e4 > 7) & (e4 < 249)
+    assert torch.equal(e5[ok], e4[ok] - 7) and torch.equal(e2[ok], e4[ok] + 6)
