@@ -409,6 +409,9 @@ def main():
                     help="N > 1: how the per-GPU maxima meet: inside the one fused launch over NVLink peer memory (p2p), "
                          "or an NCCL all-reduce between an amax launch and a cast launch (nccl); auto = p2p for shards up to 1.5 GiB "
                          "(measured: the single persistent launch wins there, two stream launches win above)")
+    ap.add_argument("--compose", choices=["shared-read", "separate"], default="shared-read",
+                    help="shared-read: the MX cast also delivers the amax (and exchanges it), then the cast: two reads "
+                         "of the input; separate: amax, cast and MX cast as independent ops: three reads")
     ap.add_argument("--ops-table-only", action="store_true", help="only the cfg1-cfg4 per-op table (profiling captures)")
     ap.add_argument("--op-iters", type=int, default=0, help="timed launches per op in the per-op table (default max(20, steps))")
     args = ap.parse_args()
@@ -461,7 +464,9 @@ def main():
     if world > 1:
         exchange = args.exchange
         if exchange == "auto":
-            exchange = "p2p" if rows_local * COLS * 2 <= 1.5 * 2**30 else "nccl"
+            # the single cooperative launch of the separate composition pays off only while part of the shard
+            # stays on chip; the shared-read composition has no such limit
+            exchange = "p2p" if args.compose == "shared-read" or rows_local * COLS * 2 <= 1.5 * 2**30 else "nccl"
         if exchange == "p2p":
             try:
                 from driss_torch_b200.sharded import ShardedQuantizer
@@ -474,7 +479,13 @@ def main():
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
             if ok.item() == 0:
                 exchange = "nccl"
-    if exchange == "p2p":
+    shared = args.compose == "shared-read"
+    if shared:
+        first = {"p2p": "mx_fp8_quantize_amax_p2p (MX cast + amax; its one-warp finishing launch exchanges over NVLink)"}.get(
+            exchange, "mx_fp8_quantize_amax (MX cast + amax, with its one-warp finishing launch)")
+        names = [first] + (["all_reduce(max) [NCCL]"] if exchange == "nccl" else []) + ["cast_with_amax"]
+        my_launches_per_step = 3
+    elif exchange == "p2p":
         names = ["dynamic_scaled_quant_p2p (amax + NVLink exchange + cast, one launch)", "mx_fp8_quantize"]
         my_launches_per_step = 2
     elif exchange == "nccl":
@@ -495,6 +506,19 @@ def main():
                 marks.append(e)
 
         mark()
+        if shared:
+            epoch[0] += 1
+            _cabi.mx_fp8_quantize_amax(x, payload=mx_payload, scales=mx_scales, amax_out=amax, ws=ws,
+                                       peer_ptrs=peer_ptrs if exchange == "p2p" else None, rank=rank, epoch=epoch[0])
+            mark()
+            if exchange == "nccl":
+                dist.all_reduce(amax, op=dist.ReduceOp.MAX)
+                mark()
+            _cabi.cast_with_amax(x, amax, E4M3, out=payload, scale_out=scale)
+            mark()
+            if events is not None:
+                events.append(marks)
+            return
         if exchange == "p2p":
             epoch[0] += 1
             _cabi.dynamic_scaled_quant_p2p(x, E4M3, peer_ptrs, rank, epoch[0], out=payload, amax_out=amax,
@@ -568,7 +592,8 @@ def main():
         if "NCCL" in name:
             kernels.append({"kernel": name, "ms": round(ms, 4), "bytes": 4})
             continue
-        op = "dynamic_scaled_quant" if name.startswith("dynamic_scaled_quant_p2p") else name
+        op = ("dynamic_scaled_quant" if name.startswith("dynamic_scaled_quant_p2p")
+              else "mx_fp8_quantize" if name.startswith("mx_fp8_quantize") else name)
         nbytes = algorithmic_bytes(op, rows_local, COLS)
         gbs = nbytes / (ms * 1e-3) / 1e9
         k = {"kernel": name, "ms": round(ms, 4), "algorithmic_bytes_per_launch": nbytes, "GBps": round(gbs, 1),
@@ -580,7 +605,17 @@ def main():
                 "unit": "GB/s", "frac": round(dominant["GBps"] / peak, 4), "peak_kind": f"of {peak_kind}",
                 "traffic": None, "frac_of_nominal_8TBps": dominant["frac_of_nominal_8TBps"]}
     tw_ms = sum(k["ms"] for k in mine if not k["kernel"].startswith("mx"))
-    roofline["note"] = ("tensor-wise quant (amax and cast, as one or two launches): together %.4f ms for %d compulsory bytes N*(2+1) "
+    if shared:
+        step_ms = sum(k["ms"] for k in mine)
+        roofline["note"] = ("shared-read composition: the MX cast delivers the amax, so the step reads the input twice, "
+                            "N*(2+1+1/32) + N*(2+1) = %d bytes moved per GPU in %.4f ms (%.1f GB/s); the ops' own "
+                            "algorithmic bytes (what `value` counts) add up to the same figure, since the amax costs no traffic" % (
+                                algorithmic_bytes("mx_fp8_quantize", rows_local, COLS)
+                                + algorithmic_bytes("cast_with_amax", rows_local, COLS), step_ms,
+                                (algorithmic_bytes("mx_fp8_quantize", rows_local, COLS)
+                                 + algorithmic_bytes("cast_with_amax", rows_local, COLS)) / (step_ms * 1e-3) / 1e9))
+    else:
+        roofline["note"] = ("tensor-wise quant (amax and cast, as one or two launches): together %.4f ms for %d compulsory bytes N*(2+1) "
                         "(%.1f GB/s) and N*(2*2+1) moved (%.1f GB/s); the global-max dependency forces the second read "
                         "of an input this much larger than L2" % (
                             tw_ms, algorithmic_bytes("dynamic_scaled_quant", rows_local, COLS),
@@ -592,7 +627,7 @@ def main():
     n_local = rows_local * COLS
     if dominant["kernel"].startswith("dynamic_scaled_quant_p2p"):
         roofline["traffic"] = int(max(3 * n_local, 5 * n_local - 138e6))
-    elif dominant["kernel"] == "mx_fp8_quantize":
+    elif dominant["kernel"].startswith("mx_fp8_quantize"):
         roofline["traffic"] = int(3.03125 * n_local - min(54e6, 0.25 * n_local))
     elif dominant["kernel"] == "cast_with_amax":
         roofline["traffic"] = int(3 * n_local - min(34e6, 0.25 * n_local))
@@ -654,6 +689,7 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"cfg5: bf16 [{total_rows},{COLS}] row-sharded over {world} GPU(s); tensor-wise e4m3 "
                                    "quant (amax -> max all-reduce -> cast) + MX block-32 cast",
+                       "composition": args.compose,
                        "rows_per_gpu": rows_local, "exchange": exchange, "l2": "inputs larger than L2 (no flush needed)",
                        "timing": "CUDA events on the launch stream, max over ranks"},
             "bytes_per_step": tw_bytes + mx_bytes,

@@ -113,6 +113,12 @@ def cast_with_amax(inpt: Tensor, amax_value: Tensor, dtype: torch.dtype) -> tupl
     return ops.cast_with_amax(inpt, amax_value, dtype)
 
 
+def mx_fp8_quantize_with_amax(input: Tensor) -> tuple[Tensor, Tensor, Tensor]:
+    """``mx_fp8_quantize(x)`` plus ``max(0, amax(x))`` (fp32 [1]) from the same read of ``x``: with
+    ``cast_with_amax`` behind it, a tensor is quantised both tensor-wise and MX in two reads instead of three."""
+    return ops.mx_fp8_quantize_with_amax(input)
+
+
 def mx_fp4_quantize(input: Tensor) -> tuple[Tensor, Tensor]:
     """MXFP4: ``(uint8 [M, N/2], E8M0 scales [M * N / 32])``; e2m1 values packed two per byte, the
     lower index in the low nibble -- the operands of the reference's ``mx_fp4_bf16``, which has no
@@ -151,6 +157,7 @@ __all__ = [
     "cast_with_amax",
     "saturated_cast_transposed",
     "saturated_cast_dual",
+    "mx_fp8_quantize_with_amax",
     "mx_fp4_quantize",
     "mx_fp8_quantize_dual",
     "mx_fp8_quantize_blocked",

@@ -37,6 +37,8 @@ SIGNATURES = {
     "dtq_cast_with_amax": ([_vp, _vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_dynamic_scaled_quant_rowwise": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
+    "dtq_mx_fp8_quantize_amax": ([_vp, _vp, _vp, _vp, _i64, _i64, _vp, _sz, _vp], _i32),
+    "dtq_mx_fp8_quantize_amax_p2p": ([_vp, _vp, _vp, _vp, _i64, _i64, _vp, _sz, _vp, _i32, _i32, C.c_uint32, C.c_uint32, _vp], _i32),
     "dtq_mx_quantize": ([_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize_dual": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp], _i32),
     "dtq_mx_fp8_quantize_tma": ([_vp, _vp, _vp, _i64, _i64, _vp, _vp], _i32),
@@ -251,3 +253,24 @@ def mx_quantize(x, elem, payload=None, scales=None):
     check(load().dtq_mx_quantize(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, MX_IN_CODE[x.dtype], fmt,
                                  _stream()), "dtq_mx_quantize")
     return payload, scales
+
+
+def mx_fp8_quantize_amax(x, payload=None, scales=None, amax_out=None, ws=None, peer_ptrs=None, rank=0, epoch=0,
+                         spin_limit=0):
+    """MX cast + the tensor's amax (>= 0) from one read; with ``peer_ptrs`` the amax is exchanged with the
+    other ranks of a row-sharded tensor inside the launch."""
+    rows, cols = x.shape
+    payload = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device) if payload is None else payload
+    scales = torch.empty(rows * (cols // 32), dtype=torch.float8_e8m0fnu, device=x.device) if scales is None else scales
+    amax_out = torch.empty(1, dtype=torch.float32, device=x.device) if amax_out is None else amax_out
+    ws = workspace(x.device) if ws is None else ws
+    if peer_ptrs is None:
+        check(load().dtq_mx_fp8_quantize_amax(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), amax_out.data_ptr(),
+                                              rows, cols, ws.data_ptr(), ws.numel(), _stream()), "dtq_mx_fp8_quantize_amax")
+    else:
+        world = len(peer_ptrs)
+        ptrs = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
+        check(load().dtq_mx_fp8_quantize_amax_p2p(x.data_ptr(), payload.data_ptr(), scales.data_ptr(),
+                                                  amax_out.data_ptr(), rows, cols, ws.data_ptr(), ws.numel(), ptrs, rank,
+                                                  world, epoch, spin_limit, _stream()), "dtq_mx_fp8_quantize_amax_p2p")
+    return payload, scales, amax_out

@@ -80,3 +80,11 @@ def mx_fp4_quantize_meta(x: torch.Tensor):
     m, n = x.shape
     return (torch.empty((m, n // 2), dtype=torch.uint8, device=x.device),
             torch.empty(m * (n // 32), dtype=torch.float8_e8m0fnu, device=x.device))
+
+
+@register_fake("DrissTorch::mx_fp8_quantize_with_amax")
+def mx_fp8_quantize_with_amax_meta(x: torch.Tensor):
+    m, n = x.shape
+    return (torch.empty_like(x, dtype=torch.float8_e4m3fn),
+            torch.empty(m * (n // 32), dtype=torch.float8_e8m0fnu, device=x.device),
+            torch.empty(1, dtype=torch.float32, device=x.device))

@@ -39,6 +39,7 @@ KERNEL_SOURCES = [
     "mx_cast_tma.cu",
     "mx_cast_dual.cu",
     "mx_cast_formats.cu",
+    "mx_cast_amax.cu",
 ]
 
 NVCC_FLAGS = [

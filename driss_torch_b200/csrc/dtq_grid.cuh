@@ -116,6 +116,35 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
   return v;
 }
 
+// The exchange alone, for a kernel without a grid barrier: run by all 32 lanes of one warp of one
+// block per rank.  Stores {epoch, local_bits} into this rank's slot on every rank and returns the
+// maximum of all ranks' values for this epoch (unsigned order); *ok is false if a peer's value did
+// not arrive within the spin limit.
+__device__ __forceinline__ unsigned int peer_exchange_max(const PeerExchange &px, unsigned int local_bits, bool *ok) {
+  const int lane = threadIdx.x & 31;
+  const int parity = px.epoch & 1u;
+  unsigned int value = 0;
+  bool mine_ok = true;
+  if (lane < px.world) {
+    st_release_sys(px.buffer[lane] + parity * kMaxPeers + px.rank,
+                   (static_cast<unsigned long long>(px.epoch) << 32) | local_bits);
+    const unsigned long long *mine = px.buffer[px.rank] + parity * kMaxPeers + lane;
+    unsigned int spins = 0;
+    unsigned long long v = ld_acquire_sys(mine);
+    while (static_cast<unsigned int>(v >> 32) != px.epoch) {
+      if (++spins > px.spin_limit) {
+        mine_ok = false;
+        break;
+      }
+      __nanosleep(40);
+      v = ld_acquire_sys(mine);
+    }
+    value = static_cast<unsigned int>(v);
+  }
+  *ok = __all_sync(0xFFFFFFFFu, mine_ok);
+  return __reduce_max_sync(0xFFFFFFFFu, value);
+}
+
 // As grid_max_barrier, but the value every block leaves with is the maximum over all ranks.
 // Waiting blocks watch the local count reach gridDim.x + 1: the last arriver adds the extra one
 // after the exchange, when ws->amax holds the global value.

@@ -22,7 +22,11 @@ struct alignas(256) Workspace {
   // per parity of `generation`; a launch uses the pair of its parity and clears the other.
   unsigned int bar_count[2];
   unsigned int bar_max[2];
-  unsigned int pad[56];
+  // Running maxima of kernels whose blocks fold their value into a few words (atomicMax, block b
+  // into word b % 32) instead of publishing partials; a one-warp finishing launch takes them and
+  // leaves zeros behind.
+  unsigned int slot_max[32];
+  unsigned int pad[24];
   float partials[kMaxGridBlocks];
 };
 

@@ -210,6 +210,26 @@ std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize(at::Tensor input, int64_t blo
 
 // ---- additions ---------------------------------------------------------------------------------------
 
+// MX cast + the tensor's amax (>= 0) from one read of the input: the first half of a step that also
+// quantises the tensor tensor-wise (follow with cast_with_amax).
+std::tuple<at::Tensor, at::Tensor, at::Tensor> mx_fp8_quantize_with_amax(at::Tensor input) {
+  TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D");
+  TORCH_CHECK(input.scalar_type() == at::kBFloat16, "Input tensor must be bfloat16, but got ", input.dtype());
+  const int64_t m = input.size(0), n = input.size(1);
+  TORCH_CHECK(n % 32 == 0, "The last dimension must be a multiple of the block size 32, but got ", n);
+  at::Tensor out = at::empty_like(input, input.options().dtype(at::kFloat8_e4m3fn));
+  at::Tensor scale = at::empty({m * (n / 32)}, input.options().dtype(at::kFloat8_e8m0fnu));
+  at::Tensor amax = at::empty({1}, input.options().dtype(at::kFloat));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_mx_fp8_quantize_amax(input.data_ptr(), out.data_ptr(), scale.data_ptr(), amax.data_ptr<float>(), m, n,
+                                        workspaces().get(stream), dtq_workspace_bytes(), stream.stream()),
+               "mx_fp8_quantize_with_amax");
+  return {out, scale, amax};
+}
+
 // MXFP4: e2m1 payload packed two per byte ([M, N/2] uint8, lower index in the low nibble: the operand
 // layout of the reference's mx_fp4_bf16, which reads K as a.size(1) * 2) + E8M0 scales.
 std::tuple<at::Tensor, at::Tensor> mx_fp4_quantize(at::Tensor input) {
@@ -336,6 +356,8 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("saturated_cast_transposed", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast_transposed));
   m.def("saturated_cast_dual(Tensor input, Tensor scale, ScalarType dtype) -> (Tensor, Tensor)");
   m.impl("saturated_cast_dual", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast_dual));
+  m.def("mx_fp8_quantize_with_amax(Tensor input) -> (Tensor, Tensor, Tensor)");
+  m.impl("mx_fp8_quantize_with_amax", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_with_amax));
   m.def("mx_fp4_quantize(Tensor input) -> (Tensor, Tensor)");
   m.impl("mx_fp4_quantize", c10::DispatchKey::CUDA, TORCH_FN(mx_fp4_quantize));
   m.def("mx_fp8_quantize_dual(Tensor input) -> (Tensor, Tensor, Tensor, Tensor)");

@@ -184,6 +184,33 @@ int dtq_mx_fp8_quantize(const void *in_bf16, void *payload, void *scales_e8m0, i
                         int64_t cols, void *stream);
 
 /*
+ * dtq_mx_fp8_quantize that also returns the tensor's amax from the same read, for steps that
+ * quantise one tensor both tensor-wise and MX: this call, then dtq_cast_with_amax, reads the
+ * input twice instead of three times (amax, cast, MX cast).  payload / scales: exactly
+ * dtq_mx_fp8_quantize's.  amax_out[0]: the largest non-NaN |x| as fp32, 0 if there is none -- the
+ * running maximum of the reference's fused op (src/dynamic_scaled_quant.cu:83-110), i.e.
+ * dtq_amax's result clamped at 0.  Needs an initialised workspace (as dtq_amax); `in` 16-byte
+ * and `payload` 8-byte aligned.  No reference counterpart.
+ */
+int dtq_mx_fp8_quantize_amax(const void *in_bf16, void *payload, void *scales_e8m0, float *amax_out, int64_t rows,
+                             int64_t cols, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * The same for a tensor that is row-sharded over the GPUs of one node (one process per GPU, every
+ * rank making this call on its shard, empty shards included): the one-warp launch that finishes the
+ * reduction on each GPU also exchanges the local maximum with all peers through peer-addressable
+ * memory, so amax_out[0] is the maximum over the whole tensor on every rank and the cast can be
+ * enqueued right behind it: no collective call.  peer_exchange, rank, world,
+ * epoch, spin_limit: as for dtq_dynamic_scaled_quant_p2p (the two calls may share the exchange
+ * buffers and the epoch sequence).  A peer that never arrives: DTQ_ERR_TIMEOUT in the workspace
+ * status word, amax_out[0] = 0.
+ */
+int dtq_mx_fp8_quantize_amax_p2p(const void *in_bf16, void *payload, void *scales_e8m0, float *amax_out,
+                                 int64_t rows, int64_t cols, void *workspace, size_t workspace_bytes,
+                                 void *const *peer_exchange, int rank, int world, uint32_t epoch,
+                                 uint32_t spin_limit, void *stream);
+
+/*
  * MX block-32 quantisation for every input type and element format the reference's schema names:
  * in_dtype DTQ_BF16 / DTQ_F16 / DTQ_F32, elem_format DTQ_E4M3 / DTQ_E5M2 / DTQ_E2M1.
  * The reference accepts fp8_type = e5m2 and fp16 / fp32 inputs but computes bf16 -> e4m3 on the

@@ -371,3 +371,51 @@ def test_mx_formats_bf16_e4m3_is_the_reference_kernel_and_ops():
     scale = torch.exp2(as_bytes(s4).cpu().float() - 127).view(512, 32, 1)
     err = (q.view(512, 32, 32) * scale - a.cpu().float().view(512, 32, 32)).abs()
     assert (err <= scale * 1.0 + 1e-30).all()
+
+
+# ---- MX cast with the tensor's amax as a by-product ---------------------------------------------------------
+
+@pytest.mark.parametrize("shape", [(128, 32), (33, 96), (1024, 4096), (4096, 8192), (1, 32)], ids=lambda s: f"{s[0]}x{s[1]}")
+def test_mx_with_amax_equals_mx_and_amax(shape):
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg3(rows=shape[0], cols=shape[1])
+    for _ in range(2):  # twice: the workspace must be left clean
+        p, s, amax = dt.mx_fp8_quantize_with_amax(a.cuda())
+        want_p, want_s = qo.mx_fp8_quantize(a)
+        assert_fp8_equal(p, want_p, E4M3, "payload")
+        assert torch.equal(as_bytes(s), as_bytes(want_s))
+        assert amax.shape == (1,) and amax.dtype == torch.float32
+        assert amax.item() == qo.amax(a).item() == dt.amax(a.cuda()).item()
+    assert dt.amax(a.cuda()).item() == qo.amax(a).item()  # the plain amax kernel still finds the workspace clean
+
+
+def test_mx_with_amax_drops_nans_and_handles_empty_and_all_nan():
+    import driss_torch_b200 as dt
+    from driss_torch_b200 import _cabi
+
+    g = torch.Generator().manual_seed(4)
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    a = bits[torch.randperm(65536, generator=g)].view(torch.bfloat16).view(64, 1024)  # NaNs and infs in most chunks
+    p, s, amax = dt.mx_fp8_quantize_with_amax(a.cuda())
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    assert_fp8_equal(p, want_p, E4M3, "payload")
+    assert torch.equal(as_bytes(s), as_bytes(want_s))
+    assert amax.item() == float("inf") == qo.amax(a).item()
+    b = a.clone()
+    b[b.float().isinf()] = 3.0
+    b[5, 77] = -7e30  # the largest finite magnitude sits in a chunk that also holds NaNs
+    b[5, 78] = float("nan")
+    _, _, amax = dt.mx_fp8_quantize_with_amax(b.cuda())
+    assert amax.item() == qo.amax(b).item() and amax.item() >= 7e30 * 0.99
+    nan = torch.full((32, 64), float("nan"), dtype=torch.bfloat16)
+    _, _, amax = dt.mx_fp8_quantize_with_amax(nan.cuda())
+    assert amax.item() == 0.0  # no non-NaN element: the fused op's starting value
+    empty = torch.zeros(0, 64, dtype=torch.bfloat16, device="cuda")
+    p, s, amax = dt.mx_fp8_quantize_with_amax(empty)
+    assert p.shape == (0, 64) and s.numel() == 0 and amax.item() == 0.0
+    # a misaligned payload is refused rather than sent down a different kernel
+    buf = torch.empty(64 * 64 + 8, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        _cabi.mx_fp8_quantize_amax(x, payload=buf[4:4 + 64 * 64].view(E4M3).view(64, 64))

@@ -31,6 +31,11 @@ class OracleKernels:
     def cast_with_amax(x, amax, dtype):
         return qo.cast_with_amax(x, amax.item(), dtype)
 
+    @staticmethod
+    def mx_fp8_quantize_with_amax(x):
+        p, s = qo.mx_fp8_quantize(x)
+        return p, s, torch.clamp_min(qo.amax(x), 0.0)
+
 
 def _free_port():
     with socket.socket() as s:
@@ -53,6 +58,11 @@ def _worker(rank, world, port, outdir, rows, cols, empty_last):
         payload, amax, scale = q.tensorwise(shard, E4M3)
         mx_payload, mx_scales = q.mx(shard)
         rw_payload, rw_amax, rw_scale = q.rowwise(shard, E4M3)
+        both = q.tensorwise_and_mx(shard, E4M3)  # two reads of the shard instead of three: same bytes
+        assert torch.equal(both[0].view(torch.uint8), payload.view(torch.uint8))
+        assert both[1].item() == amax.item() and both[2].item() == scale.item()
+        assert torch.equal(both[3].view(torch.uint8), mx_payload.view(torch.uint8))
+        assert torch.equal(both[4].view(torch.uint8), mx_scales.view(torch.uint8))
         torch.save(
             dict(span=(start, stop), payload=payload.view(torch.uint8), amax=amax, scale=scale,
                  mx_payload=mx_payload.view(torch.uint8), mx_scales=mx_scales.view(torch.uint8),

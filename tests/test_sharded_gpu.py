@@ -36,6 +36,10 @@ def test_world_size_one_uses_the_cuda_ops():
     assert scale.cpu().view(torch.int32).item() == want_scale.view(torch.int32).item()
     p, s = q.mx(full.cuda())
     assert torch.equal(as_bytes(p), as_bytes(want_mx_p)) and torch.equal(as_bytes(s), as_bytes(want_mx_s))
+    both = q.tensorwise_and_mx(full.cuda(), E4M3)
+    assert torch.equal(as_bytes(both[0]), as_bytes(want)) and both[1].item() == want_amax.item()
+    assert both[2].item() == want_scale.item()
+    assert torch.equal(as_bytes(both[3]), as_bytes(want_mx_p)) and torch.equal(as_bytes(both[4]), as_bytes(want_mx_s))
     p, am, sc = q.rowwise(full.cuda(), E4M3)
     assert torch.equal(as_bytes(p), as_bytes(want_rw)) and torch.equal(am.cpu(), want_rw_amax) and torch.equal(sc.cpu(), want_rw_scale)
 
@@ -69,7 +73,16 @@ def _worker(rank, world, port, outdir):
             f_payload, f_amax, f_scale = qf.tensorwise(shard, E4M3)
         shard2 = (shard.float() * 0.5).to(torch.bfloat16)
         f2_payload, f2_amax, _ = qf.tensorwise(shard2, torch.float8_e5m2)
+        # both quantisations in two reads: MX cast that also delivers the amax (exchanged inside that launch,
+        # or by one all-reduce), then the cast; interleaved with the other fused call on the same exchange buffers
+        b_f = qf.tensorwise_and_mx(shard, E4M3)
+        b_f2 = qf.tensorwise_and_mx(shard2, torch.float8_e5m2)
+        b_n = q.tensorwise_and_mx(shard, E4M3)
         torch.cuda.synchronize()
+        for b in (b_f, b_n):
+            assert torch.equal(as_bytes(b[0]), as_bytes(payload)) and b[1].item() == amax.item() and b[2].item() == scale.item()
+            assert torch.equal(as_bytes(b[3]), as_bytes(mx_p)) and torch.equal(as_bytes(b[4]), as_bytes(mx_s))
+        assert torch.equal(as_bytes(b_f2[0]), as_bytes(f2_payload)) and b_f2[1].item() == f2_amax.item()
         dt.check_device_status()
         torch.save(dict(payload=as_bytes(payload), amax=amax.cpu(), scale=scale.cpu(), mx_p=as_bytes(mx_p), mx_s=as_bytes(mx_s),
                         f_payload=as_bytes(f_payload), f_amax=f_amax.cpu(), f_scale=f_scale.cpu(),
@@ -131,6 +144,18 @@ def test_fused_exchange_single_rank_and_missing_peer_timeout():
     assert (out == 0x5A).all()  # no payload is written without a global maximum
     # the rank's own value did reach the peer's buffer (what a live peer would have read)
     assert (silent_peer.cpu() != 0).sum().item() == 1
+    # the MX cast with the amax exchange in its last block: world 1, then the same silent peer
+    want_p, want_s = qo.mx_fp8_quantize(x)
+    for epoch in (5, 6):
+        p, s_, am = _cabi.mx_fp8_quantize_amax(xd, peer_ptrs=[mine.data_ptr()], rank=0, epoch=epoch)
+        assert torch.equal(as_bytes(p), as_bytes(want_p)) and torch.equal(as_bytes(s_), as_bytes(want_s))
+        assert am.item() == want_amax.item()
+    _cabi.check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), stream), "init")
+    p, s_, am = _cabi.mx_fp8_quantize_amax(xd, ws=ws, peer_ptrs=[mine.data_ptr(), silent_peer.data_ptr()], rank=0, epoch=7,
+                                           spin_limit=2000)
+    torch.cuda.synchronize()  # returns: nothing hangs
+    assert _cabi.workspace_status(ws) == 5 and am.item() == 0.0
+    assert torch.equal(as_bytes(p), as_bytes(want_p))  # the MX outputs do not depend on the peers
     # a fresh workspace and the ordinary op still work
     _cabi.check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), stream), "init")
     assert torch.equal(as_bytes(_cabi.dynamic_scaled_quant(xd, E4M3, ws=ws)), as_bytes(want))
