@@ -49,6 +49,7 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
   const int64_t c = col0 + chunk * 8;
   const bool col_live = FULL || c < cols;  // cols % 32 == 0, so a quad of lanes is live or dead as a whole
   uint4 v[kRowPasses];
+  int my_scale = 0;
 #pragma unroll
   for (int p = 0; p < kRowPasses; ++p) {
     const int64_t r = row0 + p * 16 + warp * 2 + (lane >> 4);
@@ -63,9 +64,13 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
     mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 1));
     mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
     const int biased = block_biased_exponent(mag);
-    if (FULL || (col_live && r < rows)) {
-      stg_stream(payload + r * cols + c, mx_payload(v[p], inverse_scale(biased)));
-      if ((lane & 3) == 0) scales[r * kblocks + (c >> 5)] = mx_scale_byte(biased);
+    if (FULL || (col_live && r < rows)) stg_stream(payload + r * cols + c, mx_payload(v[p], inverse_scale(biased)));
+    // All four lanes of a quad hold the block's scale; lane 4k + j keeps the one of pass 4h + j, so that
+    // every lane has one byte to store after four passes instead of a quarter of the lanes after each.
+    if ((lane & 3) == (p & 3)) my_scale = biased;
+    if ((p & 3) == 3) {
+      const int64_t sr = row0 + (p - 3 + (lane & 3)) * 16 + warp * 2 + (lane >> 4);
+      if (FULL || (col_live && sr < rows)) scales[sr * kblocks + (c >> 5)] = mx_scale_byte(my_scale);
     }
   }
   __syncthreads();
@@ -84,16 +89,17 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       w[i] = tile[g * 16 + i][word ^ (g << 2)];
-      m = packed_mag_max(m, w[i] & 0x7FFF7FFFu);
+      m = packed_absmax_signed(m, w[i]);
     }
+    m &= 0x7FFF7FFFu;
     m = packed_mag_max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
     const int biased_a = block_biased_exponent(m & 0xFFFFu), biased_b = block_biased_exponent(m >> 16);
     const float inv_a = inverse_scale(biased_a), inv_b = inverse_scale(biased_b);
     uint32_t a[8], b[8];  // two consecutive rows of one column per word, as e4m3 byte pairs
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      a[i] = mx_pair(__byte_perm(w[2 * i], w[2 * i + 1], 0x5410), inv_a);
-      b[i] = mx_pair(__byte_perm(w[2 * i], w[2 * i + 1], 0x7632), inv_b);
+      a[i] = mx_pair_f32(bf16_lo(w[2 * i]), bf16_lo(w[2 * i + 1]), inv_a);
+      b[i] = mx_pair_f32(bf16_hi(w[2 * i]), bf16_hi(w[2 * i + 1]), inv_b);
     }
     if (FULL || (rows_live && col_a < cols)) {
       uint8_t *dst = payload_t + col_a * rows + r_first;  // 16 consecutive bytes of row col_a of the transpose

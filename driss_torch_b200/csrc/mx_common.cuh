@@ -16,10 +16,17 @@ __device__ __forceinline__ uint32_t packed_mag_max(uint32_t a, uint32_t b) {
   return r;
 }
 
+// The same on signed values: per-half max(|a|, |b|), with a sign bit that is the XOR of the operands'
+// signs -- garbage to be masked off once at the end of a chain (a canonical NaN included).
+__device__ __forceinline__ uint32_t packed_absmax_signed(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
 // Largest 15-bit magnitude among the eight bf16 of a 16-byte chunk.
 __device__ __forceinline__ uint32_t chunk_absmax_bits(uint4 v) {
-  const uint32_t m = packed_mag_max(packed_mag_max(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu),
-                                    packed_mag_max(v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu));
+  const uint32_t m = packed_absmax_signed(packed_absmax_signed(v.x, v.y), packed_absmax_signed(v.z, v.w)) & 0x7FFF7FFFu;
   return max(m & 0xFFFFu, m >> 16);
 }
 
@@ -44,6 +51,12 @@ __device__ __forceinline__ float inverse_scale(int biased) {
 // Two packed bf16 -> two e4m3 bytes of x * inv.
 __device__ __forceinline__ uint32_t mx_pair(uint32_t w, float inv) {
   const float2 p = __fmul2_rn(make_float2(bf16_lo(w), bf16_hi(w)), make_float2(inv, inv));
+  return cvt_fp8x2<DTQ_E4M3>(p.x, p.y);
+}
+
+// The same from two values already widened to fp32.
+__device__ __forceinline__ uint32_t mx_pair_f32(float lo, float hi, float inv) {
+  const float2 p = __fmul2_rn(make_float2(lo, hi), make_float2(inv, inv));
   return cvt_fp8x2<DTQ_E4M3>(p.x, p.y);
 }
 
