@@ -28,8 +28,15 @@ namespace {
 
 constexpr int kTile = 128;          // rows and columns of a CTA tile
 constexpr int kTileWords = kTile / 2;  // 32-bit words (bf16 pairs) per tile row
-constexpr int kThreadsDual = 256;
-constexpr int kRowPasses = kTile / 16;  // a pass of 8 warps covers 16 rows (2 per warp)
+#ifndef DTQ_DUAL_THREADS
+#define DTQ_DUAL_THREADS 256
+#endif
+constexpr int kThreadsDual = DTQ_DUAL_THREADS;
+constexpr int kWarpsDual = kThreadsDual / 32;
+constexpr int kPassRows = 2 * kWarpsDual;        // a row pass: every warp takes two rows
+constexpr int kRowPasses = kTile / kPassRows;    // 8 (256 threads) or 4 (512)
+constexpr int kColPasses = kTileWords / (4 * kWarpsDual);  // a column pass: every warp takes four word columns
+static_assert(kRowPasses % 4 == 0 && kColPasses >= 1, "256 or 512 threads");
 #ifndef DTQ_DUAL_GROUP
 #define DTQ_DUAL_GROUP 8
 #endif
@@ -52,14 +59,14 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
   int my_scale = 0;
 #pragma unroll
   for (int p = 0; p < kRowPasses; ++p) {
-    const int64_t r = row0 + p * 16 + warp * 2 + (lane >> 4);
+    const int64_t r = row0 + p * kPassRows + warp * 2 + (lane >> 4);
     v[p] = (FULL || (col_live && r < rows)) ? ldg_stream(in + r * cols + c) : make_uint4(0, 0, 0, 0);
   }
 #pragma unroll
   for (int p = 0; p < kRowPasses; ++p) {
-    const int rt = p * 16 + warp * 2 + (lane >> 4);  // rt >> 4 == p: the 16-row group of this row
+    const int rt = p * kPassRows + warp * 2 + (lane >> 4);
     const int64_t r = row0 + rt;
-    *reinterpret_cast<uint4 *>(&tile[rt][(chunk * 4) ^ (p << 2)]) = v[p];
+    *reinterpret_cast<uint4 *>(&tile[rt][(chunk * 4) ^ ((rt >> 4) << 2)]) = v[p];  // swizzled by the 16-row group
     uint32_t mag = chunk_absmax_bits(v[p]);
     mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 1));
     mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
@@ -69,7 +76,7 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
     // every lane has one byte to store after four passes instead of a quarter of the lanes after each.
     if ((lane & 3) == (p & 3)) my_scale = biased;
     if ((p & 3) == 3) {
-      const int64_t sr = row0 + (p - 3 + (lane & 3)) * 16 + warp * 2 + (lane >> 4);
+      const int64_t sr = row0 + (p - 3 + (lane & 3)) * kPassRows + warp * 2 + (lane >> 4);
       if (FULL || (col_live && sr < rows)) scales[sr * kblocks + (c >> 5)] = mx_scale_byte(my_scale);
     }
   }
@@ -81,8 +88,8 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
   const bool rows_live = FULL || r_first < rows;  // rows % 32 == 0: lanes g and g^1 are live or dead together
   const int64_t row_blocks = rows / 32;
 #pragma unroll
-  for (int pass = 0; pass < 2; ++pass) {
-    const int word = pass * 32 + warp * 4 + q;
+  for (int pass = 0; pass < kColPasses; ++pass) {
+    const int word = pass * (4 * kWarpsDual) + warp * 4 + q;
     const int64_t col_a = col0 + word * 2;  // and col_a + 1; cols is even, so both or neither exist
     uint32_t w[16];
     uint32_t m = 0;
@@ -115,7 +122,7 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
 }
 
 #ifndef DTQ_DUAL_MIN_BLOCKS
-#define DTQ_DUAL_MIN_BLOCKS 4
+#define DTQ_DUAL_MIN_BLOCKS (1024 / DTQ_DUAL_THREADS)
 #endif
 __global__ void __launch_bounds__(kThreadsDual, DTQ_DUAL_MIN_BLOCKS)
 mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
