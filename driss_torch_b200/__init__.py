@@ -126,11 +126,12 @@ def mx_fp4_quantize(input: Tensor) -> tuple[Tensor, Tensor]:
     return ops.mx_fp4_quantize(input)
 
 
-def mx_fp8_quantize_dual(input: Tensor) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+def mx_fp8_quantize_dual(input: Tensor, blocked: bool = False) -> tuple[Tensor, Tensor, Tensor, Tensor]:
     """``(p, s, p_t, s_t)`` with ``(p, s) == mx_fp8_quantize(x)`` and
     ``(p_t, s_t) == mx_fp8_quantize(x.t().contiguous())``, from a single read of ``x``
-    (both dimensions multiples of 32)."""
-    return ops.mx_fp8_quantize_dual(input)
+    (both dimensions multiples of 32).  ``blocked=True``: both scale tensors as
+    ``mx_fp8_quantize_blocked`` lays them out, ready for the MX GEMM."""
+    return ops.mx_fp8_quantize_dual(input, blocked)
 
 
 def mx_fp8_quantize_blocked(input: Tensor) -> tuple[Tensor, Tensor]:

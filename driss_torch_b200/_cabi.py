@@ -41,6 +41,7 @@ SIGNATURES = {
     "dtq_mx_fp8_quantize_amax_p2p": ([_vp, _vp, _vp, _vp, _i64, _i64, _vp, _sz, _vp, _i32, _i32, C.c_uint32, C.c_uint32, _vp], _i32),
     "dtq_mx_quantize": ([_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize_dual": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp], _i32),
+    "dtq_mx_fp8_quantize_dual_blocked": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp], _i32),
     "dtq_mx_fp8_quantize_tma": ([_vp, _vp, _vp, _i64, _i64, _vp, _vp], _i32),
     "dtq_mx_blocked_scale_bytes": ([_i64, _i64], _sz),
     "dtq_mx_fp8_quantize_blocked": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
@@ -213,13 +214,22 @@ def mx_fp8_quantize_tma(x, payload=None, scales=None, status=None):
     return payload, scales, status
 
 
-def mx_fp8_quantize_dual(x, payload=None, scales=None, payload_t=None, scales_t=None):
-    """MX cast of x and of its transpose from one read of x."""
+def mx_fp8_quantize_dual(x, payload=None, scales=None, payload_t=None, scales_t=None, blocked=False):
+    """MX cast of x and of its transpose from one read of x; ``blocked``: scales in the MX GEMM's layout."""
     rows, cols = x.shape
     e4m3, e8m0 = torch.float8_e4m3fn, torch.float8_e8m0fnu
     payload = torch.empty(rows, cols, dtype=e4m3, device=x.device) if payload is None else payload
-    scales = torch.empty(rows * (cols // 32), dtype=e8m0, device=x.device) if scales is None else scales
     payload_t = torch.empty(cols, rows, dtype=e4m3, device=x.device) if payload_t is None else payload_t
+    if blocked:
+        L = load()
+        if scales is None:
+            scales = torch.zeros(L.dtq_mx_blocked_scale_bytes(rows, cols), dtype=torch.uint8, device=x.device).view(e8m0)
+        if scales_t is None:
+            scales_t = torch.zeros(L.dtq_mx_blocked_scale_bytes(cols, rows), dtype=torch.uint8, device=x.device).view(e8m0)
+        check(L.dtq_mx_fp8_quantize_dual_blocked(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), payload_t.data_ptr(),
+                                                 scales_t.data_ptr(), rows, cols, _stream()), "dtq_mx_fp8_quantize_dual_blocked")
+        return payload, scales, payload_t, scales_t
+    scales = torch.empty(rows * (cols // 32), dtype=e8m0, device=x.device) if scales is None else scales
     scales_t = torch.empty(cols * (rows // 32), dtype=e8m0, device=x.device) if scales_t is None else scales_t
     check(load().dtq_mx_fp8_quantize_dual(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), payload_t.data_ptr(),
                                           scales_t.data_ptr(), rows, cols, _stream()), "dtq_mx_fp8_quantize_dual")

@@ -57,9 +57,14 @@ def mx_fp8_quantize_blocked_meta(x: torch.Tensor):
 
 
 @register_fake("DrissTorch::mx_fp8_quantize_dual")
-def mx_fp8_quantize_dual_meta(x: torch.Tensor):
+def mx_fp8_quantize_dual_meta(x: torch.Tensor, blocked: bool = False):
     m, n = x.shape
     e4m3, e8m0 = torch.float8_e4m3fn, torch.float8_e8m0fnu
+    if blocked:
+        def nbytes(r, c):
+            return ((r + 127) // 128) * ((c // 32 + 3) // 4) * 512
+        return (torch.empty((m, n), dtype=e4m3, device=x.device), torch.empty(nbytes(m, n), dtype=e8m0, device=x.device),
+                torch.empty((n, m), dtype=e4m3, device=x.device), torch.empty(nbytes(n, m), dtype=e8m0, device=x.device))
     return (torch.empty((m, n), dtype=e4m3, device=x.device), torch.empty(m * (n // 32), dtype=e8m0, device=x.device),
             torch.empty((n, m), dtype=e4m3, device=x.device), torch.empty(n * (m // 32), dtype=e8m0, device=x.device))
 

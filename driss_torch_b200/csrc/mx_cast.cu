@@ -27,21 +27,6 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;  // tied to the scale-byte mapping below: lane&3 picks the iteration
 
-// Where the scale of MX block `blk` (row-major index over [rows, kblocks]) goes.
-// Row-major: scales[blk], the reference's layout (src/mx_cast.cu:199,210-211).
-// Blocked: the layout the reference's MX GEMM consumes (src/mx_fp8_bf16.cu:97-110, CUTLASS
-// Sm1xxBlockScaledConfig::tile_atom_to_shape_SFA; the reference gets there through a separate
-// `to_blocked` pass, test/test_mx.py:28-32): 128-row x 4-k-block atoms of 512 bytes, atoms ordered
-// k-block-major within a 128-row band; inside an atom row r, k-block c sit at
-// (r % 32) * 16 + (r / 32) * 4 + c.
-template <bool BLOCKED>
-__device__ __forceinline__ int64_t scale_offset(int64_t blk, int64_t kblocks, int64_t katoms) {
-  if constexpr (!BLOCKED) return blk;
-  const int64_t r = blk / kblocks, c = blk - r * kblocks;
-  const int64_t atom = (r >> 7) * katoms + (c >> 2);
-  return atom * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c & 3);
-}
-
 // nchunks = numel / 8 is a multiple of 4.  A warp owns kUnroll consecutive 512-byte rows of
 // chunks; a CTA tile is kThreads * kUnroll chunks.
 template <bool BLOCKED>

@@ -43,13 +43,14 @@ static_assert(kRowPasses % 4 == 0 && kColPasses >= 1, "256 or 512 threads");
 constexpr int kGroupRowTiles = DTQ_DUAL_GROUP;
 
 // One tile.  FULL: the tile lies inside the matrix, no access is predicated.
-template <bool FULL>
+template <bool FULL, bool BLOCKED>
 __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], const uint16_t *__restrict__ in,
                                           uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
                                           uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows,
                                           int64_t cols, int64_t row0, int64_t col0) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t kblocks = cols / 32;
+  const int64_t kblocks = cols / 32, katoms = (kblocks + 3) / 4;          // scale grid of x: [rows, kblocks]
+  const int64_t row_blocks = rows / 32, row_atoms = (row_blocks + 3) / 4;  // scale grid of x^T: [cols, row_blocks]
 
   // ---- row direction: in pass p warp w owns tile rows 16p + 2w and + 1; lane l the columns 8(l&15) .. +7
   const int chunk = lane & 15;
@@ -77,7 +78,7 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
     if ((lane & 3) == (p & 3)) my_scale = biased;
     if ((p & 3) == 3) {
       const int64_t sr = row0 + (p - 3 + (lane & 3)) * kPassRows + warp * 2 + (lane >> 4);
-      if (FULL || (col_live && sr < rows)) scales[sr * kblocks + (c >> 5)] = mx_scale_byte(my_scale);
+      if (FULL || (col_live && sr < rows)) scales[scale_offset<BLOCKED>(sr * kblocks + (c >> 5), kblocks, katoms)] = mx_scale_byte(my_scale);
     }
   }
   __syncthreads();
@@ -86,7 +87,6 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
   const int g = lane & 7, q = lane >> 3;
   const int64_t r_first = row0 + g * 16;
   const bool rows_live = FULL || r_first < rows;  // rows % 32 == 0: lanes g and g^1 are live or dead together
-  const int64_t row_blocks = rows / 32;
 #pragma unroll
   for (int pass = 0; pass < kColPasses; ++pass) {
     const int word = pass * (4 * kWarpsDual) + warp * 4 + q;
@@ -113,9 +113,9 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
       stg_stream(dst, make_uint4(a[0] | (a[1] << 16), a[2] | (a[3] << 16), a[4] | (a[5] << 16), a[6] | (a[7] << 16)));
       stg_stream(dst + rows, make_uint4(b[0] | (b[1] << 16), b[2] | (b[3] << 16), b[4] | (b[5] << 16), b[6] | (b[7] << 16)));
       if ((g & 1) == 0) {
-        uint8_t *sdst = scales_t + col_a * row_blocks + (r_first >> 5);
-        sdst[0] = mx_scale_byte(biased_a);
-        sdst[row_blocks] = mx_scale_byte(biased_b);
+        const int64_t blk = col_a * row_blocks + (r_first >> 5);
+        scales_t[scale_offset<BLOCKED>(blk, row_blocks, row_atoms)] = mx_scale_byte(biased_a);
+        scales_t[scale_offset<BLOCKED>(blk + row_blocks, row_blocks, row_atoms)] = mx_scale_byte(biased_b);
       }
     }
   }
@@ -124,6 +124,7 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
 #ifndef DTQ_DUAL_MIN_BLOCKS
 #define DTQ_DUAL_MIN_BLOCKS (1024 / DTQ_DUAL_THREADS)
 #endif
+template <bool BLOCKED>
 __global__ void __launch_bounds__(kThreadsDual, DTQ_DUAL_MIN_BLOCKS)
 mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
                uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows, int64_t cols,
@@ -138,17 +139,19 @@ mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, u
   const int64_t row0 = (first_row_tile + in_group % group_rows) * kTile;
   const int64_t col0 = (in_group / group_rows) * kTile;
   if (row0 + kTile <= rows && col0 + kTile <= cols)
-    dual_tile<true>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
+    dual_tile<true, BLOCKED>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
   else
-    dual_tile<false>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
+    dual_tile<false, BLOCKED>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
 }
 
 }  // namespace
 }  // namespace dtq
 
-extern "C" int dtq_mx_fp8_quantize_dual(const void *in_bf16, void *payload, void *scales_e8m0, void *payload_t,
-                                        void *scales_t_e8m0, int64_t rows, int64_t cols, void *stream) {
-  using namespace dtq;
+namespace dtq {
+namespace {
+template <bool BLOCKED>
+int launch_dual(const void *in_bf16, void *payload, void *scales_e8m0, void *payload_t, void *scales_t_e8m0, int64_t rows,
+                int64_t cols, void *stream) {
   if (rows < 0 || cols < 0) return DTQ_ERR_INVALID_ARGUMENT;
   if (cols % 32 != 0 || rows % 32 != 0) return DTQ_ERR_SHAPE;
   if (rows == 0 || cols == 0) return DTQ_OK;
@@ -157,8 +160,20 @@ extern "C" int dtq_mx_fp8_quantize_dual(const void *in_bf16, void *payload, void
   if (!aligned_to(in_bf16, 16) || !aligned_to(payload, 8) || !aligned_to(payload_t, 16)) return DTQ_ERR_INVALID_ARGUMENT;
   const int64_t row_tiles = ceil_div64(rows, kTile), col_tiles = ceil_div64(cols, kTile);
   if (row_tiles > 0x7FFFFFFFLL / col_tiles) return DTQ_ERR_TOO_LARGE;  // grid.x
-  mx_dual_kernel<<<static_cast<unsigned>(row_tiles * col_tiles), kThreadsDual, 0, static_cast<cudaStream_t>(stream)>>>(
+  mx_dual_kernel<BLOCKED><<<static_cast<unsigned>(row_tiles * col_tiles), kThreadsDual, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint16_t *>(in_bf16), static_cast<uint8_t *>(payload), static_cast<uint8_t *>(scales_e8m0),
       static_cast<uint8_t *>(payload_t), static_cast<uint8_t *>(scales_t_e8m0), rows, cols, row_tiles, col_tiles);
   return cuda_status(cudaGetLastError());
+}
+}  // namespace
+}  // namespace dtq
+
+extern "C" int dtq_mx_fp8_quantize_dual(const void *in_bf16, void *payload, void *scales_e8m0, void *payload_t,
+                                        void *scales_t_e8m0, int64_t rows, int64_t cols, void *stream) {
+  return dtq::launch_dual<false>(in_bf16, payload, scales_e8m0, payload_t, scales_t_e8m0, rows, cols, stream);
+}
+
+extern "C" int dtq_mx_fp8_quantize_dual_blocked(const void *in_bf16, void *payload, void *scales_e8m0, void *payload_t,
+                                                void *scales_t_e8m0, int64_t rows, int64_t cols, void *stream) {
+  return dtq::launch_dual<true>(in_bf16, payload, scales_e8m0, payload_t, scales_t_e8m0, rows, cols, stream);
 }

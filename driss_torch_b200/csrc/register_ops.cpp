@@ -251,8 +251,9 @@ std::tuple<at::Tensor, at::Tensor> mx_fp4_quantize(at::Tensor input) {
   return {out, scale};
 }
 
-// MX cast of the input and of its transpose from one read of the input.
-std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> mx_fp8_quantize_dual(at::Tensor input) {
+// MX cast of the input and of its transpose from one read of the input; `blocked`: both scale tensors in the
+// blocked layout of the MX GEMM (zero in the padding).
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> mx_fp8_quantize_dual(at::Tensor input, bool blocked) {
   TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
   TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
   TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D");
@@ -262,11 +263,20 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> mx_fp8_quantize_dual(
   auto fp8 = input.options().dtype(at::kFloat8_e4m3fn);
   auto e8m0 = input.options().dtype(at::kFloat8_e8m0fnu);
   at::Tensor out = at::empty({m, n}, fp8), out_t = at::empty({n, m}, fp8);
-  at::Tensor scale = at::empty({m * (n / 32)}, e8m0), scale_t = at::empty({n * (m / 32)}, e8m0);
+  at::Tensor scale, scale_t;
+  if (blocked) {
+    auto bytes = input.options().dtype(at::kByte);
+    scale = at::zeros({static_cast<int64_t>(dtq_mx_blocked_scale_bytes(m, n))}, bytes).view(at::kFloat8_e8m0fnu);
+    scale_t = at::zeros({static_cast<int64_t>(dtq_mx_blocked_scale_bytes(n, m))}, bytes).view(at::kFloat8_e8m0fnu);
+  } else {
+    scale = at::empty({m * (n / 32)}, e8m0);
+    scale_t = at::empty({n * (m / 32)}, e8m0);
+  }
   c10::cuda::CUDAGuard guard(input.device());
   auto stream = c10::cuda::getCurrentCUDAStream();
-  check_status(dtq_mx_fp8_quantize_dual(input.data_ptr(), out.data_ptr(), scale.data_ptr(), out_t.data_ptr(),
-                                        scale_t.data_ptr(), m, n, stream.stream()),
+  auto fn = blocked ? dtq_mx_fp8_quantize_dual_blocked : dtq_mx_fp8_quantize_dual;
+  check_status(fn(input.data_ptr(), out.data_ptr(), scale.data_ptr(), out_t.data_ptr(), scale_t.data_ptr(), m, n,
+                  stream.stream()),
                "mx_fp8_quantize_dual");
   return {out, scale, out_t, scale_t};
 }
@@ -360,7 +370,7 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("mx_fp8_quantize_with_amax", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_with_amax));
   m.def("mx_fp4_quantize(Tensor input) -> (Tensor, Tensor)");
   m.impl("mx_fp4_quantize", c10::DispatchKey::CUDA, TORCH_FN(mx_fp4_quantize));
-  m.def("mx_fp8_quantize_dual(Tensor input) -> (Tensor, Tensor, Tensor, Tensor)");
+  m.def("mx_fp8_quantize_dual(Tensor input, bool blocked=False) -> (Tensor, Tensor, Tensor, Tensor)");
   m.impl("mx_fp8_quantize_dual", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_dual));
   m.def("mx_fp8_quantize_blocked(Tensor input) -> (Tensor, Tensor)");
   m.impl("mx_fp8_quantize_blocked", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_blocked));

@@ -239,6 +239,17 @@ int dtq_mx_fp8_quantize_dual(const void *in_bf16, void *payload, void *scales_e8
                              void *scales_t_e8m0, int64_t rows, int64_t cols, void *stream);
 
 /*
+ * The same with both scale arrays in the blocked layout of dtq_mx_fp8_quantize_blocked: `scales`
+ * for the [rows, cols/32] grid (dtq_mx_blocked_scale_bytes(rows, cols) bytes), `scales_t` for the
+ * [cols, rows/32] grid (dtq_mx_blocked_scale_bytes(cols, rows) bytes); padding bytes are not
+ * written (zero-fill the arrays when rows or cols is not a multiple of 128).  Both operands of the
+ * reference's mx_fp8_bf16 (src/mx_fp8_bf16.cu:197-205) for x and for x^T from one read, with no
+ * transpose, second cast or to_blocked pass.
+ */
+int dtq_mx_fp8_quantize_dual_blocked(const void *in_bf16, void *payload, void *scales_e8m0, void *payload_t,
+                                     void *scales_t_e8m0, int64_t rows, int64_t cols, void *stream);
+
+/*
  * dtq_mx_fp8_quantize through shared memory: same outputs, but the input is staged by the bulk
  * asynchronous copy engine (TMA, cp.async.bulk + mbarrier ring) for a persistent grid of
  * producer/consumer CTAs instead of being loaded straight into registers.  Kept as a measured

@@ -114,6 +114,23 @@ def test_fake_implementations():
     assert p.shape == x.shape and am.shape == (256, 1) and scale.shape == (256, 1)
     p, scale = dt.cast_with_amax(x, s, torch.float8_e4m3fn)
     assert p.shape == x.shape and scale.shape == (1,)
+    # the additions
+    e8m0 = torch.float8_e8m0fnu
+    p, sc = dt.mx_fp8_quantize_blocked(x)
+    assert p.shape == x.shape and sc.dtype == e8m0 and sc.numel() == 2 * 1 * 512
+    p, sc, p_t, sc_t = dt.mx_fp8_quantize_dual(x)
+    assert p.shape == (256, 128) and p_t.shape == (128, 256) and sc.shape == (1024,) and sc_t.shape == (1024,)
+    assert p_t.dtype == torch.float8_e4m3fn and sc_t.dtype == e8m0
+    p, sc, am = dt.mx_fp8_quantize_with_amax(x)
+    assert p.shape == x.shape and sc.shape == (1024,) and am.shape == (1,) and am.dtype == torch.float32
+    p4, sc = dt.mx_fp4_quantize(x)
+    assert p4.shape == (256, 64) and p4.dtype == torch.uint8 and sc.shape == (1024,)
+    p5, sc = dt.mx_fp8_quantize(x.float(), ScalarType=torch.float8_e5m2)
+    assert p5.dtype == torch.float8_e5m2 and p5.shape == x.shape
+    y_t = dt.saturated_cast_transposed(x, s, torch.float8_e4m3fn)
+    assert y_t.shape == (128, 256) and y_t.dtype == torch.float8_e4m3fn
+    y, y_t = dt.saturated_cast_dual(x, s, torch.float8_e5m2)
+    assert y.shape == (256, 128) and y_t.shape == (128, 256) and y.dtype == torch.float8_e5m2
 
 
 def test_python_surface_matches_the_reference_wrappers():

@@ -419,3 +419,21 @@ def test_mx_with_amax_drops_nans_and_handles_empty_and_all_nan():
     x = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError):
         _cabi.mx_fp8_quantize_amax(x, payload=buf[4:4 + 64 * 64].view(E4M3).view(64, 64))
+
+
+@pytest.mark.parametrize("rows,cols", [(128, 128), (256, 512), (96, 288), (1184, 448), (4096, 4096)])
+def test_dual_with_blocked_scales(rows, cols):
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg3(rows=rows, cols=cols)
+    p, s, p_t, s_t = dt.mx_fp8_quantize_dual(a.cuda(), blocked=True)
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    want_pt, want_st = qo.mx_fp8_quantize(a.t().contiguous())
+    assert_fp8_equal(p, want_p, E4M3, "payload")
+    assert_fp8_equal(p_t, want_pt, E4M3, "transposed payload")
+    assert torch.equal(as_bytes(s).cpu(), as_bytes(qo.to_blocked(want_s, rows, cols // 32)))
+    assert torch.equal(as_bytes(s_t).cpu(), as_bytes(qo.to_blocked(want_st, cols, rows // 32)))
+    # and equal to the single-orientation blocked op on both orientations
+    q, qs = dt.mx_fp8_quantize_blocked(a.cuda())
+    qt, qts = dt.mx_fp8_quantize_blocked(a.t().contiguous().cuda())
+    assert torch.equal(as_bytes(s), as_bytes(qs)) and torch.equal(as_bytes(s_t), as_bytes(qts))
