@@ -26,10 +26,25 @@ struct RowIn;
 template <>
 struct RowIn<DTQ_BF16> {
   static constexpr int kElems = 8, kElemBytes = 2;
+  // Running per-half max(|acc|, |w|) of packed bf16; the sign bit is garbage until `finish` masks it.
+  // A NaN operand is dropped (the other operand is returned), and acc starts at 0, so acc is never NaN.
+  using Acc = uint32_t;
+  __device__ static Acc fold1(Acc acc, uint32_t w) {
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(acc) : "r"(acc), "r"(w));
+    return acc;
+  }
+  __device__ static void fold(Acc &a, Acc &b, uint4 v) {
+    a = fold1(fold1(a, v.x), v.z);
+    b = fold1(fold1(b, v.y), v.w);
+  }
+  __device__ static float finish(Acc a, Acc b) {
+    const uint32_t m = fold1(a, b) & 0x7FFF7FFFu;
+    return fmaxf(bf16_lo(m), bf16_hi(m));
+  }
   __device__ static float absmax(uint4 v) {
-    __nv_bfloat162 m = __hmax2(__hmax2(as_bf162(v.x & 0x7FFF7FFFu), as_bf162(v.y & 0x7FFF7FFFu)),
-                               __hmax2(as_bf162(v.z & 0x7FFF7FFFu), as_bf162(v.w & 0x7FFF7FFFu)));
-    return fmaxf(__bfloat162float(m.x), __bfloat162float(m.y));
+    Acc a = 0, b = 0;
+    fold(a, b, v);
+    return finish(a, b);
   }
   template <int OUT>
   __device__ static void convert_store(uint4 v, const DsqScale &s, uint8_t *dst) {
@@ -42,6 +57,12 @@ struct RowIn<DTQ_BF16> {
 template <>
 struct RowIn<DTQ_F32> {
   static constexpr int kElems = 4, kElemBytes = 4;
+  using Acc = float;
+  __device__ static void fold(Acc &a, Acc &b, uint4 v) {
+    a = fmaxf(fmaxf(a, fabsf(__uint_as_float(v.x))), fabsf(__uint_as_float(v.z)));
+    b = fmaxf(fmaxf(b, fabsf(__uint_as_float(v.y))), fabsf(__uint_as_float(v.w)));
+  }
+  __device__ static float finish(Acc a, Acc b) { return fmaxf(a, b); }
   __device__ static float absmax(uint4 v) {
     return fmaxf(fmaxf(fabsf(__uint_as_float(v.x)), fabsf(__uint_as_float(v.y))),
                  fmaxf(fabsf(__uint_as_float(v.z)), fabsf(__uint_as_float(v.w))));
@@ -83,24 +104,30 @@ rowwise_regs_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, flo
     const int c = t + j * kTeam;
     v[j] = (live && c < chunks_per_row) ? ldg_stream(src + c) : make_uint4(0, 0, 0, 0);
   }
-  float a = 0.0f;
+  typename R::Acc acc0 = 0, acc1 = 0;
 #pragma unroll
-  for (int j = 0; j < CHUNKS; ++j) a = fmaxf(a, R::absmax(v[j]));
+  for (int j = 0; j < CHUNKS; ++j) R::fold(acc0, acc1, v[j]);
+  const float a = R::finish(acc0, acc1);
 
-  float amax;
+  DsqScale sd;
   if constexpr (TEAM_WARPS == 1) {
-    amax = warp_max_nonneg(a);
+    const float amax = warp_max_nonneg(a);
+    if (!live) return;
+    sd = make_dsq_scale<OUT>(amax);
+    if (t == 0) {
+      if (amax_out) amax_out[row] = amax;
+      if (scale_out) scale_out[row] = static_cast<float>(sd.sd);
+    }
   } else {
-    amax = block_max_nonneg(a, smem32, 0.0f);
+    float amax = block_max_nonneg(a, smem32, 0.0f);
     if (threadIdx.x == 0) smem32[0] = amax;
     __syncthreads();
     amax = smem32[0];
-  }
-  if (!live) return;
-  const DsqScale sd = make_dsq_scale<OUT>(amax);
-  if (t == 0) {
-    if (amax_out) amax_out[row] = amax;
-    if (scale_out) scale_out[row] = static_cast<float>(sd.sd);
+    sd = make_dsq_scale<OUT>(amax);
+    if (t == 0) {
+      if (amax_out) amax_out[row] = amax;
+      if (scale_out) scale_out[row] = static_cast<float>(sd.sd);
+    }
   }
   uint8_t *dst = out + row * chunks_per_row * R::kElems;
 #pragma unroll

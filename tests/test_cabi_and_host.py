@@ -60,6 +60,28 @@ def test_argument_validation_before_any_device_work():
     assert lib.dtq_mx_fp8_quantize(one, one, one, 0, 64, None) == 0
     assert lib.dtq_mx_fp8_quantize(None, one, one, 4, 64, None) == 1
     assert lib.dtq_dynamic_scaled_quant_rowwise(one, one, None, None, 4, 0, 0, 0, None) == 3
+    # the added entry points
+    assert lib.dtq_saturated_cast_transposed(one, None, one, None, 4, 4, 0, 0, None) == 1   # no scale
+    assert lib.dtq_saturated_cast_transposed(one, None, one, one, 4, 4, 5, 0, None) == 2
+    assert lib.dtq_saturated_cast_transposed(one, None, None, one, 4, 4, 0, 0, None) == 1   # no transposed output
+    assert lib.dtq_saturated_cast_transposed(one, None, one, one, 0, 4, 0, 0, None) == 0
+    assert lib.dtq_mx_quantize(one, one, one, 4, 64, 3, 0, None) == 2
+    assert lib.dtq_mx_quantize(one, one, one, 4, 64, 0, 3, None) == 2
+    assert lib.dtq_mx_quantize(one, one, one, 4, 48, 0, 2, None) == 3
+    assert lib.dtq_mx_quantize(one, None, one, 4, 64, 2, 2, None) == 1
+    assert lib.dtq_mx_quantize(one, one, one, 0, 64, 1, 1, None) == 0
+    for fn in (lib.dtq_mx_fp8_quantize_dual, lib.dtq_mx_fp8_quantize_dual_blocked):
+        assert fn(one, one, one, one, one, 48, 64, None) == 3   # rows not a multiple of 32
+        assert fn(one, one, one, one, one, 64, 48, None) == 3
+        assert fn(one, one, one, None, one, 64, 64, None) == 1
+        assert fn(one, one, one, one, one, 0, 64, None) == 0
+    assert lib.dtq_mx_fp8_quantize_amax(one, one, one, one, 4, 64, None, 0, None) == 4      # no workspace
+    assert lib.dtq_mx_fp8_quantize_amax(one, one, one, None, 4, 64, one, 1 << 20, None) == 1  # no amax output
+    assert lib.dtq_mx_fp8_quantize_amax(one, one, one, one, 4, 48, one, 1 << 20, None) == 3
+    assert lib.dtq_mx_fp8_quantize_amax_p2p(one, one, one, one, 4, 64, one, 1 << 20, None, 0, 1, 1, 0, None) == 1
+    ptrs = (ctypes.c_void_p * 2)(256, 512)
+    assert lib.dtq_mx_fp8_quantize_amax_p2p(one, one, one, one, 4, 64, one, 1 << 20, ptrs, 2, 2, 1, 0, None) == 1  # rank
+    assert lib.dtq_mx_fp8_quantize_amax_p2p(one, one, one, one, 4, 64, one, 1 << 20, ptrs, 0, 17, 1, 0, None) == 1  # world
     assert lib.dtq_dynamic_scaled_quant_rowwise(one, one, None, None, 0, 16, 0, 0, None) == 0
     assert lib.dtq_dynamic_scaled_quant_rowwise(one, one, None, None, 4, 16, 9, 0, None) == 2
     assert lib.dtq_workspace_init(None, 0, None) == 4
