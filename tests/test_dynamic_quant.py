@@ -240,3 +240,55 @@ def test_ops_capture_into_a_cuda_graph_and_replay():
     assert_fp8_equal(mx_p, wp, E4M3, "graph: mx payload")
     assert torch.equal(mx_s.view(torch.uint8).cpu(), ws_.view(torch.uint8))
     assert _cabi.workspace_status(ws) == 0
+
+
+def test_shared_read_step_and_two_orientation_casts_capture_into_a_cuda_graph():
+    # The step's default composition (MX cast that delivers the amax, its one-warp finishing launch, the cast)
+    # and the two-orientation casts, captured once and replayed on new data.
+    from driss_torch_b200 import _cabi
+
+    E4M3 = torch.float8_e4m3fn
+    x = workloads.make_cfg2(rows=1024, cols=2048).cuda()
+    x2 = workloads.make_cfg3(rows=1024, cols=2048)
+    out = torch.empty(x.shape, dtype=E4M3, device="cuda")
+    mx_p = torch.empty_like(out)
+    mx_s = torch.empty(x.numel() // 32, dtype=torch.float8_e8m0fnu, device="cuda")
+    amax, scale = torch.zeros(1, device="cuda"), torch.zeros(1, device="cuda")
+    dual = None
+    sat = None
+    stream = torch.cuda.Stream()
+
+    def step():
+        nonlocal dual, sat
+        _cabi.mx_fp8_quantize_amax(x, payload=mx_p, scales=mx_s, amax_out=amax, ws=ws)
+        _cabi.cast_with_amax(x, amax, E4M3, out=out, scale_out=scale)
+        dual = _cabi.mx_fp8_quantize_dual(x, *(dual or ()))
+        sat = _cabi.saturated_cast_transposed(x, scale, E4M3, *((sat[1], sat[0]) if sat else ()), both=True)
+
+    with torch.cuda.stream(stream):
+        ws = _cabi.workspace()
+        for _ in range(2):
+            step()
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step()
+    x.copy_(x2)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    want, want_amax, want_scale = qo.dynamic_scaled_quant(x2, E4M3)
+    assert_fp8_equal(out, want, E4M3, "graph: MX cast with amax + cast")
+    assert _bits(amax) == _bits(want_amax) and _bits(scale) == _bits(want_scale)
+    wp, ws_ = qo.mx_fp8_quantize(x2)
+    wpt, wst = qo.mx_fp8_quantize(x2.t().contiguous())
+    assert_fp8_equal(mx_p, wp, E4M3, "graph: mx payload")
+    assert torch.equal(mx_s.view(torch.uint8).cpu(), ws_.view(torch.uint8))
+    assert_fp8_equal(dual[0], wp, E4M3, "graph: dual payload")
+    assert_fp8_equal(dual[2], wpt, E4M3, "graph: dual transposed payload")
+    assert torch.equal(dual[3].view(torch.uint8).cpu(), wst.view(torch.uint8))
+    # the transposed cast read the scale the graph itself produced
+    want_sat = qo.saturated_cast(x2, want_scale.item(), E4M3)
+    assert_fp8_equal(sat[0], want_sat, E4M3, "graph: saturated_cast")
+    assert_fp8_equal(sat[1], want_sat.t().contiguous(), E4M3, "graph: saturated_cast transposed")
+    assert _cabi.workspace_status(ws) == 0
