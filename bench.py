@@ -247,7 +247,24 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
              algorithmic_bytes("dynamic_scaled_quant", w.rows, w.cols), rt,
              note="compulsory bytes N*(2+1); a two-pass kernel moves N*(2*2+1) unless the re-read hits L2; "
                   "reference kernel timed on fp32 input")
-    del xs, outs, xf
+    outs_t = [torch.empty(w.cols, w.rows, dtype=E4M3, device=dev) for _ in range(ns)]
+    ws_ = _cabi.workspace(dev)
+
+    def dual(i):
+        _cabi.amax(xs[i], out=one, ws=ws_)
+        _cabi.cast_with_amax_transposed(xs[i], one, E4M3, out_t=outs_t[i], out=outs[i])
+
+    def twice(i):
+        _cabi.dynamic_scaled_quant(xs[i], E4M3, out=outs[i], ws=ws_)
+        _cabi.dynamic_scaled_quant(xs[i].t().contiguous(), E4M3, out=outs_t[i], ws=ws_)
+
+    t = timed(dual, ns, iters)
+    t2 = timed(twice, ns, iters)
+    line("cfg2", "dynamic_scaled_quant_dual (amax, then x and x^T cast from one read)", x.shape, t,
+         x.numel() * 4, None,
+         note=f"compulsory bytes N*(2+1+1); two launches move N*(2+2+1+1); the same two outputs by fused op + torch "
+              f"transpose + fused op: {t2[0] * 1e3:.1f} us")
+    del xs, outs, xf, outs_t
 
     # cfg3: mx_fp8_quantize bf16 [16384,8192]
     w = workloads.WORKLOADS["cfg3"]

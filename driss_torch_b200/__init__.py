@@ -113,6 +113,18 @@ def cast_with_amax(inpt: Tensor, amax_value: Tensor, dtype: torch.dtype) -> tupl
     return ops.cast_with_amax(inpt, amax_value, dtype)
 
 
+def cast_with_amax_dual(inpt: Tensor, amax_value: Tensor, dtype: torch.dtype) -> tuple[Tensor, Tensor, Tensor]:
+    """``(payload, payload_t, scale)``: ``cast_with_amax`` of ``x`` and of ``x.t().contiguous()`` from one read."""
+    return ops.cast_with_amax_dual(inpt, amax_value, dtype)
+
+
+def dynamic_scaled_quant_dual(inpt: Tensor, dtype: torch.dtype) -> tuple[Tensor, Tensor, Tensor, Tensor]:
+    """``(payload, payload_t, amax, scale)`` with ``payload == dynamic_scaled_quant(x)`` and
+    ``payload_t == dynamic_scaled_quant(x.t().contiguous())``: the two fp8 operands tensor-wise scaled
+    training needs, in two reads of ``x`` (amax, then both casts at once)."""
+    return ops.dynamic_scaled_quant_dual(inpt, dtype)
+
+
 def mx_fp8_quantize_with_amax(input: Tensor) -> tuple[Tensor, Tensor, Tensor]:
     """``mx_fp8_quantize(x)`` plus ``max(0, amax(x))`` (fp32 [1]) from the same read of ``x``: with
     ``cast_with_amax`` behind it, a tensor is quantised both tensor-wise and MX in two reads instead of three."""
@@ -158,6 +170,8 @@ __all__ = [
     "cast_with_amax",
     "saturated_cast_transposed",
     "saturated_cast_dual",
+    "cast_with_amax_dual",
+    "dynamic_scaled_quant_dual",
     "mx_fp8_quantize_with_amax",
     "mx_fp4_quantize",
     "mx_fp8_quantize_dual",

@@ -27,6 +27,7 @@ SIGNATURES = {
     "dtq_workspace_init": ([_vp, _sz, _vp], _i32),
     "dtq_workspace_status": ([_vp, _vp, _vp], _i32),
     "dtq_saturated_cast": ([_vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
+    "dtq_cast_with_amax_transposed": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_saturated_cast_transposed": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_amax": ([_vp, _vp, _i64, _i32, _vp, _sz, _vp], _i32),
     "dtq_amax_static_scratch": ([_vp, _vp, _i64, _i32, _vp], _i32),
@@ -284,3 +285,16 @@ def mx_fp8_quantize_amax(x, payload=None, scales=None, amax_out=None, ws=None, p
                                                   amax_out.data_ptr(), rows, cols, ws.data_ptr(), ws.numel(), ptrs, rank,
                                                   world, epoch, spin_limit, _stream()), "dtq_mx_fp8_quantize_amax_p2p")
     return payload, scales, amax_out
+
+
+def cast_with_amax_transposed(x, amax_value, out_dtype, out_t=None, out=None, both=False, scale_out=None):
+    """The dynamic cast of x transposed ([cols, rows]) for a device-resident amax; with ``both`` (or ``out``)
+    also the cast of x itself."""
+    rows, cols = x.shape
+    out_t = torch.empty(cols, rows, dtype=out_dtype, device=x.device) if out_t is None else out_t
+    if both and out is None:
+        out = torch.empty(rows, cols, dtype=out_dtype, device=x.device)
+    check(load().dtq_cast_with_amax_transposed(x.data_ptr(), out.data_ptr() if out is not None else None, out_t.data_ptr(),
+                                               amax_value.data_ptr(), _ptr(scale_out), rows, cols, IN_CODE[x.dtype],
+                                               OUT_CODE[out_dtype], _stream()), "dtq_cast_with_amax_transposed")
+    return (out, out_t) if out is not None else out_t

@@ -93,3 +93,17 @@ def mx_fp8_quantize_with_amax_meta(x: torch.Tensor):
     return (torch.empty_like(x, dtype=torch.float8_e4m3fn),
             torch.empty(m * (n // 32), dtype=torch.float8_e8m0fnu, device=x.device),
             torch.empty(1, dtype=torch.float32, device=x.device))
+
+
+@register_fake("DrissTorch::cast_with_amax_dual")
+def cast_with_amax_dual_meta(x: torch.Tensor, amax: torch.Tensor, dtype: torch.dtype):
+    return (torch.empty(tuple(x.shape), dtype=dtype, device=x.device),
+            torch.empty((x.shape[1], x.shape[0]), dtype=dtype, device=x.device),
+            torch.empty(1, dtype=torch.float32, device=x.device))
+
+
+@register_fake("DrissTorch::dynamic_scaled_quant_dual")
+def dynamic_scaled_quant_dual_meta(x: torch.Tensor, dtype: torch.dtype):
+    return (torch.empty(tuple(x.shape), dtype=dtype, device=x.device),
+            torch.empty((x.shape[1], x.shape[0]), dtype=dtype, device=x.device),
+            torch.empty(1, dtype=torch.float32, device=x.device), torch.empty(1, dtype=torch.float32, device=x.device))

@@ -128,6 +128,51 @@ std::tuple<at::Tensor, at::Tensor> saturated_cast_dual(const at::Tensor &input, 
   return cast_transposed(input, scale, dtype, true, "saturated_cast_dual");
 }
 
+// Both orientations of the dynamic cast for a device-resident amax: (payload, payload_t, scale).
+std::tuple<at::Tensor, at::Tensor, at::Tensor> cast_with_amax_dual(const at::Tensor &input, const at::Tensor &amax_value,
+                                                                   at::ScalarType dtype) {
+  check_fp8(dtype);
+  check_input(input);
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  TORCH_CHECK(amax_value.scalar_type() == at::kFloat && amax_value.numel() == 1 && amax_value.is_cuda() &&
+                  amax_value.device() == input.device(),
+              "amax must be a one-element fp32 tensor on the input's device");
+  const int64_t rows = input.size(0), cols = input.size(1);
+  at::Tensor out = at::empty({rows, cols}, input.options().dtype(dtype));
+  at::Tensor out_t = at::empty({cols, rows}, input.options().dtype(dtype));
+  at::Tensor scale = at::empty({1}, input.options().dtype(at::kFloat));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  if (input.numel() == 0) {  // nothing is launched: derive the scale like the cast kernels do
+    scale.copy_((dtype == at::kFloat8_e4m3fn ? 448.0 : 57344.0) / (amax_value.clamp_min(0).to(at::kDouble) + 1e-12));
+    return {out, out_t, scale};
+  }
+  check_status(dtq_cast_with_amax_transposed(input.data_ptr(), out.data_ptr(), out_t.data_ptr(),
+                                             amax_value.data_ptr<float>(), scale.data_ptr<float>(), rows, cols,
+                                             in_code(input.scalar_type()), out_code(dtype), stream.stream()),
+               "cast_with_amax_dual");
+  return {out, out_t, scale};
+}
+
+// amax, then both orientations of the cast: (payload, payload_t, amax, scale); two launches, the input read twice.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> dynamic_scaled_quant_dual(const at::Tensor &input,
+                                                                                      at::ScalarType dtype) {
+  check_fp8(dtype);
+  check_input(input);
+  TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
+  at::Tensor amax_value = at::empty({1}, input.options().dtype(at::kFloat));
+  {
+    c10::cuda::CUDAGuard guard(input.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    check_status(dtq_amax(input.data_ptr(), amax_value.data_ptr<float>(), input.numel(), in_code(input.scalar_type()),
+                          workspaces().get(stream), dtq_workspace_bytes(), stream.stream()),
+                 "dynamic_scaled_quant_dual");
+  }
+  amax_value.clamp_min_(0.0);  // an empty input gives -inf; the fused op starts its maximum at 0
+  auto r = cast_with_amax_dual(input, amax_value, dtype);
+  return {std::get<0>(r), std::get<1>(r), amax_value, std::get<2>(r)};
+}
+
 at::Tensor amax(const at::Tensor &input) {
   check_input(input);
   // max is order independent, so any dense layout can be reduced over its storage.
@@ -362,6 +407,10 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("dynamic_scaled_quant_rowwise", c10::DispatchKey::CUDA, TORCH_FN(dynamic_scaled_quant_rowwise));
   m.def("cast_with_amax(Tensor input, Tensor amax, ScalarType dtype) -> (Tensor, Tensor)");
   m.impl("cast_with_amax", c10::DispatchKey::CUDA, TORCH_FN(cast_with_amax));
+  m.def("cast_with_amax_dual(Tensor input, Tensor amax, ScalarType dtype) -> (Tensor, Tensor, Tensor)");
+  m.impl("cast_with_amax_dual", c10::DispatchKey::CUDA, TORCH_FN(cast_with_amax_dual));
+  m.def("dynamic_scaled_quant_dual(Tensor input, ScalarType dtype) -> (Tensor, Tensor, Tensor, Tensor)");
+  m.impl("dynamic_scaled_quant_dual", c10::DispatchKey::CUDA, TORCH_FN(dynamic_scaled_quant_dual));
   m.def("saturated_cast_transposed(Tensor input, Tensor scale, ScalarType dtype) -> Tensor");
   m.impl("saturated_cast_transposed", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast_transposed));
   m.def("saturated_cast_dual(Tensor input, Tensor scale, ScalarType dtype) -> (Tensor, Tensor)");

@@ -87,6 +87,19 @@ int dtq_saturated_cast_transposed(const void *in, void *out, void *out_t, const 
                                   int64_t cols, int in_dtype, int out_dtype, void *stream);
 
 /*
+ * dtq_cast_with_amax with the output transposed, or in both orientations from one read of a
+ * contiguous [rows, cols] input (the two fp8 operands tensor-wise scaled training needs):
+ *   out_t [cols, rows] = dtq_cast_with_amax(transpose(in))   always written
+ *   out   [rows, cols] = dtq_cast_with_amax(in)              written unless `out` is NULL
+ * Arithmetic of dtq_cast_with_amax / the reference's fused op (src/dynamic_scaled_quant.cu:111-117)
+ * bit for bit; `amax` is a device float (dtq_amax's output, an all-reduced value, or the MX cast's
+ * by-product), `scale_out` (nullable) receives the fp32 scale.  Shapes and alignment as for
+ * dtq_saturated_cast_transposed.  No reference counterpart.
+ */
+int dtq_cast_with_amax_transposed(const void *in, void *out, void *out_t, const float *amax, float *scale_out,
+                                  int64_t rows, int64_t cols, int in_dtype, int out_dtype, void *stream);
+
+/*
  * out[0] = max_i |in[i]| as fp32 (-inf for numel == 0; NaNs are dropped), one
  * launch, no pre-initialised output.
  * Replaces driss_torch::amax and amax_kernel: src/amax.cu:50-80, :82-119.

@@ -151,6 +151,10 @@ def test_fake_implementations():
     assert p5.dtype == torch.float8_e5m2 and p5.shape == x.shape
     y_t = dt.saturated_cast_transposed(x, s, torch.float8_e4m3fn)
     assert y_t.shape == (128, 256) and y_t.dtype == torch.float8_e4m3fn
+    p, p_t, scale = dt.cast_with_amax_dual(x, s, torch.float8_e4m3fn)
+    assert p.shape == (256, 128) and p_t.shape == (128, 256) and scale.shape == (1,)
+    p, p_t, am, scale = dt.dynamic_scaled_quant_dual(x, torch.float8_e5m2)
+    assert p_t.shape == (128, 256) and p_t.dtype == torch.float8_e5m2 and am.shape == (1,) and scale.shape == (1,)
     y, y_t = dt.saturated_cast_dual(x, s, torch.float8_e5m2)
     assert y.shape == (256, 128) and y_t.shape == (128, 256) and y.dtype == torch.float8_e5m2
 

@@ -292,3 +292,51 @@ def test_shared_read_step_and_two_orientation_casts_capture_into_a_cuda_graph():
     assert_fp8_equal(sat[0], want_sat, E4M3, "graph: saturated_cast")
     assert_fp8_equal(sat[1], want_sat.t().contiguous(), E4M3, "graph: saturated_cast transposed")
     assert _cabi.workspace_status(ws) == 0
+
+
+# ---- both orientations of the dynamic cast ----------------------------------------------------------------
+
+DUAL_SHAPES = [(128, 128), (16, 8), (48, 200), (144, 1032), (2048, 1024), (1040, 4104),  # tiled path
+               (3, 7), (33, 512), (100, 36), (1, 1)]                                       # byte-tile path
+
+
+@pytest.mark.parametrize("shape", DUAL_SHAPES, ids=lambda s: f"{s[0]}x{s[1]}")
+@pytest.mark.parametrize("fp8_dtype", FP8_DTYPES)
+@pytest.mark.parametrize("in_dtype", IN_DTYPES)
+def test_dynamic_quant_dual(shape, in_dtype, fp8_dtype):
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg2(rows=shape[0], cols=shape[1]).to(in_dtype)
+    want, want_amax, want_scale = qo.dynamic_scaled_quant(a, fp8_dtype)
+    p, p_t, amax, scale = dt.dynamic_scaled_quant_dual(a.cuda(), fp8_dtype)
+    assert p.shape == tuple(shape) and p_t.shape == (shape[1], shape[0]) and p_t.is_contiguous()
+    assert_fp8_equal(p, want, fp8_dtype, "row-major")
+    assert_fp8_equal(p_t, want.t().contiguous(), fp8_dtype, "transposed")
+    assert _bits(amax) == _bits(want_amax) and _bits(scale) == _bits(want_scale)
+
+
+@pytest.mark.parametrize("fp8_dtype", FP8_DTYPES)
+def test_cast_with_amax_dual_on_the_tie_lattice_and_with_foreign_amax(fp8_dtype):
+    # every bf16 value against amax values that put many products exactly on fp8 rounding ties (compensated
+    # path), an amax that is not a bf16 value (bracket path with the double-precision redo), and an amax
+    # smaller than the data (saturation)
+    import driss_torch_b200 as dt
+    from driss_torch_b200 import _cabi
+
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).view(256, 256)
+    bits = torch.where(bits.float().isnan(), torch.zeros((), dtype=torch.bfloat16), bits)
+    xd = bits.cuda()
+    for amax_value in (4.0, 5.3125, 448.0, 0.7431640625, 3.1415927, 1e-3):
+        am = torch.tensor([amax_value], dtype=torch.float32)
+        want, want_scale = qo.cast_with_amax(bits, am.item(), fp8_dtype)
+        p, p_t, scale = dt.cast_with_amax_dual(xd, am.cuda(), fp8_dtype)
+        assert_fp8_equal(p, want, fp8_dtype, f"row-major, amax {amax_value}")
+        assert_fp8_equal(p_t, want.t().contiguous(), fp8_dtype, f"transposed, amax {amax_value}")
+        assert _bits(scale) == _bits(want_scale)
+        only_t = _cabi.cast_with_amax_transposed(xd, am.cuda(), fp8_dtype)
+        assert_fp8_equal(only_t, want.t().contiguous(), fp8_dtype, "transposed only")
+        f32 = bits.float()
+        want32, _ = qo.cast_with_amax(f32, am.item(), fp8_dtype)
+        p32, p32_t, _ = dt.cast_with_amax_dual(f32.cuda(), am.cuda(), fp8_dtype)
+        assert_fp8_equal(p32, want32, fp8_dtype, "fp32 row-major")
+        assert_fp8_equal(p32_t, want32.t().contiguous(), fp8_dtype, "fp32 transposed")
