@@ -103,3 +103,62 @@ def test_large_input_split_path_and_chunk_invariance():
     assert total == int(p.view(torch.uint8).sum(dtype=torch.int64))
     assert _cabi.workspace_status(_cabi.workspace()) == 0
     dt.check_device_status()
+
+
+def test_two_orientation_ops_full_size_are_the_base_ops_and_their_transposes():
+    # size-independent properties at the benchmark shapes: the row-major outputs are the base ops' outputs,
+    # the transposed outputs are the base ops on the transposed input (MX) or the transposed payload (elementwise casts)
+    import driss_torch_b200 as dt
+
+    x = workloads.make_cfg3(device="cuda")  # [16384, 8192]
+    p, s = dt.mx_fp8_quantize(x)
+    dp, ds, dpt, dst = dt.mx_fp8_quantize_dual(x)
+    _same(dp, p, "dual payload")
+    _same(ds, s, "dual scales")
+    xt = x.t().contiguous()
+    pt, st = dt.mx_fp8_quantize(xt)
+    _same(dpt, pt, "dual transposed payload")
+    _same(dst, st, "dual transposed scales")
+    del xt, pt, st, dpt, dst
+    mp, ms, am = dt.mx_fp8_quantize_with_amax(x)
+    _same(mp, p, "payload of the MX cast that delivers the amax")
+    _same(ms, s, "its scales")
+    assert am.item() == dt.amax(x).item()
+    x2 = workloads.make_cfg2(device="cuda")  # [8192, 8192]
+    for fp8_dtype in (E4M3, E5M2):
+        want = dt.dynamic_scaled_quant(x2, fp8_dtype)
+        q, qt, amax, scale = dt.dynamic_scaled_quant_dual(x2, fp8_dtype)
+        _same(q, want, "dynamic dual, row-major")
+        _same(qt, want.view(torch.uint8).t().contiguous(), "dynamic dual, transposed")
+        sc = workloads.tensor_scale(x2, fp8_dtype)
+        y = dt.saturated_cast(x2, sc, fp8_dtype)
+        y2, yt = dt.saturated_cast_dual(x2, sc, fp8_dtype)
+        _same(y2, y, "saturated dual, row-major")
+        _same(yt, y.view(torch.uint8).t().contiguous(), "saturated dual, transposed")
+        _same(dt.saturated_cast_transposed(x2, sc, fp8_dtype), yt, "transposed only")
+
+
+def test_other_mx_formats_full_size_properties():
+    # e5m2 / e2m1 at the cfg3 shape: scale bytes are e4m3's shifted by the formats' exponent difference (no block
+    # of this workload is near a clamp), chunked == whole, and dequantised values stay within half a step
+    import driss_torch_b200 as dt
+
+    x = workloads.make_cfg3(device="cuda")
+    _, s8 = dt.mx_fp8_quantize(x)
+    p5, s5 = dt.mx_fp8_quantize(x, ScalarType=E5M2)
+    p4, s4 = dt.mx_fp4_quantize(x)
+    e8, e5, e4 = (t.view(torch.uint8).int() for t in (s8, s5, s4))
+    assert torch.equal(e5, e8 - 7) and torch.equal(e4, e8 + 6)
+    half = x.shape[0] // 2
+    q4, t4 = dt.mx_fp4_quantize(x[half:])
+    _same(q4, p4[half:], "fp4 chunked == whole")
+    _same(t4, s4[half * (x.shape[1] // 32):], "fp4 scales chunked == whole")
+    rows = slice(5000, 5016)
+    want_p, want_s = qo.mx_quantize(x[rows].cpu(), "e2m1")
+    _same(p4[rows].cpu(), want_p, "fp4 rows vs oracle")
+    want_p, want_s = qo.mx_quantize(x[rows].cpu(), E5M2)
+    _same(p5[rows].cpu(), want_p, "e5m2 rows vs oracle")
+    # dequantisation: |x - q * 2^(e-127)| <= half the largest step of the format at that block's scale
+    scale = torch.exp2(e5.float() - 127).view(x.shape[0], -1, 1)
+    err = (p5.float().view(x.shape[0], -1, 32) * scale - x.float().view(x.shape[0], -1, 32)).abs()
+    assert bool((err <= scale * 2.0**13 * 0.5 + 1e-30).all())  # e5m2: two mantissa bits, largest binade 2^15
