@@ -168,8 +168,11 @@ __device__ __forceinline__ void transposed_tile(uint32_t (&tile)[kTileRows][kTil
 
 // `scale` points to the scale (Cast) or to the amax (DynCast); scale_out, if given, receives the fp32 scale
 // a DynCast derived from the amax.
+#ifndef DTQ_CT_MIN_BLOCKS
+#define DTQ_CT_MIN_BLOCKS 4
+#endif
 template <typename C, bool BOTH>
-__global__ void __launch_bounds__(kThreadsT, 4)
+__global__ void __launch_bounds__(kThreadsT, DTQ_CT_MIN_BLOCKS)
 cast_transposed_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, uint8_t *__restrict__ out_t,
                        const float *__restrict__ scale, float *__restrict__ scale_out, int64_t rows, int64_t cols,
                        int64_t col_tiles) {
