@@ -362,7 +362,7 @@ def step_bytes(rows: int) -> int:
     return algorithmic_bytes("dynamic_scaled_quant", rows, COLS) + algorithmic_bytes("mx_fp8_quantize", rows, COLS)
 
 
-def cpu_baseline(sample_rows: int = 4096):
+def cpu_baseline(sample_rows: int = 32768):
     from oracle import quant_oracle as qo
 
     x = cpu_sample(sample_rows)
@@ -371,7 +371,7 @@ def cpu_baseline(sample_rows: int = 4096):
     te = time_cpu_eager(x, repeats=2)
     nbytes = step_bytes(sample_rows)
     return {"value": round(nbytes / t / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"first {sample_rows} rows of chunk 0 of the workload ({sample_rows}x{COLS} bf16), best of 3; "
+            "sample": f"first {sample_rows} rows of the workload = row chunk 0 ({sample_rows}x{COLS} bf16, 1/8 of the matrix), best of 3; "
                       "oracle/quant_oracle.c with OpenMP",
             "eager_value": round(nbytes / te / 1e9, 3), "eager_cores": torch.get_num_threads(),
             "eager_note": "the reference tests' PyTorch-eager formulas (oracle/eager.py) on the same sample, best of 2"}
@@ -385,7 +385,7 @@ def run_reference_arm(args, rank: int):
 
     # torchrun pins OMP_NUM_THREADS=1 for its children; this arm is meant to use every host core
     qo.set_num_threads(os.cpu_count() or 1)
-    sample_rows = 8192
+    sample_rows = 16384
     x = cpu_sample(sample_rows)
     for _ in range(args.warmup):
         time_cpu_step(x, 1)
