@@ -20,6 +20,20 @@ __device__ __forceinline__ uint4 ldg_stream(const void *p) {
                : "l"(p));
   return v;
 }
+// The same load with an L2 eviction policy attached (see l2_policy_evict_last): for data that the
+// same launch reads again and that should therefore outlive the streaming traffic in L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint4 ldg_stream_hint(const void *p, uint64_t policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(policy));
+  return v;
+}
 // Same access without the streaming hint: for data that is read again later in the same launch.
 __device__ __forceinline__ uint4 ldg_keep(const void *p) {
   uint4 v;

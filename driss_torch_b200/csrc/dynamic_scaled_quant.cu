@@ -129,6 +129,17 @@ struct DsqChunk<DTQ_F32, OUT, BOUNDED> {
 // Requires `in` 16-byte aligned and `out` aligned for the packed store; numel may be anything
 // (block 0 handles the elements past the last whole chunk).  Dynamic shared memory holds
 // `smem_tiles` tiles.
+// Phase 1 loads the newest DTQ_FUSED_L2_KEEP_MB of the tiles it cannot keep on chip with an L2 evict_last
+// policy, so that they survive the rest of the streaming traffic until phase 2 comes back for them (newest
+// first).  Measured on B200, 128 MiB input: 53.2 us without the hint, 52.6 / 50.9 / 50.0 / 49.3 us with
+// 32 / 48 / 64 / 80 MB, 49.8 us with every streamed tile marked (more than L2 holds: the marked lines evict
+// each other).
+#ifndef DTQ_FUSED_L2_HINT
+#define DTQ_FUSED_L2_HINT 1
+#endif
+#ifndef DTQ_FUSED_L2_KEEP_MB
+#define DTQ_FUSED_L2_KEEP_MB 80
+#endif
 constexpr int kFusedThreads = DTQ_FUSED_THREADS;
 
 template <int UNROLL>
@@ -144,6 +155,18 @@ __device__ __forceinline__ void load_tile(uint4 (&v)[UNROLL], const uint4 *__res
     for (int u = 0; u < UNROLL; ++u)
       v[u] = (first + u * kFusedThreads < nchunks) ? ldg_stream(in + first + u * kFusedThreads) : make_uint4(0, 0, 0, 0);
   }
+}
+
+// The same with an L2 eviction policy on every load.
+template <int UNROLL>
+__device__ __forceinline__ void load_tile_hint(uint4 (&v)[UNROLL], const uint4 *__restrict__ in, int64_t tile,
+                                               int64_t nchunks, uint64_t policy) {
+  constexpr int64_t kTile = int64_t(kFusedThreads) * UNROLL;
+  const int64_t first = tile * kTile + threadIdx.x;
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u)
+    v[u] = (first + u * kFusedThreads < nchunks) ? ldg_stream_hint(in + first + u * kFusedThreads, policy)
+                                                 : make_uint4(0, 0, 0, 0);
 }
 
 template <typename C, int UNROLL>
@@ -186,6 +209,12 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   const int64_t kept = count < smem_tiles + kRegTiles ? count : smem_tiles + kRegTiles;
 
   // phase 1
+#if DTQ_FUSED_L2_HINT
+  const uint64_t keep_policy = l2_policy_evict_last();
+  // the newest DTQ_FUSED_L2_KEEP_MB of the streamed tiles (phase 2 starts with them); never a kept tile
+  const int64_t hint_tiles = (int64_t(DTQ_FUSED_L2_KEEP_MB) << 20) / (G * kTile * 16);
+  const int64_t hint_from = count - hint_tiles > kept ? count - hint_tiles : kept;
+#endif
   float a = 0.0f, b = 0.0f;
   uint4 first_tile[UNROLL];
 #pragma unroll
@@ -198,8 +227,18 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   for (int64_t k = kRegTiles; k < count; k += 2) {  // two tiles (2 * UNROLL loads) in flight
     uint4 v[UNROLL], w[UNROLL];
     const bool second = k + 1 < count;
+#if DTQ_FUSED_L2_HINT
+    // tiles that are not kept on chip come back in phase 2: ask L2 to hold on to them
+    if (k >= hint_from) load_tile_hint<UNROLL>(v, in, blockIdx.x + k * G, nchunks, keep_policy);
+    else load_tile<UNROLL>(v, in, blockIdx.x + k * G, nchunks);
+    if (second) {
+      if (k + 1 >= hint_from) load_tile_hint<UNROLL>(w, in, blockIdx.x + (k + 1) * G, nchunks, keep_policy);
+      else load_tile<UNROLL>(w, in, blockIdx.x + (k + 1) * G, nchunks);
+    }
+#else
     load_tile<UNROLL>(v, in, blockIdx.x + k * G, nchunks);
     if (second) load_tile<UNROLL>(w, in, blockIdx.x + (k + 1) * G, nchunks);
+#endif
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) C::absmax(a, b, v[u]);
     if (k < kept) {
