@@ -134,6 +134,9 @@ struct DsqChunk<DTQ_F32, OUT, BOUNDED> {
 // first).  Measured on B200, 128 MiB input: 53.2 us without the hint, 52.6 / 50.9 / 50.0 / 49.3 us with
 // 32 / 48 / 64 / 80 MB, 49.8 us with every streamed tile marked (more than L2 holds: the marked lines evict
 // each other).
+#ifndef DTQ_CAST_REVERSE
+#define DTQ_CAST_REVERSE 1
+#endif
 #ifndef DTQ_FUSED_L2_HINT
 #define DTQ_FUSED_L2_HINT 1
 #endif
@@ -325,7 +328,14 @@ cast_with_amax_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, c
   }
   const int64_t nchunks = numel / C::kElems;
   constexpr int64_t kTile = int64_t(kThreads) * UNROLL;
+#if DTQ_CAST_REVERSE
+  // highest addresses first: what the kernel before this one read last (an amax, an MX cast) may still be in L2
+  const int64_t ntiles = (nchunks + kTile - 1) / kTile;
+  for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const int64_t tile = ntiles - 1 - t;
+#else
   for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
+#endif
     const int64_t first = tile * kTile + threadIdx.x;
     uint4 v[UNROLL];
     if ((tile + 1) * kTile <= nchunks) {

@@ -28,6 +28,9 @@
 namespace dtq {
 namespace {
 
+#ifndef DTQ_MX_AMAX_L2_KEEP_MB
+#define DTQ_MX_AMAX_L2_KEEP_MB 48
+#endif
 constexpr int kThreadsA = 256;
 constexpr int kUnrollA = 4;  // tied to the scale-byte mapping: lane & 3 picks the iteration
 
@@ -57,13 +60,24 @@ mx_amax_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int64_t kTile = int64_t(kThreadsA) * kUnrollA;
   uint32_t cand = 0;
+#if DTQ_MX_AMAX_L2_KEEP_MB
+  // The cast that follows reads the same input again, newest tiles first: the last tiles of this read are
+  // loaded under an L2 evict_last policy so that they are still there.
+  const uint64_t keep_policy = l2_policy_evict_last();
+  const int64_t keep_from = nchunks - (int64_t(DTQ_MX_AMAX_L2_KEEP_MB) << 20) / 16;
+#endif
   for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
     const int64_t warp_first = tile * kTile + int64_t(warp) * (32 * kUnrollA);
     uint4 v[kUnrollA];
 #pragma unroll
     for (int u = 0; u < kUnrollA; ++u) {
       const int64_t c = warp_first + u * 32 + lane;
+#if DTQ_MX_AMAX_L2_KEEP_MB
+      v[u] = c < nchunks ? (warp_first >= keep_from ? ldg_stream_hint(in + c, keep_policy) : ldg_stream(in + c))
+                         : make_uint4(0, 0, 0, 0);
+#else
       v[u] = c < nchunks ? ldg_stream(in + c) : make_uint4(0, 0, 0, 0);
+#endif
     }
     uint32_t my_scale_byte = 0;
 #pragma unroll
