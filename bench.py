@@ -221,6 +221,24 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
          note=f"same two outputs by cast + torch transpose + cast: {t2[0] * 1e3:.1f} us")
     del xs, outs, outs_t
 
+    # the shapes of the reference author's own benchmark (benchmarks/benchmark_saturated_casting.py:52-64),
+    # bf16 -> e4m3 and e5m2, N(0,1) values as there, the reference kernel timed beside each
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1000)
+    for (r, c) in [(512, 512), (1024, 1024), (2048, 2048), (1024, 8192), (8192, 1280), (8192, 7168), (3584, 8192),
+                   (2048, 109760), (1, 3232), (2048, 1), (14144, 2048)]:
+        xa = torch.randn(r, c, generator=gen, device=dev).to(torch.bfloat16)
+        ns = min(sets_for(xa.numel() * 3), 64)
+        xs = [xa.clone() for _ in range(ns)]
+        for dt_, name in ((E4M3, "e4m3"), (E5M2, "e5m2")):
+            sc = workloads.tensor_scale(xa, dt_)
+            outs = [torch.empty(xa.shape, dtype=dt_, device=dev) for _ in range(ns)]
+            t = timed(lambda i: _cabi.saturated_cast(xs[i], sc, dt_, out=outs[i]), ns, iters)
+            rt = timed(lambda i: ref.saturated_cast(xs[i], sc, dt_, False), ns, iters) if ref else None
+            line("author", f"saturated_cast->{name}", xa.shape, t, algorithmic_bytes("saturated_cast", r, c), rt)
+            del outs
+        del xs, xa
+
     # cfg2: amax + fused dynamic_scaled_quant bf16 [8192,8192], e4m3 and e5m2
     w = workloads.WORKLOADS["cfg2"]
     x = workloads.make_cfg2(device=dev)
@@ -251,8 +269,7 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
     ws_ = _cabi.workspace(dev)
 
     def dual(i):
-        _cabi.amax(xs[i], out=one, ws=ws_)
-        _cabi.cast_with_amax_transposed(xs[i], one, E4M3, out_t=outs_t[i], out=outs[i])
+        _cabi.dynamic_scaled_quant_dual(xs[i], E4M3, out=outs[i], out_t=outs_t[i], amax_out=one, ws=ws_)
 
     def twice(i):
         _cabi.dynamic_scaled_quant(xs[i], E4M3, out=outs[i], ws=ws_)
@@ -262,8 +279,8 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
     t2 = timed(twice, ns, iters)
     line("cfg2", "dynamic_scaled_quant_dual (amax, then x and x^T cast from one read)", x.shape, t,
          x.numel() * 4, None,
-         note=f"compulsory bytes N*(2+1+1); two launches move N*(2+2+1+1); the same two outputs by fused op + torch "
-              f"transpose + fused op: {t2[0] * 1e3:.1f} us")
+         note=f"compulsory bytes N*(2+1+1); two launches (the second started under the tail of the first) move "
+              f"N*(2+2+1+1); the same two outputs by fused op + torch transpose + fused op: {t2[0] * 1e3:.1f} us")
     del xs, outs, xf, outs_t
 
     # cfg3: mx_fp8_quantize bf16 [16384,8192]
@@ -324,25 +341,60 @@ def per_op_table(dev, peak, iters: int, warmup: int = 3):
     return rows
 
 
-# ---- CPU baselines -------------------------------------------------------------------------------------------
+# ---- CPU baselines and the oracle check of the timed buffers -------------------------------------------
 
-def cpu_sample(rows: int):
-    from driss_torch_b200 import workloads
+def load_workloads():
+    """The input generators (driss_torch_b200/workloads.py) loaded as a stand-alone module: importing the
+    package would load the CUDA libraries, which the CPU-only reference arm must not map."""
+    import importlib.util
 
-    return workloads.make_cfg5_chunk(0, rows=rows, cols=COLS)
+    spec = importlib.util.spec_from_file_location("dtq_workloads", ROOT / "driss_torch_b200" / "workloads.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    return mod
 
 
-def time_cpu_step(x, repeats: int):
-    """One 'step' of the workload on the CPU restatement: tensor-wise e4m3 quant + MX cast of x."""
-    from oracle import quant_oracle as qo
+def make_chunks_cpu(workloads, chunk_ids, chunk_rows: int):
+    """Row chunks of the workload from the CPU generator (the one source of the values for both arms, so their
+    output checksums are comparable); a few chunks at a time, since one chunk's generation is mostly serial."""
+    from concurrent.futures import ThreadPoolExecutor
 
-    best = float("inf")
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        qo.dynamic_scaled_quant(x, E4M3)
-        qo.mx_fp8_quantize(x)
-        best = min(best, time.perf_counter() - t0)
-    return best
+    with ThreadPoolExecutor(max_workers=min(4, max(1, len(chunk_ids)))) as pool:
+        return list(pool.map(lambda c: workloads.make_cfg5_chunk(c, rows=chunk_rows, cols=COLS), chunk_ids))
+
+
+class CpuStep:
+    """One step of the workload on the CPU restatement of the reference kernels (oracle/quant_oracle.c): the
+    tensor-wise e4m3 quantisation (amax over every chunk, then the cast) and the MX cast of a list of row chunks,
+    into preallocated output buffers."""
+
+    def __init__(self, chunks):
+        from oracle import quant_oracle as qo
+
+        self.qo, self.chunks = qo, chunks
+        self.payload = [torch.empty(c.shape, dtype=torch.uint8) for c in chunks]
+        self.mx_payload = [torch.empty(c.shape, dtype=torch.uint8) for c in chunks]
+        self.mx_scales = [torch.empty(c.numel() // 32, dtype=torch.uint8) for c in chunks]
+        self.amax, self.scale = 0.0, None
+
+    def run(self):
+        qo = self.qo
+        self.amax = max([0.0] + [qo.amax(c).item() for c in self.chunks])
+        for c, p, mp, ms in zip(self.chunks, self.payload, self.mx_payload, self.mx_scales):
+            _, self.scale = qo.cast_with_amax(c, self.amax, E4M3, out=p)
+            qo.mx_fp8_quantize(c, payload=mp, scales=ms)
+
+    def time(self, repeats: int) -> float:
+        best = float("inf")
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            self.run()
+            best = min(best, time.perf_counter() - t0)
+        return best
+
+    def checksums(self):
+        return [sum(int(t.sum(dtype=torch.int64)) for t in ts) for ts in (self.payload, self.mx_payload, self.mx_scales)]
 
 
 def time_cpu_eager(x, repeats: int):
@@ -362,51 +414,82 @@ def step_bytes(rows: int) -> int:
     return algorithmic_bytes("dynamic_scaled_quant", rows, COLS) + algorithmic_bytes("mx_fp8_quantize", rows, COLS)
 
 
-def cpu_baseline(sample_rows: int = 32768):
+def oracle_check_and_cpu_baseline(x, payload, mx_payload, mx_scales, amax, scale, check_rows: int, chunk_rows: int,
+                                  whole_matrix: bool, time_it: bool):
+    """After the timed region: the first `check_rows` rows of the buffers the benchmark just timed (the input as it
+    sits on the device, and the three outputs) against the C oracle, byte for byte; `whole_matrix` says that
+    these rows are the entire matrix, in which case the oracle derives the amax itself and its byte sums are the
+    reference for `output_checksums`.  The same oracle run is the CPU baseline (`time_it`: best of 2 more runs)."""
     from oracle import quant_oracle as qo
 
-    x = cpu_sample(sample_rows)
-    threads = qo.num_threads()
-    t = time_cpu_step(x, repeats=3)
-    te = time_cpu_eager(x, repeats=2)
-    nbytes = step_bytes(sample_rows)
-    return {"value": round(nbytes / t / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"first {sample_rows} rows of the workload = row chunk 0 ({sample_rows}x{COLS} bf16, 1/8 of the matrix), best of 3; "
-                      "oracle/quant_oracle.c with OpenMP",
-            "eager_value": round(nbytes / te / 1e9, 3), "eager_cores": torch.get_num_threads(),
-            "eager_note": "the reference tests' PyTorch-eager formulas (oracle/eager.py) on the same sample, best of 2"}
+    qo.set_num_threads(os.cpu_count() or 1)  # torchrun pins OMP_NUM_THREADS=1 for its children
+    bpr = COLS // 32
+    spans = [(r0, min(check_rows, r0 + chunk_rows)) for r0 in range(0, check_rows, chunk_rows)]
+    step = CpuStep([x[r0:r1].cpu() for r0, r1 in spans])
+    gpu_amax, gpu_scale = float(amax.item()), float(scale.item())
+    step.run()
+    if not whole_matrix:  # a part of the matrix cannot know the global amax: take the device's, check it is no smaller
+        assert step.amax <= gpu_amax
+        step.amax = gpu_amax
+        for c, p in zip(step.chunks, step.payload):
+            _, step.scale = qo.cast_with_amax(c, gpu_amax, E4M3, out=p)
+    equal = step.amax == gpu_amax and float(step.scale.item()) == gpu_scale
+    differing = 0
+    for (r0, r1), p, mp, ms in zip(spans, step.payload, step.mx_payload, step.mx_scales):
+        differing += int((payload[r0:r1].view(torch.uint8).cpu() != p).sum())
+        differing += int((mx_payload[r0:r1].view(torch.uint8).cpu() != mp).sum())
+        differing += int((mx_scales[r0 * bpr:r1 * bpr].view(torch.uint8).cpu() != ms).sum())
+    parity = {"rows": check_rows, "whole_matrix": whole_matrix, "bytes_equal": bool(equal and differing == 0),
+              "bytes_differing": differing, "amax_equal": step.amax == gpu_amax,
+              "checker": "oracle/quant_oracle.c on the timed input as downloaded from the device"}
+    if whole_matrix:
+        parity["oracle_checksums"] = step.checksums()
+    cpu = None
+    if time_it:
+        t = step.time(repeats=2)
+        sample_rows = min(check_rows, 32768)
+        te = time_cpu_eager(step.chunks[0][:sample_rows], repeats=2)
+        cpu = {"value": round(step_bytes(check_rows) / t / 1e9, 3), "unit": "GB/s", "cores": qo.num_threads(),
+               "kind": "port",
+               "sample": f"{check_rows}x{COLS} bf16 rows (" + ("the whole matrix" if whole_matrix else "rank 0's first rows")
+                         + "), best of 2; oracle/quant_oracle.c with OpenMP",
+               "eager_value": round(step_bytes(sample_rows) / te / 1e9, 3), "eager_cores": torch.get_num_threads(),
+               "eager_note": f"the reference tests' PyTorch-eager formulas (oracle/eager.py) on the first {sample_rows} rows, best of 2"}
+    return parity, cpu
 
 
 def run_reference_arm(args, rank: int):
-    """CPU restatement of the reference on a bounded sample per step (rank 0 only)."""
+    """CPU restatement of the reference kernels on the whole matrix, every step (rank 0 only; no CUDA library
+    is loaded in this process)."""
     if rank != 0:
         return
     from oracle import quant_oracle as qo
 
+    workloads = load_workloads()
     # torchrun pins OMP_NUM_THREADS=1 for its children; this arm is meant to use every host core
     qo.set_num_threads(os.cpu_count() or 1)
-    sample_rows = 16384
-    x = cpu_sample(sample_rows)
+    chunk_rows = args.rows // TOTAL_CHUNKS
+    step = CpuStep(make_chunks_cpu(workloads, list(range(TOTAL_CHUNKS)), chunk_rows))
     for _ in range(args.warmup):
-        time_cpu_step(x, 1)
+        step.run()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        time_cpu_step(x, 1)
+        step.run()
     dt_ = (time.perf_counter() - t0) / args.steps
-    value = step_bytes(sample_rows) / dt_ / 1e9
-    sample = f"{sample_rows}x{COLS} bf16 rows of chunk 0 per step (1/{TOTAL_ROWS // sample_rows} of the matrix)"
+    value = step_bytes(args.rows) / dt_ / 1e9
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt_ * 1e3, 3), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16->fp8 (f64 scale arithmetic)", "data": "synthetic",
-        "config": {"workload": f"cfg5: bf16 [{TOTAL_ROWS},{COLS}] row-sharded over {args.gpus} GPU(s); tensor-wise e4m3 "
+        "config": {"workload": f"cfg5: bf16 [{args.rows},{COLS}] row-sharded over {args.gpus} GPU(s); tensor-wise e4m3 "
                                "quant (amax -> max all-reduce -> cast) + MX block-32 cast",
-                   "sample": sample, "what_runs": "CPU restatement of the reference kernels (oracle/quant_oracle.c, "
-                   "OpenMP); the reference itself is CUDA-only and has no CPU implementation"},
+                   "what_runs": "CPU restatement of the reference kernels (oracle/quant_oracle.c, OpenMP, every host "
+                                "core) on the whole matrix every step; the reference itself is CUDA-only and has no "
+                                "CPU implementation"},
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": qo.num_threads(), "kind": "port",
-                         "sample": sample},
+                         "sample": f"the whole {args.rows}x{COLS} bf16 matrix every step"},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "output_checksums": step.checksums(), "gpu_launches": 0,
     }), flush=True)
 
 
@@ -465,7 +548,12 @@ def main():
         print(json.dumps({"ops": per_op_table(dev, peak, iters=iters, warmup=min(3, iters))}), flush=True)
         return
     chunk_rows = args.rows // TOTAL_CHUNKS
-    x = workloads.make_cfg5_shard(rank, world, chunk_rows=chunk_rows, cols=COLS, device=dev)
+    # generated by the CPU generator and uploaded: the reference arm generates the same values
+    per_rank = TOTAL_CHUNKS // world
+    x = torch.empty(per_rank * chunk_rows, COLS, dtype=torch.bfloat16, device=dev)
+    for i, part in enumerate(make_chunks_cpu(workloads, list(range(rank * per_rank, (rank + 1) * per_rank)), chunk_rows)):
+        x[i * chunk_rows:(i + 1) * chunk_rows].copy_(part)
+    del part
     rows_local = x.shape[0]
     payload = torch.empty(x.shape, dtype=E4M3, device=dev)
     mx_payload = torch.empty(x.shape, dtype=E4M3, device=dev)
@@ -567,15 +655,26 @@ def main():
         sampler.start()
         time.sleep(0.25)
     barrier()
-    events = []
+    # The timed region has no event between the kernels of a step: an event there would make each launch wait
+    # for the previous kernel to drain, and the step relies on programmatic dependent launch (the finishing warp
+    # and the cast become resident under the tail of the kernel before them).
     t_start, t_end = event_pair()
     t_start.record()
     for _ in range(args.steps):
-        step(events)
+        step()
     t_end.record()
     barrier()
     elapsed_ms = t_start.elapsed_time(t_end)
     clocks = sampler.stop() if rank == 0 else None
+    # per-kernel durations: the same K steps once more, now with an event after every kernel
+    events = []
+    m_start, m_end = event_pair()
+    m_start.record()
+    for _ in range(args.steps):
+        step(events)
+    m_end.record()
+    barrier()
+    marked_ms_per_step = m_start.elapsed_time(m_end) / args.steps
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -598,6 +697,15 @@ def main():
     if world > 1:
         dist.all_reduce(check)
     status = _cabi.workspace_status(ws)
+
+    # the timed buffers against the oracle, outside the timed region: the whole matrix at N == 1, rank 0's first
+    # chunk otherwise (the other ranks' outputs are covered by the checksums, which the reference arm also prints)
+    parity, cpu = None, None
+    if rank == 0 and not args.no_cpu:
+        parity, cpu = oracle_check_and_cpu_baseline(
+            x, payload, mx_payload, mx_scales, amax, scale, check_rows=rows_local if world == 1 else chunk_rows,
+            chunk_rows=chunk_rows, whole_matrix=world == 1, time_it=world == 1)
+    barrier()
 
     total_rows = args.rows
     tw_bytes = algorithmic_bytes("dynamic_scaled_quant", total_rows, COLS)
@@ -683,15 +791,35 @@ def main():
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         wall = tt.item()
+        e2e_sums = [t_.view(torch.uint8).sum(dtype=torch.int64) for t_ in (ph, mph, msh)]
+        # the PCIe bound of the same pipeline: the same pinned buffers, chunks, streams and dependencies, no kernels
+        copy_outs = host_outs[e2e_steps % 2]
+        hq.wait(hq.submit(xh, *copy_outs, copies_only=True))
+        barrier()
+        t0 = time.perf_counter()
+        prev = None
+        for i in range(e2e_steps):
+            ticket = hq.submit(xh, *copy_outs, copies_only=True)
+            if prev is not None:
+                hq.wait(prev)
+            prev = ticket
+        hq.wait(prev)
+        barrier()
+        copy_wall = (time.perf_counter() - t0) / e2e_steps
+        tt = torch.tensor([copy_wall], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        copy_wall = tt.item()
         h2d = x.numel() * 2
         d2h = x.numel() * 2 + x.numel() // 32
         e2e = {"value": round((tw_bytes + mx_bytes) / wall / 1e9, 2), "unit": "GB/s", "ms_per_step": round(wall * 1e3, 3),
                "steps": e2e_steps, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
                "launches_per_step": hq.launches,
+               "copy_bound_ms": round(copy_wall * 1e3, 3), "frac_of_copy_bound": round(copy_wall / wall, 4),
+               "copy_bound_note": "the same pinned buffers, chunks, three streams and dependencies with the kernels left "
+                                  "out: what the host<->device copies alone take per step",
                "api": "driss_torch_b200.host_pipeline.HostQuantizer.submit/wait, two matrices in flight (pinned host tensors in and out)"}
-        e2e_check = torch.stack([ph.view(torch.uint8).sum(dtype=torch.int64),
-                                 mph.view(torch.uint8).sum(dtype=torch.int64),
-                                 msh.view(torch.uint8).sum(dtype=torch.int64)]).to(dev)
+        e2e_check = torch.stack(e2e_sums).to(dev)
         if world > 1:
             dist.all_reduce(e2e_check)
         e2e["matches_device_run"] = bool(torch.equal(e2e_check, check))
@@ -717,7 +845,11 @@ def main():
             "bytes_per_step": tw_bytes + mx_bytes,
             "frac_of_measured_peak": round(value / (peak * world), 4),
             "frac_of_nominal_8TBps": round(value / (NOMINAL_HBM_GBS * world), 4),
-            "roofline": roofline, "kernels": kernels, "clocks": clocks,
+            "roofline": roofline, "kernels": kernels,
+            "kernels_note": "per-kernel ms: a second pass of the same steps with an event after every kernel, which "
+                            f"serialises the launches ({marked_ms_per_step:.4f} ms per step that way); the timed region "
+                            "has no events inside a step",
+            "clocks": clocks,
             "gpu_launches": my_launches_per_step * args.steps,
             "device_status": status, "output_checksums": check.tolist(),
         }
@@ -727,8 +859,10 @@ def main():
             out["e2e"] = e2e
         if ops is not None:
             out["ops"] = ops
-        if not args.no_cpu and world == 1:
-            out["cpu_baseline"] = cpu_baseline()
+        if parity is not None:
+            out["parity_checked"] = parity
+        if cpu is not None:
+            out["cpu_baseline"] = cpu
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()

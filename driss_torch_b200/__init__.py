@@ -85,7 +85,13 @@ def mx_fp8_quantize(
 
     bf16 input with e4m3 payload is the reference's kernel, bit for bit.  fp16 / fp32 inputs and
     ``ScalarType=torch.float8_e5m2`` (which the reference accepts but computes as bf16 -> e4m3) use
-    the same scale rule with the format's own largest exponent (15 for e5m2)."""
+    the same scale rule with the format's own largest exponent (15 for e5m2).
+
+    ``axis`` / ``transpose`` (declared and ignored by the reference, src/mx_cast.cu:168-171; bf16 -> e4m3,
+    both dimensions multiples of 32): ``transpose=True`` returns ``mx_fp8_quantize(input.t().contiguous())``
+    -- payload [N, M], one scale per 32 rows of a column of ``input`` -- from one read of ``input``;
+    ``axis=0`` returns the same bytes with the payload viewed as [M, N]; both together give the ordinary
+    blocks with the payload viewed as [N, M]."""
     return ops.mx_fp8_quantize(input, block_size, axis, transpose, ScalarType)
 
 

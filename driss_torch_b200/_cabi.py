@@ -7,6 +7,7 @@ below only unwrap ``data_ptr()`` of CUDA tensors and raise on a non-zero status.
 from __future__ import annotations
 
 import ctypes as C
+import functools
 from pathlib import Path
 
 import torch
@@ -26,6 +27,8 @@ SIGNATURES = {
     "dtq_workspace_bytes": ([], _sz),
     "dtq_workspace_init": ([_vp, _sz, _vp], _i32),
     "dtq_workspace_status": ([_vp, _vp, _vp], _i32),
+    "dtq_workspace_status_async": ([_vp, _vp, _vp], _i32),
+    "dtq_dynamic_scaled_quant_dual": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp, _sz, _vp], _i32),
     "dtq_saturated_cast": ([_vp, _vp, _vp, _i64, _i32, _i32, _vp], _i32),
     "dtq_cast_with_amax_transposed": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_saturated_cast_transposed": ([_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
@@ -77,8 +80,20 @@ def check(status: int, what: str) -> None:
         raise DtqError(what, status)
 
 
-def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+def _stream(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _on_device_of_first_tensor(fn):
+    """The C ABI launches on the CURRENT device: make the first argument's device current for the call, so
+    that its current stream and the workspace cached for that stream are the ones used."""
+
+    @functools.wraps(fn)
+    def wrapper(x, *args, **kwargs):
+        with torch.cuda.device(x.device):
+            return fn(x, *args, **kwargs)
+
+    return wrapper
 
 
 def _ptr(t):
@@ -91,22 +106,34 @@ _workspaces: dict = {}
 def workspace(device=None) -> torch.Tensor:
     """A zero-initialised workspace for the current stream of ``device`` (cached)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    key = (device.index, _stream())
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    key = (device.index, _stream(device))
     ws = _workspaces.get(key)
     if ws is None:
         lib = load()
-        ws = torch.empty(lib.dtq_workspace_bytes(), dtype=torch.uint8, device=device)
-        check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), _stream()), "dtq_workspace_init")
+        with torch.cuda.device(device):
+            ws = torch.empty(lib.dtq_workspace_bytes(), dtype=torch.uint8, device=device)
+            check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), _stream(device)), "dtq_workspace_init")
         _workspaces[key] = ws
     return ws
 
 
+@_on_device_of_first_tensor
 def workspace_status(ws: torch.Tensor) -> int:
+    """The workspace's sticky status word (0 = no bounded wait ever gave up); synchronises the stream."""
     out = C.c_int(0)
     check(load().dtq_workspace_status(ws.data_ptr(), C.addressof(out), _stream()), "dtq_workspace_status")
     return out.value
 
 
+@_on_device_of_first_tensor
+def workspace_status_async(ws: torch.Tensor, status_host: torch.Tensor) -> None:
+    """Enqueues the copy of the status word into ``status_host`` (a pinned int32 tensor); no synchronisation."""
+    check(load().dtq_workspace_status_async(ws.data_ptr(), status_host.data_ptr(), _stream()), "dtq_workspace_status_async")
+
+
+@_on_device_of_first_tensor
 def saturated_cast(x: torch.Tensor, scale: torch.Tensor, out_dtype: torch.dtype, out: torch.Tensor | None = None):
     out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
     check(
@@ -117,6 +144,7 @@ def saturated_cast(x: torch.Tensor, scale: torch.Tensor, out_dtype: torch.dtype,
     return out
 
 
+@_on_device_of_first_tensor
 def amax(x: torch.Tensor, out: torch.Tensor | None = None, ws: torch.Tensor | None = None):
     out = torch.empty(1, dtype=torch.float32, device=x.device) if out is None else out
     ws = workspace(x.device) if ws is None else ws
@@ -127,6 +155,7 @@ def amax(x: torch.Tensor, out: torch.Tensor | None = None, ws: torch.Tensor | No
     return out
 
 
+@_on_device_of_first_tensor
 def amax_static_scratch(x: torch.Tensor, out: torch.Tensor | None = None):
     """amax through the entry point that allocates nothing (scratch inside the library image)."""
     out = torch.empty(1, dtype=torch.float32, device=x.device) if out is None else out
@@ -135,6 +164,7 @@ def amax_static_scratch(x: torch.Tensor, out: torch.Tensor | None = None):
     return out
 
 
+@_on_device_of_first_tensor
 def dynamic_scaled_quant(x, out_dtype, out=None, amax_out=None, scale_out=None, ws=None):
     out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
     ws = workspace(x.device) if ws is None else ws
@@ -146,6 +176,7 @@ def dynamic_scaled_quant(x, out_dtype, out=None, amax_out=None, scale_out=None, 
     return out
 
 
+@_on_device_of_first_tensor
 def dynamic_scaled_quant_p2p(x, out_dtype, peer_ptrs, rank, epoch, out=None, amax_out=None, scale_out=None, ws=None,
                              spin_limit=0):
     """One launch per GPU of a row-sharded tensor; ``peer_ptrs[r]`` addresses rank r's exchange buffer."""
@@ -162,6 +193,7 @@ def dynamic_scaled_quant_p2p(x, out_dtype, peer_ptrs, rank, epoch, out=None, ama
     return out
 
 
+@_on_device_of_first_tensor
 def cast_with_amax(x, amax_value, out_dtype, out=None, scale_out=None):
     out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
     check(
@@ -172,6 +204,7 @@ def cast_with_amax(x, amax_value, out_dtype, out=None, scale_out=None):
     return out
 
 
+@_on_device_of_first_tensor
 def dynamic_scaled_quant_rowwise(x, out_dtype, out=None, amax_out=None, scale_out=None):
     rows, cols = x.shape
     out = torch.empty(x.shape, dtype=out_dtype, device=x.device) if out is None else out
@@ -183,6 +216,7 @@ def dynamic_scaled_quant_rowwise(x, out_dtype, out=None, amax_out=None, scale_ou
     return out
 
 
+@_on_device_of_first_tensor
 def mx_fp8_quantize(x, payload=None, scales=None):
     rows, cols = x.shape
     payload = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device) if payload is None else payload
@@ -192,6 +226,7 @@ def mx_fp8_quantize(x, payload=None, scales=None):
     return payload, scales
 
 
+@_on_device_of_first_tensor
 def mx_fp8_quantize_blocked(x, payload=None, scales=None):
     """MX cast with the scales in the blocked layout of the consumer GEMM (zero-filled padding)."""
     rows, cols = x.shape
@@ -204,6 +239,7 @@ def mx_fp8_quantize_blocked(x, payload=None, scales=None):
     return payload, scales
 
 
+@_on_device_of_first_tensor
 def mx_fp8_quantize_tma(x, payload=None, scales=None, status=None):
     """The shared-memory-staged (TMA bulk copy) variant of the MX cast; same outputs."""
     rows, cols = x.shape
@@ -215,6 +251,7 @@ def mx_fp8_quantize_tma(x, payload=None, scales=None, status=None):
     return payload, scales, status
 
 
+@_on_device_of_first_tensor
 def mx_fp8_quantize_dual(x, payload=None, scales=None, payload_t=None, scales_t=None, blocked=False):
     """MX cast of x and of its transpose from one read of x; ``blocked``: scales in the MX GEMM's layout."""
     rows, cols = x.shape
@@ -237,6 +274,7 @@ def mx_fp8_quantize_dual(x, payload=None, scales=None, payload_t=None, scales_t=
     return payload, scales, payload_t, scales_t
 
 
+@_on_device_of_first_tensor
 def saturated_cast_transposed(x, scale, out_dtype, out_t=None, out=None, both=False):
     """The cast of x transposed ([cols, rows]); with ``both`` (or ``out``) also the cast of x itself."""
     rows, cols = x.shape
@@ -253,6 +291,7 @@ MX_IN_CODE = {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}
 MX_FMT_CODE = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1, torch.float4_e2m1fn_x2: 2, "e2m1": 2}
 
 
+@_on_device_of_first_tensor
 def mx_quantize(x, elem, payload=None, scales=None):
     """MX block-32 cast of bf16 / fp16 / fp32 to e4m3 / e5m2 (payload [M, N]) or e2m1 (uint8 [M, N/2])."""
     rows, cols = x.shape
@@ -266,6 +305,7 @@ def mx_quantize(x, elem, payload=None, scales=None):
     return payload, scales
 
 
+@_on_device_of_first_tensor
 def mx_fp8_quantize_amax(x, payload=None, scales=None, amax_out=None, ws=None, peer_ptrs=None, rank=0, epoch=0,
                          spin_limit=0):
     """MX cast + the tensor's amax (>= 0) from one read; with ``peer_ptrs`` the amax is exchanged with the
@@ -287,6 +327,7 @@ def mx_fp8_quantize_amax(x, payload=None, scales=None, amax_out=None, ws=None, p
     return payload, scales, amax_out
 
 
+@_on_device_of_first_tensor
 def cast_with_amax_transposed(x, amax_value, out_dtype, out_t=None, out=None, both=False, scale_out=None):
     """The dynamic cast of x transposed ([cols, rows]) for a device-resident amax; with ``both`` (or ``out``)
     also the cast of x itself."""
@@ -298,3 +339,16 @@ def cast_with_amax_transposed(x, amax_value, out_dtype, out_t=None, out=None, bo
                                                amax_value.data_ptr(), _ptr(scale_out), rows, cols, IN_CODE[x.dtype],
                                                OUT_CODE[out_dtype], _stream()), "dtq_cast_with_amax_transposed")
     return (out, out_t) if out is not None else out_t
+
+
+@_on_device_of_first_tensor
+def dynamic_scaled_quant_dual(x, out_dtype, out=None, out_t=None, amax_out=None, scale_out=None, ws=None):
+    """Tensor-wise dynamic quantisation of x into both orientations: (payload [rows, cols], payload_t [cols, rows])."""
+    rows, cols = x.shape
+    out = torch.empty(rows, cols, dtype=out_dtype, device=x.device) if out is None else out
+    out_t = torch.empty(cols, rows, dtype=out_dtype, device=x.device) if out_t is None else out_t
+    ws = workspace(x.device) if ws is None else ws
+    check(load().dtq_dynamic_scaled_quant_dual(x.data_ptr(), out.data_ptr(), out_t.data_ptr(), _ptr(amax_out), _ptr(scale_out),
+                                               rows, cols, IN_CODE[x.dtype], OUT_CODE[out_dtype], ws.data_ptr(), ws.numel(),
+                                               _stream()), "dtq_dynamic_scaled_quant_dual")
+    return out, out_t

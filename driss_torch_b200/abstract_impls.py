@@ -11,6 +11,8 @@ from torch.library import register_fake
 
 @register_fake("DrissTorch::saturated_cast")
 def saturated_cast_meta(x: torch.Tensor, scale: torch.Tensor, out_dtype: torch.dtype, transpose: bool = False):
+    if transpose:
+        return torch.empty((x.shape[1], x.shape[0]), dtype=out_dtype, device=x.device)
     return torch.empty_like(x, dtype=out_dtype)
 
 
@@ -27,9 +29,14 @@ def dynamic_scaled_quant_meta(x: torch.Tensor, dtype: torch.dtype):
 @register_fake("DrissTorch::mx_fp8_quantize")
 def mx_fp8_quantize_meta(x: torch.Tensor, block_size: int, axis: int, transpose: bool, fp8_type: torch.dtype):
     m, n = x.shape
+    along_rows = axis in (0, -2)
+    if along_rows != transpose:  # blocks down the columns: the transposing kernel's outputs
+        payload_t = torch.empty((n, m), dtype=fp8_type, device=x.device)
+        scales_t = torch.empty(n * (m // 32), dtype=torch.float8_e8m0fnu, device=x.device)
+        return (payload_t if transpose else payload_t.t()), scales_t
     payload = torch.empty_like(x, dtype=fp8_type)
     scales = torch.empty(m * ((n + 31) // 32), dtype=torch.float8_e8m0fnu, device=x.device)
-    return payload, scales
+    return (payload.t() if transpose else payload), scales
 
 
 @register_fake("DrissTorch::dynamic_scaled_quant_with_scale")

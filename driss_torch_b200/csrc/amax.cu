@@ -15,16 +15,9 @@
 
 namespace dtq {
 
-#ifndef DTQ_AMAX_UNROLL
-#define DTQ_AMAX_UNROLL 8
-#endif
-#ifndef DTQ_AMAX_BLOCKS_PER_SM
-#define DTQ_AMAX_BLOCKS_PER_SM 4
-#endif
-#ifndef DTQ_AMAX_THREADS
-#define DTQ_AMAX_THREADS 512
-#endif
-constexpr int kAmaxThreads = DTQ_AMAX_THREADS;
+constexpr int kAmaxUnroll = 8;       // 128-bit loads in flight per thread
+constexpr int kAmaxBlocksPerSm = 4;  // persistent grid: blocks per SM
+constexpr int kAmaxThreads = 512;
 
 template <int IN>
 struct AbsMax;
@@ -92,6 +85,7 @@ amax_kernel(const void *__restrict__ in, float *__restrict__ out, int64_t numel,
   __shared__ float smem32[32];
   __shared__ int flag;
   constexpr int kElems = 16 / AbsMax<IN>::kElemBytes;
+  pdl_launch_dependents();  // a cast queued behind this launch with launch_after_dependency may become resident early
   const float identity = -INFINITY;
   AbsMax<IN> acc(identity);
 
@@ -115,8 +109,8 @@ amax_kernel(const void *__restrict__ in, float *__restrict__ out, int64_t numel,
 }
 
 int amax_grid(int64_t numel, int elem_bytes, const DeviceInfo &dev) {
-  const int64_t tiles = ceil_div64(numel * elem_bytes / 16, int64_t(kAmaxThreads) * DTQ_AMAX_UNROLL);
-  const int64_t max_grid = int64_t(dev.sm_count) * DTQ_AMAX_BLOCKS_PER_SM;
+  const int64_t tiles = ceil_div64(numel * elem_bytes / 16, int64_t(kAmaxThreads) * kAmaxUnroll);
+  const int64_t max_grid = int64_t(dev.sm_count) * kAmaxBlocksPerSm;
   return balanced_grid(tiles, max_grid);
 }
 
@@ -133,9 +127,9 @@ int launch_amax(const void *in, float *out, int64_t numel, int in_dtype, Workspa
   const int grid = amax_grid(numel, eb, dev);
   const int64_t head = head_elems(in, eb, numel);
   if (in_dtype == DTQ_BF16)
-    amax_kernel<DTQ_BF16, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+    amax_kernel<DTQ_BF16, kAmaxUnroll><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
   else
-    amax_kernel<DTQ_F32, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+    amax_kernel<DTQ_F32, kAmaxUnroll><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
   return cuda_status(cudaGetLastError());
 }
 
@@ -165,7 +159,7 @@ extern "C" int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype,
 // In host code the array's NAME is only a host-side handle, not a device address, so the address
 // is looked up once per device with cudaGetSymbolAddress (with that device current) and cached.
 // One block per tile is launched, so the array's kMaxGridBlocks partial slots bound the input:
-// kMaxGridBlocks tiles of kAmaxThreads * DTQ_AMAX_UNROLL 16-byte chunks = DTQ_AMAX_STATIC_MAX_BYTES.
+// kMaxGridBlocks tiles of kAmaxThreads * kAmaxUnroll 16-byte chunks = DTQ_AMAX_STATIC_MAX_BYTES.
 namespace dtq {
 namespace {
 
@@ -199,7 +193,7 @@ int static_scratch_address(Workspace **ws) {
 
 extern "C" int dtq_amax_static_scratch(const void *in, float *out, int64_t numel, int in_dtype, void *stream) {
   using namespace dtq;
-  static_assert(int64_t(kMaxGridBlocks) * kAmaxThreads * DTQ_AMAX_UNROLL * 16 == DTQ_AMAX_STATIC_MAX_BYTES,
+  static_assert(int64_t(kMaxGridBlocks) * kAmaxThreads * kAmaxUnroll * 16 == DTQ_AMAX_STATIC_MAX_BYTES,
                 "the documented limit must match the scratch array");
   if (numel < 0 || !out || (numel > 0 && !in)) return DTQ_ERR_INVALID_ARGUMENT;
   if (in_dtype != DTQ_BF16 && in_dtype != DTQ_F32) return DTQ_ERR_UNSUPPORTED_DTYPE;
@@ -211,12 +205,12 @@ extern "C" int dtq_amax_static_scratch(const void *in, float *out, int64_t numel
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The array keeps whatever the previous call left: start the arrival counter from zero.
   DTQ_CUDA_TRY(cudaMemsetAsync(&ws->arrivals, 0, sizeof(ws->arrivals), st));
-  const int64_t tiles = ceil_div64(numel * eb / 16, int64_t(kAmaxThreads) * DTQ_AMAX_UNROLL);
+  const int64_t tiles = ceil_div64(numel * eb / 16, int64_t(kAmaxThreads) * kAmaxUnroll);
   const int grid = static_cast<int>(tiles < 1 ? 1 : tiles);  // <= kMaxGridBlocks by the size check
   const int64_t head = head_elems(in, eb, numel);
   if (in_dtype == DTQ_BF16)
-    amax_kernel<DTQ_BF16, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+    amax_kernel<DTQ_BF16, kAmaxUnroll><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
   else
-    amax_kernel<DTQ_F32, DTQ_AMAX_UNROLL><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
+    amax_kernel<DTQ_F32, kAmaxUnroll><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
   return cuda_status(cudaGetLastError());
 }

@@ -58,6 +58,13 @@ extern "C" int dtq_workspace_init(void *workspace, size_t workspace_bytes, void 
   return dtq::cuda_status(cudaMemsetAsync(workspace, 0, sizeof(dtq::Workspace), static_cast<cudaStream_t>(stream)));
 }
 
+extern "C" int dtq_workspace_status_async(const void *workspace, int *status_host, void *stream) {
+  if (!workspace || !status_host) return DTQ_ERR_INVALID_ARGUMENT;
+  const dtq::Workspace *ws = static_cast<const dtq::Workspace *>(workspace);
+  return dtq::cuda_status(cudaMemcpyAsync(status_host, &ws->status, sizeof(int), cudaMemcpyDeviceToHost,
+                                          static_cast<cudaStream_t>(stream)));
+}
+
 extern "C" int dtq_workspace_status(const void *workspace, int *status_host, void *stream) {
   if (!workspace || !status_host) return DTQ_ERR_INVALID_ARGUMENT;
   const dtq::Workspace *ws = static_cast<const dtq::Workspace *>(workspace);

@@ -53,6 +53,18 @@ __device__ __forceinline__ void stg_stream(void *p, uint4 v) {
                : "memory");
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// Two kernels queued back to back on one stream normally run strictly one after the other: the
+// second is launched when the first has drained.  A kernel launched with the programmatic-
+// serialization attribute (launch_after_dependency in dtq_host.h) may instead become resident as
+// soon as every block of its predecessor has executed pdl_launch_dependents (or exited); it must
+// then execute pdl_wait before it touches anything the predecessor reads or writes: the wait
+// returns when the predecessor has completed and its memory operations are visible.  Launch
+// latency and the ramp of the second kernel hide under the tail of the first.  Both instructions
+// are no-ops in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- number formats --------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }

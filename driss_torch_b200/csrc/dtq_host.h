@@ -46,6 +46,25 @@ inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? DTQ_OK : DTQ_E
     if (_e != cudaSuccess) return dtq::cuda_status(_e); \
   } while (0)
 
+// Launches `kernel` so that it may start while the kernel queued before it on `st` is still
+// draining (programmatic dependent launch).  The kernel must call pdl_wait() before its first
+// access to memory that its predecessor on the stream may read or write.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after_dependency(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem_bytes,
+                                           cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned_to(const void *p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }

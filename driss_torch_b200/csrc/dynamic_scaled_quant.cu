@@ -40,49 +40,23 @@ int launch_amax(const void *in, float *out, int64_t numel, int in_dtype, Workspa
 
 namespace {
 
-#ifndef DTQ_DSQ_UNROLL
-#define DTQ_DSQ_UNROLL 4
-#endif
-#ifndef DTQ_DSQ_COOP
-#define DTQ_DSQ_COOP 1
-#endif
+constexpr int kUnroll = 4;  // 128-bit loads in flight per thread, all kernels of this file
 // The fused kernel: threads per block, resident blocks per SM it is sized for, and how many
-// tiles (of FUSED_THREADS * UNROLL 16-byte chunks) a block keeps in shared memory.
-#ifndef DTQ_FUSED_THREADS
-#define DTQ_FUSED_THREADS 512
-#endif
-#ifndef DTQ_FUSED_BLOCKS_PER_SM
-#define DTQ_FUSED_BLOCKS_PER_SM 2
-#endif
-#ifndef DTQ_FUSED_SMEM_TILES
-#define DTQ_FUSED_SMEM_TILES 3
-#endif
-// 1: a block's first tile stays in registers across the barrier (one more tile kept on chip,
-// 4 * UNROLL registers per thread); 0: only shared memory keeps tiles.
-#ifndef DTQ_FUSED_KEEP_REGS
-#define DTQ_FUSED_KEEP_REGS 1
-#endif
-// 1: the second pass holds two tiles in registers (next tile's loads in flight while the current
-// one is converted); 0: one tile, overlap comes from the other warps.  Measured on B200: 1 is 1 %
-// faster at 4 GiB, 4 % slower at 128 MiB (register pressure), so 0.
+// tiles (of kFusedThreads * kUnroll 16-byte chunks) a block keeps in shared memory at most.
+constexpr int kFusedThreads = 512;
+constexpr int kFusedBlocksPerSm = 2;
+constexpr int kFusedSmemTiles = 3;
+// A block's first tile stays in registers across the barrier: one more tile kept on chip for
+// 4 * kUnroll registers per thread.
+constexpr int kFusedRegTiles = 1;
 // Inputs above this many bytes are quantised as amax kernel + cast kernel instead of the single
 // fused launch: what the chip can keep between the two looks (about 140 MB) no longer matters at
 // that size, and the two stream kernels run at higher occupancy than the persistent fused one
 // (measured at 512 MiB: 199 us against 209 us; at 128 MiB the fused launch wins 48 us to 60 us).
-#ifndef DTQ_FUSED_MAX_BYTES
-#define DTQ_FUSED_MAX_BYTES (int64_t(320) << 20)
-#endif
-#ifndef DTQ_FUSED_PIPELINE
-#define DTQ_FUSED_PIPELINE 0
-#endif
-#ifndef DTQ_DSQ_THREADS
-#define DTQ_DSQ_THREADS 256
-#endif
-// Grid cap of the stand-alone cast kernel; default "no cap" (one tile per block), see saturated_cast.cu.
-#ifndef DTQ_CAST_BLOCKS_PER_SM
-#define DTQ_CAST_BLOCKS_PER_SM (1 << 20)
-#endif
-constexpr int kThreads = DTQ_DSQ_THREADS;
+constexpr int64_t kFusedMaxBytes = int64_t(320) << 20;
+// The stand-alone cast kernel: one tile per block (no grid cap), see saturated_cast.cu.
+constexpr int kThreads = 256;
+constexpr int64_t kCastBlocksPerSmCap = 1 << 20;
 
 // ---- per-chunk arithmetic ----------------------------------------------------------------------
 // BOUNDED: |x| <= amax is guaranteed (amax was computed from the same data in this launch).
@@ -129,21 +103,12 @@ struct DsqChunk<DTQ_F32, OUT, BOUNDED> {
 // Requires `in` 16-byte aligned and `out` aligned for the packed store; numel may be anything
 // (block 0 handles the elements past the last whole chunk).  Dynamic shared memory holds
 // `smem_tiles` tiles.
-// Phase 1 loads the newest DTQ_FUSED_L2_KEEP_MB of the tiles it cannot keep on chip with an L2 evict_last
+// Phase 1 loads the newest kFusedL2KeepMB of the tiles it cannot keep on chip with an L2 evict_last
 // policy, so that they survive the rest of the streaming traffic until phase 2 comes back for them (newest
 // first).  Measured on B200, 128 MiB input: 53.2 us without the hint, 52.6 / 50.9 / 50.0 / 49.3 us with
 // 32 / 48 / 64 / 80 MB, 49.8 us with every streamed tile marked (more than L2 holds: the marked lines evict
 // each other).
-#ifndef DTQ_CAST_REVERSE
-#define DTQ_CAST_REVERSE 1
-#endif
-#ifndef DTQ_FUSED_L2_HINT
-#define DTQ_FUSED_L2_HINT 1
-#endif
-#ifndef DTQ_FUSED_L2_KEEP_MB
-#define DTQ_FUSED_L2_KEEP_MB 80
-#endif
-constexpr int kFusedThreads = DTQ_FUSED_THREADS;
+constexpr int64_t kFusedL2KeepMB = 80;
 
 template <int UNROLL>
 __device__ __forceinline__ void load_tile(uint4 (&v)[UNROLL], const uint4 *__restrict__ in, int64_t tile,
@@ -190,7 +155,7 @@ __device__ __forceinline__ void store_tile(const uint4 (&v)[UNROLL], const DsqSc
 // P2P: the tensor is row-sharded over several GPUs running this same launch; the barrier between
 // the phases also exchanges the per-GPU maxima through peer memory (see grid_max_barrier_exchange).
 template <int IN, int OUT, int UNROLL, bool P2P>
-__global__ void __launch_bounds__(kFusedThreads, DTQ_FUSED_BLOCKS_PER_SM)
+__global__ void __launch_bounds__(kFusedThreads, kFusedBlocksPerSm)
 dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float *__restrict__ amax_out,
                  float *__restrict__ scale_out, int64_t numel, Workspace *ws, int smem_tiles, PeerExchange px) {
   using C = DsqChunk<IN, OUT, true>;
@@ -207,17 +172,15 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   const int64_t G = gridDim.x;
   // this block's tiles: blockIdx.x + k * G for k in [0, count)
   const int64_t count = blockIdx.x < ntiles ? (ntiles - blockIdx.x + G - 1) / G : 0;
-  constexpr int kRegTiles = DTQ_FUSED_KEEP_REGS;  // tile k = 0 lives in registers if 1
+  constexpr int kRegTiles = kFusedRegTiles;  // tile k = 0 lives in registers
   // tiles k in [kRegTiles, kept) live in shared memory, tiles k >= kept are streamed
   const int64_t kept = count < smem_tiles + kRegTiles ? count : smem_tiles + kRegTiles;
 
   // phase 1
-#if DTQ_FUSED_L2_HINT
   const uint64_t keep_policy = l2_policy_evict_last();
-  // the newest DTQ_FUSED_L2_KEEP_MB of the streamed tiles (phase 2 starts with them); never a kept tile
-  const int64_t hint_tiles = (int64_t(DTQ_FUSED_L2_KEEP_MB) << 20) / (G * kTile * 16);
+  // the newest kFusedL2KeepMB of the streamed tiles (phase 2 starts with them); never a kept tile
+  const int64_t hint_tiles = (kFusedL2KeepMB << 20) / (G * kTile * 16);
   const int64_t hint_from = count - hint_tiles > kept ? count - hint_tiles : kept;
-#endif
   float a = 0.0f, b = 0.0f;
   uint4 first_tile[UNROLL];
 #pragma unroll
@@ -230,7 +193,6 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   for (int64_t k = kRegTiles; k < count; k += 2) {  // two tiles (2 * UNROLL loads) in flight
     uint4 v[UNROLL], w[UNROLL];
     const bool second = k + 1 < count;
-#if DTQ_FUSED_L2_HINT
     // tiles that are not kept on chip come back in phase 2: ask L2 to hold on to them
     if (k >= hint_from) load_tile_hint<UNROLL>(v, in, blockIdx.x + k * G, nchunks, keep_policy);
     else load_tile<UNROLL>(v, in, blockIdx.x + k * G, nchunks);
@@ -238,10 +200,6 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
       if (k + 1 >= hint_from) load_tile_hint<UNROLL>(w, in, blockIdx.x + (k + 1) * G, nchunks, keep_policy);
       else load_tile<UNROLL>(w, in, blockIdx.x + (k + 1) * G, nchunks);
     }
-#else
-    load_tile<UNROLL>(v, in, blockIdx.x + k * G, nchunks);
-    if (second) load_tile<UNROLL>(w, in, blockIdx.x + (k + 1) * G, nchunks);
-#endif
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) C::absmax(a, b, v[u]);
     if (k < kept) {
@@ -265,10 +223,15 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   const float block_value = block_max_nonneg(fmaxf(a, b), smem32, 0.0f);
   __shared__ float amax_shared;
   float amax;
-  if constexpr (P2P) {
-    if (!grid_max_barrier_exchange(ws, gen0, block_value, px, &flag, &amax_shared, &amax)) return;
-  } else {
-    if (!grid_max_barrier(ws, gen0, block_value, &flag, &amax_shared, &amax)) return;  // status word says why
+  bool met;
+  if constexpr (P2P) met = grid_max_barrier_exchange(ws, gen0, block_value, px, &flag, &amax_shared, &amax);
+  else met = grid_max_barrier(ws, gen0, block_value, &flag, &amax_shared, &amax);
+  if (!met) {  // a bounded wait gave up (the status word says so): no payload, and NaN where a maximum was expected
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      if (amax_out) *amax_out = __uint_as_float(0x7FC00000u);
+      if (scale_out) *scale_out = __uint_as_float(0x7FC00000u);
+    }
+    return;
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     if (amax_out) *amax_out = amax;
@@ -277,29 +240,11 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
   const DsqScale sd = make_dsq_scale<OUT>(amax);
 
   // phase 2a: streamed tiles, newest first
-#if DTQ_FUSED_PIPELINE
-  {  // two register buffers: the next tile's loads are in flight while this one is converted
-    uint4 va[UNROLL], vb[UNROLL];
-    int64_t k = count - 1;
-    const int64_t stop = kept - 1;  // tiles k > stop were streamed
-    if (k > stop) load_tile<UNROLL>(va, in, blockIdx.x + k * G, nchunks);
-    while (k > stop) {
-      if (k - 1 > stop) load_tile<UNROLL>(vb, in, blockIdx.x + (k - 1) * G, nchunks);
-      store_tile<C, UNROLL>(va, sd, out, blockIdx.x + k * G, nchunks);
-      --k;
-      if (k <= stop) break;
-      if (k - 1 > stop) load_tile<UNROLL>(va, in, blockIdx.x + (k - 1) * G, nchunks);
-      store_tile<C, UNROLL>(vb, sd, out, blockIdx.x + k * G, nchunks);
-      --k;
-    }
-  }
-#else
   for (int64_t k = count - 1; k >= kept; --k) {
     uint4 v[UNROLL];
     load_tile<UNROLL>(v, in, blockIdx.x + k * G, nchunks);
     store_tile<C, UNROLL>(v, sd, out, blockIdx.x + k * G, nchunks);
   }
-#endif
   // phase 2b: tiles kept in shared memory, then the one kept in registers
   for (int64_t k = kept - 1; k >= kRegTiles; --k) {
     uint4 v[UNROLL];
@@ -320,22 +265,23 @@ __global__ void __launch_bounds__(kThreads, 2048 / kThreads)
 cast_with_amax_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, const float *__restrict__ amax_p,
                       float *__restrict__ scale_out, float *__restrict__ amax_out, int64_t numel) {
   using C = DsqChunk<IN, OUT, BOUNDED>;
-  const float amax = fmaxf(*amax_p, 0.0f);
+  pdl_launch_dependents();
+  pdl_wait();  // launched so that it may become resident under the tail of the kernel that delivers the amax
+  const float amax_in = *amax_p;
+  const float amax = fmaxf(amax_in, 0.0f);
   const DsqScale sd = make_dsq_scale<OUT>(amax);
   if (blockIdx.x == 0 && threadIdx.x == 0) {
-    if (scale_out) *scale_out = static_cast<float>(sd.sd);
-    if (amax_out) *amax_out = amax;
+    // a NaN amax (an exchange that timed out upstream) is passed on, not silently turned into 0
+    const bool bad = amax_in != amax_in;
+    if (scale_out) *scale_out = bad ? amax_in : static_cast<float>(sd.sd);
+    if (amax_out) *amax_out = bad ? amax_in : amax;
   }
   const int64_t nchunks = numel / C::kElems;
   constexpr int64_t kTile = int64_t(kThreads) * UNROLL;
-#if DTQ_CAST_REVERSE
   // highest addresses first: what the kernel before this one read last (an amax, an MX cast) may still be in L2
   const int64_t ntiles = (nchunks + kTile - 1) / kTile;
   for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const int64_t tile = ntiles - 1 - t;
-#else
-  for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
-#endif
     const int64_t first = tile * kTile + threadIdx.x;
     uint4 v[UNROLL];
     if ((tile + 1) * kTile <= nchunks) {
@@ -392,6 +338,7 @@ amax_scalar_kernel(const void *__restrict__ in, int64_t numel, float *__restrict
 
 // Per device and kernel instantiation: the shared memory the kernel may keep tiles in and the
 // largest grid a cooperative launch accepts with it (cached after the first call).
+constexpr int kMaxPlanDevices = 64;
 struct FusedPlan {
   int smem_tiles = 0;
   int max_grid = 0;
@@ -401,7 +348,7 @@ template <typename Kernel>
 int fused_plan(Kernel kernel, const DeviceInfo &dev, FusedPlan *cache, std::atomic<int> *ready, FusedPlan *plan) {
   int dev_id = 0;
   DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
-  dev_id &= 63;
+  if (dev_id < 0 || dev_id >= kMaxPlanDevices) return DTQ_ERR_INVALID_ARGUMENT;
   if (!ready[dev_id].load(std::memory_order_acquire)) {
     static std::mutex mutex;
     std::lock_guard<std::mutex> lock(mutex);
@@ -409,12 +356,12 @@ int fused_plan(Kernel kernel, const DeviceInfo &dev, FusedPlan *cache, std::atom
       int smem_per_sm = 0, reserved = 0;
       DTQ_CUDA_TRY(cudaDeviceGetAttribute(&smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev_id));
       DTQ_CUDA_TRY(cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev_id));
-      const size_t tile_bytes = size_t(kFusedThreads) * DTQ_DSQ_UNROLL * 16;
+      const size_t tile_bytes = size_t(kFusedThreads) * kUnroll * 16;
       FusedPlan p;
-      // what one of DTQ_FUSED_BLOCKS_PER_SM co-resident blocks can have, minus static use and reserve
-      const size_t budget = size_t(smem_per_sm) / DTQ_FUSED_BLOCKS_PER_SM - reserved - 512;
+      // what one of kFusedBlocksPerSm co-resident blocks can have, minus static use and reserve
+      const size_t budget = size_t(smem_per_sm) / kFusedBlocksPerSm - reserved - 512;
       p.smem_tiles = static_cast<int>(budget / tile_bytes);
-      if (p.smem_tiles > DTQ_FUSED_SMEM_TILES) p.smem_tiles = DTQ_FUSED_SMEM_TILES;
+      if (p.smem_tiles > kFusedSmemTiles) p.smem_tiles = kFusedSmemTiles;
       const size_t dyn = size_t(p.smem_tiles) * tile_bytes;
       DTQ_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dyn)));
       int per_sm = 0;
@@ -435,27 +382,22 @@ template <int IN, int OUT, bool P2P>
 int launch_fused_kernel(const void *in, void *out, float *amax_out, float *scale_out, int64_t numel, Workspace *ws,
                         const DeviceInfo &dev, const PeerExchange &px, cudaStream_t st) {
   using C = DsqChunk<IN, OUT>;
-  static FusedPlan cache[64];
-  static std::atomic<int> ready[64];
-  auto kernel = dsq_fused_kernel<IN, OUT, DTQ_DSQ_UNROLL, P2P>;
+  static FusedPlan cache[kMaxPlanDevices];
+  static std::atomic<int> ready[kMaxPlanDevices];
+  auto kernel = dsq_fused_kernel<IN, OUT, kUnroll, P2P>;
   FusedPlan plan;
   if (int e = fused_plan(kernel, dev, cache, ready, &plan)) return e;
-  const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kFusedThreads) * DTQ_DSQ_UNROLL);
+  const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kFusedThreads) * kUnroll);
   const int grid = balanced_grid(tiles, plan.max_grid);
   const uint4 *in4 = static_cast<const uint4 *>(in);
   uint8_t *o = static_cast<uint8_t *>(out);
   int smem_tiles = plan.smem_tiles;
   PeerExchange exchange = px;
-  const size_t dyn = size_t(smem_tiles) * kFusedThreads * DTQ_DSQ_UNROLL * 16;
-#if DTQ_DSQ_COOP
+  const size_t dyn = size_t(smem_tiles) * kFusedThreads * kUnroll * 16;
   void *args[] = {&in4, &o, &amax_out, &scale_out, &numel, &ws, &smem_tiles, &exchange};
   DTQ_CUDA_TRY(
       cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kernel), dim3(grid), dim3(kFusedThreads), args, dyn, st));
   return DTQ_OK;
-#else
-  kernel<<<grid, kFusedThreads, dyn, st>>>(in4, o, amax_out, scale_out, numel, ws, smem_tiles, exchange);
-  return cuda_status(cudaGetLastError());
-#endif
 }
 
 template <int IN, int OUT>
@@ -464,13 +406,13 @@ int launch_fused(const void *in, void *out, float *amax_out, float *scale_out, i
   using C = DsqChunk<IN, OUT>;
   uint8_t *o = static_cast<uint8_t *>(out);
   const bool vector_ok = aligned_to(in, 16) && aligned_to(out, C::kOutAlign);
-  if (vector_ok && numel * C::kElemBytes > DTQ_FUSED_MAX_BYTES) {
+  if (vector_ok && numel * C::kElemBytes > kFusedMaxBytes) {
     if (int e = launch_amax(in, &ws->amax, numel, IN, ws, dev, st)) return e;
-    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * DTQ_DSQ_UNROLL);
-    const int grid = balanced_grid(tiles, int64_t(dev.sm_count) * DTQ_CAST_BLOCKS_PER_SM);
-    cast_with_amax_stream<IN, OUT, DTQ_DSQ_UNROLL, true><<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in), o,
-                                                                                   &ws->amax, scale_out, amax_out, numel);
-    return cuda_status(cudaGetLastError());
+    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * kUnroll);
+    const int grid = balanced_grid(tiles, int64_t(dev.sm_count) * kCastBlocksPerSmCap);
+    return cuda_status(launch_after_dependency(cast_with_amax_stream<IN, OUT, kUnroll, true>, dim3(grid), dim3(kThreads),
+                                               0, st, static_cast<const uint4 *>(in), o, &ws->amax, scale_out, amax_out,
+                                               numel));
   }
   if (vector_ok && dev.cooperative)
     return launch_fused_kernel<IN, OUT, false>(in, out, amax_out, scale_out, numel, ws, dev, PeerExchange{}, st);
@@ -487,12 +429,13 @@ int launch_cast(const void *in, void *out, const float *amax, float *scale_out, 
                 cudaStream_t st) {
   using C = DsqChunk<IN, OUT>;
   uint8_t *o = static_cast<uint8_t *>(out);
-  const int64_t max_grid = int64_t(dev.sm_count) * DTQ_CAST_BLOCKS_PER_SM;
+  const int64_t max_grid = int64_t(dev.sm_count) * kCastBlocksPerSmCap;
   if (aligned_to(in, 16) && aligned_to(out, C::kOutAlign)) {
-    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * DTQ_DSQ_UNROLL);
+    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * kUnroll);
     const int grid = balanced_grid(tiles, max_grid);
-    cast_with_amax_stream<IN, OUT, DTQ_DSQ_UNROLL, false><<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in), o,
-                                                                                    amax, scale_out, nullptr, numel);
+    return cuda_status(launch_after_dependency(cast_with_amax_stream<IN, OUT, kUnroll, false>, dim3(grid),
+                                               dim3(kThreads), 0, st, static_cast<const uint4 *>(in), o, amax, scale_out,
+                                               static_cast<float *>(nullptr), numel));
   } else {
     const int64_t blocks = ceil_div64(numel, kThreads);
     const int grid = static_cast<int>(blocks < 1 ? 1 : (blocks < max_grid ? blocks : max_grid));

@@ -21,9 +21,7 @@ namespace dtq {
 namespace {
 
 // Grid cap in blocks per SM; the default is "no cap" (one tile per block), see saturated_cast.cu.
-#ifndef DTQ_MX_BLOCKS_PER_SM
-#define DTQ_MX_BLOCKS_PER_SM (1 << 20)
-#endif
+constexpr int64_t kBlocksPerSmCap = 1 << 20;
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;  // tied to the scale-byte mapping below: lane&3 picks the iteration
 
@@ -94,7 +92,7 @@ int launch_mx(const void *in_bf16, void *payload, void *scales_e8m0, int64_t row
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
   const int64_t kblocks = cols / 32, katoms = (kblocks + 3) / 4;
-  const int64_t max_grid = int64_t(dev.sm_count) * DTQ_MX_BLOCKS_PER_SM;
+  const int64_t max_grid = int64_t(dev.sm_count) * kBlocksPerSmCap;
   if (aligned_to(in_bf16, 16) && aligned_to(payload, 8)) {
     const int64_t nchunks = numel / 8;
     const int64_t tiles = ceil_div64(nchunks, int64_t(kThreads) * kUnroll);

@@ -28,9 +28,7 @@
 namespace dtq {
 namespace {
 
-#ifndef DTQ_MX_AMAX_L2_KEEP_MB
-#define DTQ_MX_AMAX_L2_KEEP_MB 48
-#endif
+constexpr int64_t kL2KeepMB = 48;  // how much of the end of the input is asked to stay in L2 for the cast behind
 constexpr int kThreadsA = 256;
 constexpr int kUnrollA = 4;  // tied to the scale-byte mapping: lane & 3 picks the iteration
 
@@ -57,27 +55,22 @@ __global__ void __launch_bounds__(kThreadsA, 2048 / kThreadsA)
 mx_amax_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
                int64_t nchunks, Workspace *ws) {
   __shared__ uint32_t warp_cand[kThreadsA / 32];
+  pdl_launch_dependents();  // the finishing warp may become resident now; it waits for this grid to complete
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int64_t kTile = int64_t(kThreadsA) * kUnrollA;
   uint32_t cand = 0;
-#if DTQ_MX_AMAX_L2_KEEP_MB
   // The cast that follows reads the same input again, newest tiles first: the last tiles of this read are
   // loaded under an L2 evict_last policy so that they are still there.
   const uint64_t keep_policy = l2_policy_evict_last();
-  const int64_t keep_from = nchunks - (int64_t(DTQ_MX_AMAX_L2_KEEP_MB) << 20) / 16;
-#endif
+  const int64_t keep_from = nchunks - (kL2KeepMB << 20) / 16;
   for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
     const int64_t warp_first = tile * kTile + int64_t(warp) * (32 * kUnrollA);
     uint4 v[kUnrollA];
 #pragma unroll
     for (int u = 0; u < kUnrollA; ++u) {
       const int64_t c = warp_first + u * 32 + lane;
-#if DTQ_MX_AMAX_L2_KEEP_MB
       v[u] = c < nchunks ? (warp_first >= keep_from ? ldg_stream_hint(in + c, keep_policy) : ldg_stream(in + c))
                          : make_uint4(0, 0, 0, 0);
-#else
-      v[u] = c < nchunks ? ldg_stream(in + c) : make_uint4(0, 0, 0, 0);
-#endif
     }
     uint32_t my_scale_byte = 0;
 #pragma unroll
@@ -115,13 +108,16 @@ template <bool P2P>
 __global__ void __launch_bounds__(32)
 mx_amax_finish_kernel(float *__restrict__ amax_out, Workspace *ws, PeerExchange px) {
   const int lane = threadIdx.x;
+  pdl_launch_dependents();  // a cast queued behind this launch may become resident while the maxima meet
+  pdl_wait();               // every block of the MX kernel has folded its maximum
   uint32_t total = atomicExch(&ws->slot_max[lane], 0u);
   total = __reduce_max_sync(0xFFFFFFFFu, total);
   bool ok = true;
   if constexpr (P2P) total = peer_exchange_max(px, total, &ok);
   if (lane == 0) {
     if (!ok) atomicExch(&ws->status, DTQ_ERR_TIMEOUT);
-    amax_out[0] = ok ? __uint_as_float(total << 16) : 0.0f;
+    // a peer never arrived: NaN, so that nothing downstream can take the value for a maximum
+    amax_out[0] = ok ? __uint_as_float(total << 16) : __uint_as_float(0x7FC00000u);
   }
 }
 
@@ -144,8 +140,8 @@ int launch_mx_amax(const void *in_bf16, void *payload, void *scales, float *amax
   if (numel > 0)
     mx_amax_kernel<<<grid, kThreadsA, 0, st>>>(static_cast<const uint4 *>(in_bf16), static_cast<uint8_t *>(payload),
                                                static_cast<uint8_t *>(scales), nchunks, ws);
-  mx_amax_finish_kernel<P2P><<<1, 32, 0, st>>>(amax_out, ws, px);  // an empty shard still takes part in the exchange
-  return cuda_status(cudaGetLastError());
+  // an empty shard still takes part in the exchange
+  return cuda_status(launch_after_dependency(mx_amax_finish_kernel<P2P>, dim3(1), dim3(32), 0, st, amax_out, ws, px));
 }
 
 }  // namespace

@@ -28,22 +28,17 @@ namespace {
 
 constexpr int kTile = 128;          // rows and columns of a CTA tile
 constexpr int kTileWords = kTile / 2;  // 32-bit words (bf16 pairs) per tile row
-#ifndef DTQ_DUAL_THREADS
-#define DTQ_DUAL_THREADS 256
-#endif
-constexpr int kThreadsDual = DTQ_DUAL_THREADS;
+constexpr int kThreadsDual = 256;
 constexpr int kWarpsDual = kThreadsDual / 32;
 constexpr int kPassRows = 2 * kWarpsDual;        // a row pass: every warp takes two rows
 constexpr int kRowPasses = kTile / kPassRows;    // 8 (256 threads) or 4 (512)
 constexpr int kColPasses = kTileWords / (4 * kWarpsDual);  // a column pass: every warp takes four word columns
 static_assert(kRowPasses % 4 == 0 && kColPasses >= 1, "256 or 512 threads");
-#ifndef DTQ_DUAL_GROUP
-#define DTQ_DUAL_GROUP 8
-#endif
-constexpr int kGroupRowTiles = DTQ_DUAL_GROUP;
+constexpr int kGroupRowTiles = 8;
 
-// One tile.  FULL: the tile lies inside the matrix, no access is predicated.
-template <bool FULL, bool BLOCKED>
+// One tile.  FULL: the tile lies inside the matrix, no access is predicated.  ROW_OUT: the row-major payload
+// and scales are wanted too (otherwise the row direction only loads the tile and parks it).
+template <bool FULL, bool BLOCKED, bool ROW_OUT>
 __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], const uint16_t *__restrict__ in,
                                           uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
                                           uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows,
@@ -68,6 +63,7 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
     const int rt = p * kPassRows + warp * 2 + (lane >> 4);
     const int64_t r = row0 + rt;
     *reinterpret_cast<uint4 *>(&tile[rt][(chunk * 4) ^ ((rt >> 4) << 2)]) = v[p];  // swizzled by the 16-row group
+    if constexpr (!ROW_OUT) continue;
     uint32_t mag = chunk_absmax_bits(v[p]);
     mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 1));
     mag = max(mag, __shfl_xor_sync(0xFFFFFFFFu, mag, 2));
@@ -121,12 +117,10 @@ __device__ __forceinline__ void dual_tile(uint32_t (&tile)[kTile][kTileWords], c
   }
 }
 
-#ifndef DTQ_DUAL_MIN_BLOCKS
 // 5 CTAs of 256 threads per SM (48 registers) measured 4 % faster than 4 (64 registers); 6 (40 registers) 12 % slower
-#define DTQ_DUAL_MIN_BLOCKS (DTQ_DUAL_THREADS == 256 ? 5 : 2)
-#endif
-template <bool BLOCKED>
-__global__ void __launch_bounds__(kThreadsDual, BLOCKED ? DTQ_DUAL_MIN_BLOCKS - 1 : DTQ_DUAL_MIN_BLOCKS)  // the blocked offsets need the registers
+constexpr int kDualMinBlocks = kThreadsDual == 256 ? 5 : 2;
+template <bool BLOCKED, bool ROW_OUT>
+__global__ void __launch_bounds__(kThreadsDual, BLOCKED ? kDualMinBlocks - 1 : kDualMinBlocks)  // the blocked offsets need the registers
 mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
                uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows, int64_t cols,
                int64_t row_tiles, int64_t col_tiles) {
@@ -140,9 +134,9 @@ mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, u
   const int64_t row0 = (first_row_tile + in_group % group_rows) * kTile;
   const int64_t col0 = (in_group / group_rows) * kTile;
   if (row0 + kTile <= rows && col0 + kTile <= cols)
-    dual_tile<true, BLOCKED>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
+    dual_tile<true, BLOCKED, ROW_OUT>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
   else
-    dual_tile<false, BLOCKED>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
+    dual_tile<false, BLOCKED, ROW_OUT>(tile, in, payload, scales, payload_t, scales_t, rows, cols, row0, col0);
 }
 
 }  // namespace
@@ -156,12 +150,15 @@ int launch_dual(const void *in_bf16, void *payload, void *scales_e8m0, void *pay
   if (rows < 0 || cols < 0) return DTQ_ERR_INVALID_ARGUMENT;
   if (cols % 32 != 0 || rows % 32 != 0) return DTQ_ERR_SHAPE;
   if (rows == 0 || cols == 0) return DTQ_OK;
-  if (!in_bf16 || !payload || !scales_e8m0 || !payload_t || !scales_t_e8m0) return DTQ_ERR_INVALID_ARGUMENT;
+  // payload == NULL (then scales_e8m0 is ignored): only the transposed outputs are wanted
+  const bool row_out = payload != nullptr;
+  if (!in_bf16 || (row_out && !scales_e8m0) || !payload_t || !scales_t_e8m0) return DTQ_ERR_INVALID_ARGUMENT;
   // 16-byte loads of the input, 8-byte stores of the payload, 16-byte stores of the transposed payload
   if (!aligned_to(in_bf16, 16) || !aligned_to(payload, 8) || !aligned_to(payload_t, 16)) return DTQ_ERR_INVALID_ARGUMENT;
   const int64_t row_tiles = ceil_div64(rows, kTile), col_tiles = ceil_div64(cols, kTile);
   if (row_tiles > 0x7FFFFFFFLL / col_tiles) return DTQ_ERR_TOO_LARGE;  // grid.x
-  mx_dual_kernel<BLOCKED><<<static_cast<unsigned>(row_tiles * col_tiles), kThreadsDual, 0, static_cast<cudaStream_t>(stream)>>>(
+  auto kernel = row_out ? mx_dual_kernel<BLOCKED, true> : mx_dual_kernel<BLOCKED, false>;
+  kernel<<<static_cast<unsigned>(row_tiles * col_tiles), kThreadsDual, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint16_t *>(in_bf16), static_cast<uint8_t *>(payload), static_cast<uint8_t *>(scales_e8m0),
       static_cast<uint8_t *>(payload_t), static_cast<uint8_t *>(scales_t_e8m0), rows, cols, row_tiles, col_tiles);
   return cuda_status(cudaGetLastError());

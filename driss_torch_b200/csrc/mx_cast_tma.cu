@@ -23,13 +23,8 @@ constexpr int kThreadsTma = kConsumerThreads + 32;  // + one producer warp (lane
 constexpr int kUnroll = 4;                          // 16-byte chunks per consumer thread per tile
 constexpr int kTileChunks = kConsumerThreads * kUnroll;
 constexpr int kTileBytes = kTileChunks * 16;  // 16 KiB
-#ifndef DTQ_MX_TMA_STAGES
-#define DTQ_MX_TMA_STAGES 4
-#endif
-#ifndef DTQ_MX_TMA_BLOCKS_PER_SM
-#define DTQ_MX_TMA_BLOCKS_PER_SM 3
-#endif
-constexpr int kStages = DTQ_MX_TMA_STAGES;
+constexpr int kStages = 4;
+constexpr int kTmaBlocksPerSm = 3;
 constexpr unsigned int kWaitLimit = 1u << 20;  // polls of try_wait (each already waits a while in hardware)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -71,6 +66,7 @@ struct __align__(128) TmaSmem {
   uint4 stage[kStages][kTileChunks];
   uint64_t full[kStages];
   uint64_t empty[kStages];
+  int abort;  // set by whoever gives up a wait: everybody else stops at its next tile
 };
 
 // Tiles blockIdx.x, blockIdx.x + gridDim.x, ... of kTileChunks chunks each; nchunks % 4 == 0.
@@ -87,18 +83,25 @@ mx_tma_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], kConsumerWarps);
     }
+    sm.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
 
   if (warp == kConsumerWarps) {  // producer warp
     if (lane == 0) {
+      volatile int *abort = &sm.abort;
       int64_t k = 0;
       for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++k) {
         const int s = static_cast<int>(k % kStages);
         const unsigned round = static_cast<unsigned>(k / kStages);
-        if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1u)) {
+        if (*abort || (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1u))) {
+          // Give up, but not with copies still on their way into this CTA's shared memory: wait
+          // (bounded) for the newest copy of every stage; they complete without the consumers' help.
           atomicExch(status, DTQ_ERR_TIMEOUT);
+          *abort = 1;
+          for (int64_t j = k - 1; j >= 0 && j > k - 1 - kStages; --j)
+            mbar_wait(&sm.full[j % kStages], static_cast<unsigned>(j / kStages) & 1u);
           return;
         }
         const int64_t first = tile * kTileChunks;
@@ -116,8 +119,13 @@ mx_tma_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8
   for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++k) {
     const int s = static_cast<int>(k % kStages);
     const unsigned round = static_cast<unsigned>(k / kStages);
+    if (*static_cast<volatile int *>(&sm.abort)) return;  // the producer drains its copies before the CTA ends
     if (!mbar_wait(&sm.full[s], round & 1u)) {
-      if (lane == 0) atomicExch(status, DTQ_ERR_TIMEOUT);
+      // the copy never landed: nothing can be drained; after this status the outputs are not to be trusted
+      if (lane == 0) {
+        atomicExch(status, DTQ_ERR_TIMEOUT);
+        *static_cast<volatile int *>(&sm.abort) = 1;
+      }
       return;
     }
     const int64_t warp_first = tile * kTileChunks + int64_t(warp) * (32 * kUnroll);
@@ -165,17 +173,19 @@ extern "C" int dtq_mx_fp8_quantize_tma(const void *in_bf16, void *payload, void 
   if (!aligned_to(in_bf16, 16) || !aligned_to(payload, 8)) return DTQ_ERR_INVALID_ARGUMENT;
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
-  static std::atomic<int> configured[64];
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> configured[kMaxDevices];
   int dev_id = 0;
   DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
+  if (dev_id < 0 || dev_id >= kMaxDevices) return DTQ_ERR_INVALID_ARGUMENT;
   const int smem = static_cast<int>(sizeof(TmaSmem)) + 128;
-  if (!configured[dev_id & 63].load(std::memory_order_acquire)) {
+  if (!configured[dev_id].load(std::memory_order_acquire)) {  // setting the attribute twice is harmless
     DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured[dev_id & 63].store(1, std::memory_order_release);
+    configured[dev_id].store(1, std::memory_order_release);
   }
   const int64_t nchunks = numel / 8;
   const int64_t tiles = ceil_div64(nchunks, kTileChunks);
-  const int grid = balanced_grid(tiles, int64_t(dev.sm_count) * DTQ_MX_TMA_BLOCKS_PER_SM);
+  const int grid = balanced_grid(tiles, int64_t(dev.sm_count) * kTmaBlocksPerSm);
   mx_tma_kernel<<<grid, kThreadsTma, smem, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4 *>(in_bf16), static_cast<uint8_t *>(payload), static_cast<uint8_t *>(scales_e8m0), nchunks,
       status_dev);

@@ -75,13 +75,19 @@ WorkspaceCache &workspaces() {
 
 // ---- reference ops --------------------------------------------------------------------------------
 
+std::tuple<at::Tensor, at::Tensor> cast_transposed(const at::Tensor &input, const at::Tensor &scale,
+                                                   at::ScalarType dtype, bool both, const char *what);
+
 at::Tensor saturated_cast(const at::Tensor &input, const at::Tensor &scale, at::ScalarType dtype, bool transpose) {
   check_fp8(dtype);
   check_input(input);
   TORCH_CHECK(scale.scalar_type() == at::kFloat, "Scale tensor must be of type Float, but got ", scale.dtype());
   TORCH_CHECK(scale.numel() == 1, "Scale tensor must be a scalar, but got ", scale.numel());
   TORCH_CHECK(scale.is_cuda() && scale.device() == input.device(), "Scale tensor must live on the input's device");
-  TORCH_CHECK(!transpose, "transpose=True is not supported");
+  // transpose: the cast of input.t() as a contiguous [cols, rows] tensor, in one pass.  (The reference declares
+  // the flag, asserts it off in its Python wrapper and only uses it to choose a kernel; this package's wrapper
+  // keeps that assert, the operator itself honours the flag.)
+  if (transpose) return std::get<1>(cast_transposed(input, scale, dtype, false, "saturated_cast"));
   // The op is elementwise over storage: row-major or exactly transposed inputs at storage offset
   // zero are processed in place and the output keeps their strides; anything else is made
   // contiguous first (same rule as the reference).
@@ -154,23 +160,31 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> cast_with_amax_dual(const at::Ten
   return {out, out_t, scale};
 }
 
-// amax, then both orientations of the cast: (payload, payload_t, amax, scale); two launches, the input read twice.
+// amax, then both orientations of the cast: (payload, payload_t, amax, scale); one C-ABI call that queues the
+// amax kernel and, overlapping its tail, the kernel that casts into both orientations.
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> dynamic_scaled_quant_dual(const at::Tensor &input,
                                                                                       at::ScalarType dtype) {
   check_fp8(dtype);
   check_input(input);
   TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
-  at::Tensor amax_value = at::empty({1}, input.options().dtype(at::kFloat));
-  {
-    c10::cuda::CUDAGuard guard(input.device());
-    auto stream = c10::cuda::getCurrentCUDAStream();
-    check_status(dtq_amax(input.data_ptr(), amax_value.data_ptr<float>(), input.numel(), in_code(input.scalar_type()),
-                          workspaces().get(stream), dtq_workspace_bytes(), stream.stream()),
-                 "dynamic_scaled_quant_dual");
+  const int64_t rows = input.size(0), cols = input.size(1);
+  at::Tensor out = at::empty({rows, cols}, input.options().dtype(dtype));
+  at::Tensor out_t = at::empty({cols, rows}, input.options().dtype(dtype));
+  if (input.numel() == 0) {  // nothing is launched: the fused op's maximum starts at 0
+    at::Tensor amax_value = at::zeros({1}, input.options().dtype(at::kFloat));
+    at::Tensor scale = at::full({1}, (dtype == at::kFloat8_e4m3fn ? 448.0 : 57344.0) / 1e-12, input.options().dtype(at::kFloat));
+    return {out, out_t, amax_value, scale};
   }
-  amax_value.clamp_min_(0.0);  // an empty input gives -inf; the fused op starts its maximum at 0
-  auto r = cast_with_amax_dual(input, amax_value, dtype);
-  return {std::get<0>(r), std::get<1>(r), amax_value, std::get<2>(r)};
+  at::Tensor amax_value = at::empty({1}, input.options().dtype(at::kFloat));
+  at::Tensor scale = at::empty({1}, input.options().dtype(at::kFloat));
+  c10::cuda::CUDAGuard guard(input.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_dynamic_scaled_quant_dual(input.data_ptr(), out.data_ptr(), out_t.data_ptr(), amax_value.data_ptr<float>(),
+                                             scale.data_ptr<float>(), rows, cols, in_code(input.scalar_type()),
+                                             out_code(dtype), workspaces().get(stream), dtq_workspace_bytes(),
+                                             stream.stream()),
+               "dynamic_scaled_quant_dual");
+  return {out, out_t, amax_value, scale};
 }
 
 at::Tensor amax(const at::Tensor &input) {
@@ -232,11 +246,29 @@ std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize(at::Tensor input, int64_t blo
   TORCH_CHECK(in_type == at::kBFloat16 || in_type == at::kHalf || in_type == at::kFloat,
               "Input tensor must be bfloat16, float16 or float32, but got ", input.dtype());
   TORCH_CHECK(block_size == 32, "Block size must be 32, but got ", block_size);
-  TORCH_CHECK(axis == 1 || axis == -1, "Blocks run along the last dimension (axis=1), but got axis=", axis);
-  TORCH_CHECK(!transpose, "transpose=True is not supported (see mx_fp8_quantize_dual)");
+  const bool along_rows = axis == 0 || axis == -2;
+  TORCH_CHECK(along_rows || axis == 1 || axis == -1, "axis must be 0 or 1, but got ", axis);
   TORCH_CHECK(fp8_type == at::kFloat8_e4m3fn || fp8_type == at::kFloat8_e5m2,
               "FP8 type must be Float8_e4m3fn or Float8_e5m2");
   const int64_t m = input.size(0), n = input.size(1);
+  // axis / transpose (the reference declares both and ignores them).  `transpose`: the result is that of
+  // the op on input.t(); axis = 0: blocks of 32 run down the columns instead of along the rows.  One of the
+  // two alone means blocks along the input's dimension 0, produced by the transposing kernel in one read
+  // (payload_t [n, m] contiguous, one scale per 32 rows of a column): `transpose` returns payload_t itself,
+  // axis = 0 returns it viewed as [m, n].  Both together cancel: the ordinary blocks, payload viewed as [n, m].
+  if (along_rows != transpose) {
+    TORCH_CHECK(in_type == at::kBFloat16 && fp8_type == at::kFloat8_e4m3fn,
+                "axis=0 / transpose=True need a bfloat16 input and an e4m3 payload");
+    TORCH_CHECK(m % 32 == 0 && n % 32 == 0, "Both dimensions must be multiples of the block size 32, but got ", m, " x ", n);
+    at::Tensor out_t = at::empty({n, m}, input.options().dtype(fp8_type));
+    at::Tensor scale_t = at::empty({n * (m / 32)}, input.options().dtype(at::kFloat8_e8m0fnu));
+    c10::cuda::CUDAGuard guard(input.device());
+    auto stream = c10::cuda::getCurrentCUDAStream();
+    check_status(dtq_mx_fp8_quantize_dual(input.data_ptr(), nullptr, nullptr, out_t.data_ptr(), scale_t.data_ptr(), m, n,
+                                          stream.stream()),
+                 "mx_fp8_quantize");
+    return {transpose ? out_t : out_t.t(), scale_t};
+  }
   TORCH_CHECK(n % 32 == 0, "The last dimension must be a multiple of the block size 32, but got ", n);
   at::Tensor out = at::empty_like(input, input.options().dtype(fp8_type));
   at::Tensor scale = at::empty({m * (n / 32)}, input.options().dtype(at::kFloat8_e8m0fnu));
@@ -250,7 +282,7 @@ std::tuple<at::Tensor, at::Tensor> mx_fp8_quantize(at::Tensor input, int64_t blo
                                  out_code(fp8_type), stream.stream()),
                  "mx_fp8_quantize");
   }
-  return {out, scale};
+  return {transpose ? out.t() : out, scale};
 }
 
 // ---- additions ---------------------------------------------------------------------------------------

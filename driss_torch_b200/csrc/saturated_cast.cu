@@ -13,20 +13,13 @@
 namespace dtq {
 namespace {
 
-#ifndef DTQ_SC_UNROLL
-#define DTQ_SC_UNROLL 4
-#endif
+constexpr int kUnroll = 4;  // 128-bit loads in flight per thread
 // Blocks per SM that cap the grid.  The default is "no cap": one tile per block, so the hardware
 // block scheduler hands out tiles in address order as SMs free up, which measured about 10%
 // faster on B200 than a persistent grid-stride loop (whose blocks run in lock step: load burst,
 // then store burst).  The in-kernel loop then only matters beyond 2^31-1 tiles.
-#ifndef DTQ_SC_BLOCKS_PER_SM
-#define DTQ_SC_BLOCKS_PER_SM (1 << 20)
-#endif
-#ifndef DTQ_SC_THREADS
-#define DTQ_SC_THREADS 256
-#endif
-constexpr int kThreads = DTQ_SC_THREADS;
+constexpr int64_t kBlocksPerSmCap = 1 << 20;
+constexpr int kThreads = 256;
 
 // One 16-byte input chunk -> its fp8 bytes, stored with one instruction.
 template <int IN, int OUT>
@@ -115,11 +108,11 @@ saturated_cast_scalar(const void *__restrict__ in, uint8_t *__restrict__ out, co
 template <int IN, int OUT>
 int launch(const void *in, void *out, const float *scale, int64_t numel, const DeviceInfo &dev, cudaStream_t st) {
   using C = Chunk<IN, OUT>;
-  const int64_t max_grid = int64_t(dev.sm_count) * DTQ_SC_BLOCKS_PER_SM;
+  const int64_t max_grid = int64_t(dev.sm_count) * kBlocksPerSmCap;
   if (aligned_to(in, 16) && aligned_to(out, 8)) {
-    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * DTQ_SC_UNROLL);
+    const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * kUnroll);
     const int grid = balanced_grid(tiles, max_grid);
-    saturated_cast_stream<IN, OUT, DTQ_SC_UNROLL><<<grid, kThreads, 0, st>>>(
+    saturated_cast_stream<IN, OUT, kUnroll><<<grid, kThreads, 0, st>>>(
         static_cast<const uint4 *>(in), static_cast<uint8_t *>(out), scale, numel);
   } else {
     const int64_t blocks = ceil_div64(numel, kThreads);

@@ -24,6 +24,11 @@
 #include "dtq_host.h"
 
 namespace dtq {
+
+// from amax.cu
+int launch_amax(const void *in, float *out, int64_t numel, int in_dtype, Workspace *ws, const DeviceInfo &dev,
+                cudaStream_t st);
+
 namespace {
 
 constexpr int kTileRows = 128;
@@ -167,19 +172,22 @@ __device__ __forceinline__ void transposed_tile(uint32_t (&tile)[kTileRows][kTil
 }
 
 // `scale` points to the scale (Cast) or to the amax (DynCast); scale_out, if given, receives the fp32 scale
-// a DynCast derived from the amax.
-#ifndef DTQ_CT_MIN_BLOCKS
-#define DTQ_CT_MIN_BLOCKS 4
-#endif
+// a DynCast derived from the amax, amax_out the amax it used (the given one, clamped at zero).
+constexpr int kTransposedMinBlocks = 4;
 template <typename C, bool BOTH>
-__global__ void __launch_bounds__(kThreadsT, DTQ_CT_MIN_BLOCKS)
+__global__ void __launch_bounds__(kThreadsT, kTransposedMinBlocks)
 cast_transposed_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, uint8_t *__restrict__ out_t,
-                       const float *__restrict__ scale, float *__restrict__ scale_out, int64_t rows, int64_t cols,
-                       int64_t col_tiles) {
+                       const float *__restrict__ scale, float *__restrict__ scale_out, float *__restrict__ amax_out,
+                       int64_t rows, int64_t cols, int64_t col_tiles) {
   __shared__ __align__(16) uint32_t tile[kTileRows][kTileWords];
   constexpr int kTileCols = 16 * C::kChunkElems;
+  pdl_launch_dependents();
+  pdl_wait();  // may have become resident under the tail of the kernel that delivers *scale
   const typename C::Scale s = C::load_scale(scale);
-  if (scale_out && blockIdx.x == 0 && threadIdx.x == 0) *scale_out = C::scale_value(s);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (scale_out) *scale_out = C::scale_value(s);
+    if (amax_out) *amax_out = fmaxf(*scale, 0.0f);
+  }
   const int64_t row0 = (blockIdx.x / col_tiles) * kTileRows;
   const int64_t col0 = (blockIdx.x % col_tiles) * kTileCols;
   if (row0 + kTileRows <= rows && col0 + kTileCols <= cols)
@@ -192,11 +200,16 @@ cast_transposed_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, 
 template <typename C, bool BOTH>
 __global__ void __launch_bounds__(256)
 cast_transposed_generic(const void *__restrict__ in, uint8_t *__restrict__ out, uint8_t *__restrict__ out_t,
-                        const float *__restrict__ scale, float *__restrict__ scale_out, int64_t rows, int64_t cols,
-                        int64_t col_tiles) {
+                        const float *__restrict__ scale, float *__restrict__ scale_out, float *__restrict__ amax_out,
+                        int64_t rows, int64_t cols, int64_t col_tiles) {
   __shared__ uint8_t tile[32][33];
+  pdl_launch_dependents();
+  pdl_wait();
   const typename C::Scale s = C::load_scale(scale);
-  if (scale_out && blockIdx.x == 0 && threadIdx.x == 0) *scale_out = C::scale_value(s);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (scale_out) *scale_out = C::scale_value(s);
+    if (amax_out) *amax_out = fmaxf(*scale, 0.0f);
+  }
   const int64_t row0 = (blockIdx.x / col_tiles) * 32, col0 = (blockIdx.x % col_tiles) * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
 #pragma unroll
@@ -217,42 +230,44 @@ cast_transposed_generic(const void *__restrict__ in, uint8_t *__restrict__ out, 
 }
 
 template <typename C, bool BOTH>
-int launch_transposed(const void *in, void *out, void *out_t, const float *scale, float *scale_out, int64_t rows,
-                      int64_t cols, cudaStream_t st) {
+int launch_transposed(const void *in, void *out, void *out_t, const float *scale, float *scale_out, float *amax_out,
+                      int64_t rows, int64_t cols, cudaStream_t st) {
   constexpr int kTileCols = 16 * C::kChunkElems;
   const bool fast = rows % 16 == 0 && cols % C::kChunkElems == 0 && aligned_to(in, 16) && aligned_to(out_t, 16) &&
                     (!BOTH || aligned_to(out, 8));
   if (fast) {
     const int64_t row_tiles = ceil_div64(rows, kTileRows), col_tiles = ceil_div64(cols, kTileCols);
     if (row_tiles > 0x7FFFFFFFLL / col_tiles) return DTQ_ERR_TOO_LARGE;
-    cast_transposed_kernel<C, BOTH><<<static_cast<unsigned>(row_tiles * col_tiles), kThreadsT, 0, st>>>(
-        static_cast<const uint4 *>(in), static_cast<uint8_t *>(out), static_cast<uint8_t *>(out_t), scale, scale_out,
-        rows, cols, col_tiles);
+    return cuda_status(launch_after_dependency(cast_transposed_kernel<C, BOTH>, dim3(static_cast<unsigned>(row_tiles * col_tiles)),
+                                               dim3(kThreadsT), 0, st, static_cast<const uint4 *>(in),
+                                               static_cast<uint8_t *>(out), static_cast<uint8_t *>(out_t), scale, scale_out,
+                                               amax_out, rows, cols, col_tiles));
   } else {
     const int64_t row_tiles = ceil_div64(rows, 32), col_tiles = ceil_div64(cols, 32);
     if (row_tiles > 0x7FFFFFFFLL / col_tiles) return DTQ_ERR_TOO_LARGE;
-    cast_transposed_generic<C, BOTH><<<static_cast<unsigned>(row_tiles * col_tiles), 256, 0, st>>>(
-        in, static_cast<uint8_t *>(out), static_cast<uint8_t *>(out_t), scale, scale_out, rows, cols, col_tiles);
+    return cuda_status(launch_after_dependency(cast_transposed_generic<C, BOTH>, dim3(static_cast<unsigned>(row_tiles * col_tiles)),
+                                               dim3(256), 0, st, in, static_cast<uint8_t *>(out),
+                                               static_cast<uint8_t *>(out_t), scale, scale_out, amax_out, rows, cols,
+                                               col_tiles));
   }
-  return cuda_status(cudaGetLastError());
 }
 
 template <typename C>
-int launch_by_outputs(const void *in, void *out, void *out_t, const float *scale, float *scale_out, int64_t rows,
-                      int64_t cols, cudaStream_t st) {
-  return out ? launch_transposed<C, true>(in, out, out_t, scale, scale_out, rows, cols, st)
-             : launch_transposed<C, false>(in, out, out_t, scale, scale_out, rows, cols, st);
+int launch_by_outputs(const void *in, void *out, void *out_t, const float *scale, float *scale_out, float *amax_out,
+                      int64_t rows, int64_t cols, cudaStream_t st) {
+  return out ? launch_transposed<C, true>(in, out, out_t, scale, scale_out, amax_out, rows, cols, st)
+             : launch_transposed<C, false>(in, out, out_t, scale, scale_out, amax_out, rows, cols, st);
 }
 
 // CAST<IN, OUT> = Cast (static scale) or DynCast (amax)
 template <template <int, int> class CAST>
-int launch_by_dtypes(const void *in, void *out, void *out_t, const float *scale, float *scale_out, int64_t rows,
-                     int64_t cols, int in_dtype, int out_dtype, cudaStream_t st) {
+int launch_by_dtypes(const void *in, void *out, void *out_t, const float *scale, float *scale_out, float *amax_out,
+                     int64_t rows, int64_t cols, int in_dtype, int out_dtype, cudaStream_t st) {
   if (in_dtype == DTQ_BF16)
-    return out_dtype == DTQ_E4M3 ? launch_by_outputs<CAST<DTQ_BF16, DTQ_E4M3>>(in, out, out_t, scale, scale_out, rows, cols, st)
-                                 : launch_by_outputs<CAST<DTQ_BF16, DTQ_E5M2>>(in, out, out_t, scale, scale_out, rows, cols, st);
-  return out_dtype == DTQ_E4M3 ? launch_by_outputs<CAST<DTQ_F32, DTQ_E4M3>>(in, out, out_t, scale, scale_out, rows, cols, st)
-                               : launch_by_outputs<CAST<DTQ_F32, DTQ_E5M2>>(in, out, out_t, scale, scale_out, rows, cols, st);
+    return out_dtype == DTQ_E4M3 ? launch_by_outputs<CAST<DTQ_BF16, DTQ_E4M3>>(in, out, out_t, scale, scale_out, amax_out, rows, cols, st)
+                                 : launch_by_outputs<CAST<DTQ_BF16, DTQ_E5M2>>(in, out, out_t, scale, scale_out, amax_out, rows, cols, st);
+  return out_dtype == DTQ_E4M3 ? launch_by_outputs<CAST<DTQ_F32, DTQ_E4M3>>(in, out, out_t, scale, scale_out, amax_out, rows, cols, st)
+                               : launch_by_outputs<CAST<DTQ_F32, DTQ_E5M2>>(in, out, out_t, scale, scale_out, amax_out, rows, cols, st);
 }
 
 }  // namespace
@@ -282,7 +297,7 @@ extern "C" int dtq_saturated_cast_transposed(const void *in, void *out, void *ou
   bool nothing = false;
   if (int e = check_transposed_args(in, out_t, scale, rows, cols, in_dtype, out_dtype, &nothing)) return e;
   if (nothing) return DTQ_OK;
-  return launch_by_dtypes<Cast>(in, out, out_t, scale, nullptr, rows, cols, in_dtype, out_dtype,
+  return launch_by_dtypes<Cast>(in, out, out_t, scale, nullptr, nullptr, rows, cols, in_dtype, out_dtype,
                                 static_cast<cudaStream_t>(stream));
 }
 
@@ -292,6 +307,24 @@ extern "C" int dtq_cast_with_amax_transposed(const void *in, void *out, void *ou
   bool nothing = false;
   if (int e = check_transposed_args(in, out_t, amax, rows, cols, in_dtype, out_dtype, &nothing)) return e;
   if (nothing) return DTQ_OK;  // like dtq_cast_with_amax on an empty input, scale_out is left alone
-  return launch_by_dtypes<DynCast>(in, out, out_t, amax, scale_out, rows, cols, in_dtype, out_dtype,
+  return launch_by_dtypes<DynCast>(in, out, out_t, amax, scale_out, nullptr, rows, cols, in_dtype, out_dtype,
                                    static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dtq_dynamic_scaled_quant_dual(const void *in, void *out, void *out_t, float *amax_out, float *scale_out,
+                                             int64_t rows, int64_t cols, int in_dtype, int out_dtype, void *workspace,
+                                             size_t workspace_bytes, void *stream) {
+  using namespace dtq;
+  if (!workspace || workspace_bytes < sizeof(Workspace) || !aligned_to(workspace, 256)) return DTQ_ERR_WORKSPACE;
+  Workspace *ws = static_cast<Workspace *>(workspace);
+  bool nothing = false;
+  if (int e = check_transposed_args(in, out_t, &ws->amax, rows, cols, in_dtype, out_dtype, &nothing)) return e;
+  if (nothing || !out) return nothing ? DTQ_OK : DTQ_ERR_INVALID_ARGUMENT;
+  if (!aligned_to(in, in_dtype == DTQ_BF16 ? 2 : 4)) return DTQ_ERR_INVALID_ARGUMENT;
+  DeviceInfo dev;
+  if (int e = current_device_info(&dev)) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the amax lands in the workspace; the cast is queued behind it so that it may become resident under its tail
+  if (int e = launch_amax(in, &ws->amax, rows * cols, in_dtype, ws, dev, st)) return e;
+  return launch_by_dtypes<DynCast>(in, out, out_t, &ws->amax, scale_out, amax_out, rows, cols, in_dtype, out_dtype, st);
 }

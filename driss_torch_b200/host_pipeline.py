@@ -71,19 +71,39 @@ class HostQuantizer:
         self.s_out = torch.cuda.Stream(dev)
         with torch.cuda.stream(self.s_compute):
             self.ws = _cabi.workspace(dev)
+        # the buffers were allocated (and some zero-filled) on the constructor's current stream: their first use
+        # on the three side streams must come after that
+        for st in (self.s_in, self.s_compute, self.s_out):
+            st.wait_stream(torch.cuda.current_stream(dev))
         self.submitted = 0
         self.launches = 0
+
+    def close(self) -> None:
+        """Waits for everything in flight and releases the device buffers.  The buffers are used on side
+        streams the caching allocator does not know about, so they must not be freed while work is queued."""
+        for st in (self.s_in, self.s_compute, self.s_out):
+            st.synchronize()
+        self.slots = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
     def _span(self, c):
         r0 = c * self.chunk_rows
         return r0, min(self.rows, r0 + self.chunk_rows)
 
     def submit(self, x_host: torch.Tensor, payload_host: torch.Tensor, mx_payload_host: torch.Tensor,
-               mx_scales_host: torch.Tensor) -> Ticket:
+               mx_scales_host: torch.Tensor, copies_only: bool = False) -> Ticket:
         """Enqueues one matrix and returns at once.  ``x_host`` bf16 [rows, cols] (pinned for asynchronous
         copies); the three outputs are host tensors of the matching fp8 / e8m0 shapes, which must not be
         touched before ``wait``.  If all ``depth`` slots are still in flight, the wait for a free one
-        happens on the device streams, not on the host."""
+        happens on the device streams, not on the host.
+
+        ``copies_only`` issues the same copies on the same streams with the same dependencies but no kernel
+        (the outputs are whatever the device buffers hold): the PCIe bound of this pipeline, for benchmarks."""
         assert x_host.shape == (self.rows, self.cols) and x_host.dtype == torch.bfloat16
         slot = self.slots[self.submitted % len(self.slots)]
         self.submitted += 1
@@ -104,10 +124,11 @@ class HostQuantizer:
             r0, r1 = self._span(c)
             with torch.cuda.stream(self.s_compute):
                 self.s_compute.wait_event(ready_in[c])
-                _cabi.mx_fp8_quantize_amax(slot.x[r0:r1], payload=slot.mx_payload[r0:r1],
-                                           scales=slot.mx_scales[r0 * bpr : r1 * bpr],
-                                           amax_out=slot.partials[c : c + 1], ws=self.ws)
-                launches += 2
+                if not copies_only:
+                    _cabi.mx_fp8_quantize_amax(slot.x[r0:r1], payload=slot.mx_payload[r0:r1],
+                                               scales=slot.mx_scales[r0 * bpr : r1 * bpr],
+                                               amax_out=slot.partials[c : c + 1], ws=self.ws)
+                    launches += 2
                 ev = torch.cuda.Event()
                 ev.record()
             with torch.cuda.stream(self.s_out):
@@ -116,16 +137,18 @@ class HostQuantizer:
                 mx_scales_host[r0 * bpr : r1 * bpr].copy_(slot.mx_scales[r0 * bpr : r1 * bpr], non_blocking=True)
         with torch.cuda.stream(self.s_compute):
             # max over the per-chunk values (each >= 0)
-            _cabi.amax(slot.partials.view(1, -1), out=slot.amax, ws=self.ws)
-            launches += 1
-            if self.group is not None or (dist.is_initialized() and dist.get_world_size() > 1):
+            if not copies_only:
+                _cabi.amax(slot.partials.view(1, -1), out=slot.amax, ws=self.ws)
+                launches += 1
+            if not copies_only and (self.group is not None or (dist.is_initialized() and dist.get_world_size() > 1)):
                 slot.amax.clamp_min_(0.0)
                 dist.all_reduce(slot.amax, op=dist.ReduceOp.MAX, group=self.group)
             for c in range(self.nchunks):
                 r0, r1 = self._span(c)
-                _cabi.cast_with_amax(slot.x[r0:r1], slot.amax, self.fp8_dtype, out=slot.payload[r0:r1],
-                                     scale_out=slot.scale)
-                launches += 1
+                if not copies_only:
+                    _cabi.cast_with_amax(slot.x[r0:r1], slot.amax, self.fp8_dtype, out=slot.payload[r0:r1],
+                                         scale_out=slot.scale)
+                    launches += 1
                 ev = torch.cuda.Event()
                 ev.record()
                 with torch.cuda.stream(self.s_out):
@@ -135,7 +158,8 @@ class HostQuantizer:
             done = torch.cuda.Event()
             done.record()
         slot.done = done
-        self.launches = launches
+        if not copies_only:
+            self.launches = launches
         return Ticket(slot, done, launches)
 
     def wait(self, ticket: Ticket):

@@ -12,7 +12,7 @@ The reference has no multi-GPU path; the per-shard arithmetic is its kernels'
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -32,6 +32,10 @@ def shard_rows(rows: int, world_size: int, rank: int, multiple: int = 1) -> Tupl
     return start, stop
 
 
+class ExchangeTimeout(RuntimeError):
+    """A bounded device-side wait for a peer's value gave up."""
+
+
 class _CudaKernels:
     """The product kernels; resolved lazily so that importing this module needs no GPU."""
 
@@ -49,16 +53,37 @@ class ShardedQuantizer:
     that the host logic can be exercised on CPU ranks with another implementation.
     """
 
+    #: Polls a rank spends waiting for its peers' maxima before it gives up (each poll is a round trip to
+    #: its own exchange buffer plus a short sleep: this default is on the order of half a minute, so that
+    #: ordinary skew between processes -- a first-iteration compile, a data-loader stall -- never trips it).
+    DEFAULT_SPIN_LIMIT = 1 << 24
+
     def __init__(self, group: Optional[dist.ProcessGroup] = None, kernels=None, fused_exchange: bool = False,
-                 device=None):
+                 device=None, spin_limit: Optional[int] = None, exchange_buffers: Optional[Sequence[int]] = None,
+                 rank: Optional[int] = None):
         """``fused_exchange=True`` (CUDA ranks of one node only): ``tensorwise`` becomes ONE kernel launch
         per GPU that exchanges the per-GPU maxima itself through NVLink peer memory instead of calling a
         collective between an amax launch and a cast launch.  It needs a small symmetric buffer, set up
-        here once (a collective call: construct the quantizer on every rank)."""
+        here once (a collective call: construct the quantizer on every rank).
+
+        ``spin_limit``: how long a rank waits for its peers inside the kernel (see DEFAULT_SPIN_LIMIT).  A
+        wait that runs out does not hang the GPU: the kernel returns, amax / scale come back as NaN, and
+        the next call on this quantizer -- or ``check()`` -- raises ``ExchangeTimeout``.
+
+        ``exchange_buffers`` / ``rank``: for a host that maps the peers' exchange buffers itself instead of
+        going through ``torch.distributed`` symmetric memory: entry r is rank r's buffer
+        (``dtq_p2p_exchange_bytes()`` zero-filled bytes) as addressable from this device."""
         self.group = group
         self.kernels = _CudaKernels() if kernels is None else kernels
+        self.spin_limit = self.DEFAULT_SPIN_LIMIT if spin_limit is None else int(spin_limit)
         self._exchange = None
-        if fused_exchange:
+        self._rank = rank
+        self._watched = {}  # workspace data_ptr -> (workspace, pinned mirror of its status word)
+        if exchange_buffers is not None:
+            if rank is None or not (0 <= rank < len(exchange_buffers)):
+                raise ValueError("exchange_buffers needs this process's rank among them")
+            self._exchange = dict(buffer=None, handle=None, ptrs=[int(p) for p in exchange_buffers], epoch=0)
+        elif fused_exchange:
             self._setup_exchange(device)
 
     def _setup_exchange(self, device) -> None:
@@ -80,11 +105,45 @@ class ShardedQuantizer:
 
     @property
     def world_size(self) -> int:
+        if self._exchange is not None and self._exchange["handle"] is None:
+            return len(self._exchange["ptrs"])
         return dist.get_world_size(self.group) if dist.is_initialized() else 1
 
     @property
     def rank(self) -> int:
+        if self._rank is not None:
+            return self._rank
         return dist.get_rank(self.group) if dist.is_initialized() else 0
+
+    # ---- a peer that never arrives ---------------------------------------------------------------------
+    def _workspace(self, shard: torch.Tensor) -> torch.Tensor:
+        """The workspace of the shard's device and current stream, watched from now on by ``check``."""
+        from . import _cabi
+
+        ws = _cabi.workspace(shard.device)
+        if ws.data_ptr() not in self._watched:
+            self._watched[ws.data_ptr()] = (ws, torch.zeros(1, dtype=torch.int32).pin_memory())
+        return ws
+
+    def _mirror_status(self, ws: torch.Tensor) -> None:
+        from . import _cabi
+
+        _cabi.workspace_status_async(ws, self._watched[ws.data_ptr()][1])
+
+    def check(self, synchronize: bool = False) -> None:
+        """Raises ``ExchangeTimeout`` if a bounded device-side wait of an earlier call on this quantizer gave
+        up (a peer never made the matching call).  Without ``synchronize`` nothing blocks: the status words
+        are read from pinned host mirrors that each exchanging call refreshes behind itself, so a timeout
+        shows here once the stream has passed that call.  With ``synchronize`` the streams are drained first."""
+        from . import _cabi
+
+        for ws, mirror in self._watched.values():
+            status = _cabi.workspace_status(ws) if synchronize else int(mirror.item())
+            if status != 0:
+                raise ExchangeTimeout(
+                    f"rank {self.rank}: {_cabi.load().dtq_status_string(status).decode()} (status {status}): a peer did not "
+                    "make the matching call in time; the amax / scale / payload of that call are not valid, and the "
+                    "workspace must be re-initialised (dtq_workspace_init) before it is used again")
 
     def global_amax(self, shard: torch.Tensor) -> torch.Tensor:
         """max |x| over every rank's shard, as fp32 [1] on the shard's device (one collective)."""
@@ -112,14 +171,17 @@ class ShardedQuantizer:
     def _tensorwise_fused_exchange(self, shard: torch.Tensor, dtype: torch.dtype):
         from . import _cabi
 
+        self.check()
         ex = self._exchange
         ex["epoch"] += 1  # the same sequence on every rank: all ranks make the same calls
         if not shard.is_contiguous():
             raise ValueError("the shard must be contiguous")
         amax = torch.empty(1, dtype=torch.float32, device=shard.device)
         scale = torch.empty(1, dtype=torch.float32, device=shard.device)
+        ws = self._workspace(shard)
         payload = _cabi.dynamic_scaled_quant_p2p(shard, dtype, ex["ptrs"], self.rank, ex["epoch"], amax_out=amax,
-                                                 scale_out=scale)
+                                                 scale_out=scale, ws=ws, spin_limit=self.spin_limit)
+        self._mirror_status(ws)
         return payload, amax, scale
 
     def tensorwise_and_mx(self, shard: torch.Tensor, dtype: torch.dtype):
@@ -136,10 +198,15 @@ class ShardedQuantizer:
         if self._exchange is not None:
             from . import _cabi
 
+            self.check()
             ex = self._exchange
             ex["epoch"] += 1
-            mx_payload, mx_scales, amax = _cabi.mx_fp8_quantize_amax(shard, peer_ptrs=ex["ptrs"], rank=self.rank,
-                                                                      epoch=ex["epoch"])
+            ws = self._workspace(shard)
+            mx_payload, mx_scales, amax = _cabi.mx_fp8_quantize_amax(shard, ws=ws, peer_ptrs=ex["ptrs"], rank=self.rank,
+                                                                      epoch=ex["epoch"], spin_limit=self.spin_limit)
+            payload, scale = self.kernels.cast_with_amax(shard, amax, dtype)
+            self._mirror_status(ws)
+            return payload, amax, scale, mx_payload, mx_scales
         else:
             mx_payload, mx_scales, amax = self.kernels.mx_fp8_quantize_with_amax(shard)
             if self.world_size > 1:

@@ -60,6 +60,13 @@ size_t dtq_workspace_bytes(void);
 int dtq_workspace_init(void *workspace, size_t workspace_bytes, void *stream);
 /* Copies the sticky device-side status word to the host (synchronises `stream`). */
 int dtq_workspace_status(const void *workspace, int *status_host, void *stream);
+/*
+ * The same without synchronising: enqueues the 4-byte copy on `stream` and returns.  `status_host`
+ * should be page-locked; it holds the status as of this point of the stream once the stream has
+ * got there (a host that polls it before its next call learns of a timeout one call late, but
+ * never blocks).
+ */
+int dtq_workspace_status_async(const void *workspace, int *status_host, void *stream);
 
 /*
  * out[i] = fp8_satfinite(in[i] * scale), i < numel, over flat storage.
@@ -100,6 +107,19 @@ int dtq_cast_with_amax_transposed(const void *in, void *out, void *out_t, const 
                                   int64_t rows, int64_t cols, int in_dtype, int out_dtype, void *stream);
 
 /*
+ * Tensor-wise dynamic quantisation of a contiguous [rows, cols] input into both orientations:
+ *   amax = max |in| (>= 0, NaNs dropped); out = dtq_cast_with_amax(in), out_t = dtq_cast_with_amax(transpose(in)),
+ * i.e. dtq_dynamic_scaled_quant's payload for x and for x^T.  Two launches queued by this one call: the
+ * amax kernel and, started under its tail (programmatic dependent launch), the kernel that converts
+ * every element once and writes it in both orientations.  amax_out / scale_out: one fp32 each,
+ * nullable.  `out` and `out_t` are both required.  Needs an initialised workspace.  No reference
+ * counterpart (the reference's fused op, src/dynamic_scaled_quant.cu:83-176, has one orientation).
+ */
+int dtq_dynamic_scaled_quant_dual(const void *in, void *out, void *out_t, float *amax_out, float *scale_out,
+                                  int64_t rows, int64_t cols, int in_dtype, int out_dtype, void *workspace,
+                                  size_t workspace_bytes, void *stream);
+
+/*
  * out[0] = max_i |in[i]| as fp32 (-inf for numel == 0; NaNs are dropped), one
  * launch, no pre-initialised output.
  * Replaces driss_torch::amax and amax_kernel: src/amax.cu:50-80, :82-119.
@@ -120,7 +140,9 @@ int dtq_amax(const void *in, float *out, int64_t numel, int in_dtype, void *work
  *     current); make that first call before any stream capture begins;
  *   - every call on a device uses the same array: calls that may overlap on the GPU
  *     (different streams, several host threads) race -- serialise them on one stream;
- *   - the arrival counter in the array is cleared on `stream` before each launch.
+ *   - the arrival counter in the array is cleared on `stream` before each launch;
+ *   - the looked-up address is cached per device for the life of the process: it belongs to the
+ *     device's primary context, so do not call this entry point again after cudaDeviceReset.
  * No counterpart in the reference (its amax allocates its output and relies on a fill launch).
  */
 #define DTQ_AMAX_STATIC_MAX_BYTES (268435456LL) /* 256 MiB: 4096 tiles x 64 KiB */
@@ -153,7 +175,8 @@ int dtq_dynamic_scaled_quant(const void *in, void *out, float *amax_out, float *
  *   epoch            = 1, 2, 3, ... : the same value on every rank for the same call;
  *   spin_limit       = polls before the wait for the peers gives up (0 = default, about 1 s);
  *                      a rank that never arrives makes the others return with
- *                      DTQ_ERR_TIMEOUT in the workspace status word instead of hanging
+ *                      DTQ_ERR_TIMEOUT in the workspace status word instead of hanging: no
+ *                      payload is written, amax_out / scale_out receive NaN
  *                      (re-initialise the workspace afterwards).
  * `in` must be 16-byte and `out` 8-byte (bf16) / 4-byte (fp32) aligned.  No reference counterpart
  * (the reference has no multi-GPU path); arithmetic as dtq_dynamic_scaled_quant.
@@ -216,7 +239,7 @@ int dtq_mx_fp8_quantize_amax(const void *in_bf16, void *payload, void *scales_e8
  * enqueued right behind it: no collective call.  peer_exchange, rank, world,
  * epoch, spin_limit: as for dtq_dynamic_scaled_quant_p2p (the two calls may share the exchange
  * buffers and the epoch sequence).  A peer that never arrives: DTQ_ERR_TIMEOUT in the workspace
- * status word, amax_out[0] = 0.
+ * status word, amax_out[0] = NaN (dtq_cast_with_amax passes a NaN amax on to its scale_out).
  */
 int dtq_mx_fp8_quantize_amax_p2p(const void *in_bf16, void *payload, void *scales_e8m0, float *amax_out,
                                  int64_t rows, int64_t cols, void *workspace, size_t workspace_bytes,
@@ -247,6 +270,8 @@ int dtq_mx_quantize(const void *in, void *payload, void *scales_e8m0, int64_t ro
  * byte for byte.  The reference declares `axis` and `transpose` on its op but ignores them
  * (src/mx_cast.cu:168-171); getting the second operand there takes a transpose and a second
  * cast.  `in` 16-byte, `payload` 8-byte, `payload_t` 16-byte aligned.
+ * `payload` may be NULL (`scales_e8m0` is then ignored): only the transposed pair is written, which
+ * is what the schema's own `transpose` / `axis = 0` arguments ask for.
  */
 int dtq_mx_fp8_quantize_dual(const void *in_bf16, void *payload, void *scales_e8m0, void *payload_t,
                              void *scales_t_e8m0, int64_t rows, int64_t cols, void *stream);

@@ -8,7 +8,8 @@ legs may import it.
   (``quant_oracle.c``) of the reference CUDA kernels' arithmetic.
 * ``eager`` -- the PyTorch-eager formulas the reference's own tests compare
   against (test/test_sat_cast.py:7-24, test/test_amax.py:6-7), for CPU tensors.
-* ``inputs`` -- seeded synthetic input generators shared by tests and bench.
+* ``cute_sf_layout.cpp`` -- CUTLASS's own blocked scale-factor layout evaluated on the host
+  (pins the index map of the blocked MX scales).
 * ``_ref/`` -- (built by ``Makefile.ref``) the unmodified reference CUDA ops,
   bound under ``torch.ops.DrissTorchRef`` by ``ref_binding.cpp``.
 """

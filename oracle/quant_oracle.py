@@ -130,10 +130,11 @@ def amax(x: torch.Tensor) -> torch.Tensor:
     return torch.tensor([v], dtype=torch.float32)
 
 
-def cast_with_amax(x: torch.Tensor, amax_value: float, out_dtype: torch.dtype):
-    """Cast phase of the fused op for a given (e.g. all-reduced) amax."""
+def cast_with_amax(x: torch.Tensor, amax_value: float, out_dtype: torch.dtype, out: torch.Tensor | None = None):
+    """Cast phase of the fused op for a given (e.g. all-reduced) amax; ``out``: a uint8 buffer to reuse."""
     x = _chk(x)
-    out = torch.empty(x.shape, dtype=torch.uint8)
+    out = torch.empty(x.shape, dtype=torch.uint8) if out is None else out
+    assert out.dtype == torch.uint8 and out.is_contiguous() and out.numel() == x.numel()
     scale = torch.empty(1, dtype=torch.float32)
     lib().oracle_cast_with_amax(
         x.data_ptr(), _IN[x.dtype], float(amax_value), out.data_ptr(), x.numel(), _OUT[out_dtype], scale.data_ptr()
@@ -167,12 +168,15 @@ def dynamic_scaled_quant_rowwise(x: torch.Tensor, out_dtype: torch.dtype):
     return out.view(out_dtype), am, sc
 
 
-def mx_fp8_quantize(x: torch.Tensor):
-    """bf16 [M, N] with N % 32 == 0 -> (e4m3 payload [M, N], e8m0 scales [M * N / 32])."""
+def mx_fp8_quantize(x: torch.Tensor, payload: torch.Tensor | None = None, scales: torch.Tensor | None = None):
+    """bf16 [M, N] with N % 32 == 0 -> (e4m3 payload [M, N], e8m0 scales [M * N / 32]); ``payload`` /
+    ``scales``: uint8 buffers to reuse."""
     x = _chk(x)
     assert x.dtype == torch.bfloat16 and x.numel() % 32 == 0
-    payload = torch.empty(x.shape, dtype=torch.uint8)
-    scales = torch.empty(x.numel() // 32, dtype=torch.uint8)
+    payload = torch.empty(x.shape, dtype=torch.uint8) if payload is None else payload
+    scales = torch.empty(x.numel() // 32, dtype=torch.uint8) if scales is None else scales
+    assert payload.dtype == torch.uint8 and payload.is_contiguous() and payload.numel() == x.numel()
+    assert scales.dtype == torch.uint8 and scales.is_contiguous() and scales.numel() == x.numel() // 32
     lib().oracle_mx_fp8_quantize(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), x.numel() // 32)
     return payload.view(torch.float8_e4m3fn), scales.view(torch.float8_e8m0fnu)
 

@@ -216,3 +216,14 @@ def test_workload_generators_are_deterministic_and_shaped_as_described():
     assert set(w.WORKLOADS) == {"cfg1", "cfg2", "cfg3", "cfg4", "cfg5"}
     sc = w.tensor_scale(w.make_cfg1(rows=64, cols=64), torch.float8_e4m3fn)
     assert sc.shape == (1,) and sc.dtype == torch.float32
+
+
+def test_the_reference_package_name_resolves_to_the_same_ops():
+    # existing callers write `import driss_torch` (driss_torch/__init__.py in the reference)
+    import driss_torch
+    import driss_torch.abstract_impls  # noqa: F401  (the module name the reference's library declares)
+    import driss_torch_b200 as dt
+
+    for name in ("saturated_cast", "amax", "dynamic_scaled_quant", "mx_fp8_quantize", "mx_cast"):
+        assert getattr(driss_torch, name) is getattr(dt, name)
+    assert driss_torch.ops is torch.ops.DrissTorch

@@ -160,9 +160,10 @@ def test_errors_and_compile():
         dt.dynamic_scaled_quant(a.t(), torch.float8_e4m3fn)  # must be contiguous, as in the reference
     with pytest.raises(RuntimeError):
         dt.dynamic_scaled_quant(a.view(-1), torch.float8_e4m3fn)
-    torch._dynamo.reset()
-    fn = torch.compile(dt.dynamic_scaled_quant, fullgraph=True, backend="aot_eager")
-    assert_fp8_equal(fn(a, torch.float8_e4m3fn), dt.dynamic_scaled_quant(a, torch.float8_e4m3fn))
+    for backend in ("aot_eager", "inductor"):  # the reference compiles with the default backend
+        torch._dynamo.reset()
+        fn = torch.compile(dt.dynamic_scaled_quant, fullgraph=True, backend=backend)
+        assert_fp8_equal(fn(a, torch.float8_e4m3fn), dt.dynamic_scaled_quant(a, torch.float8_e4m3fn))
     dt.check_device_status()
 
 

@@ -162,3 +162,40 @@ def test_other_mx_formats_full_size_properties():
     scale = torch.exp2(e5.float() - 127).view(x.shape[0], -1, 1)
     err = (p5.float().view(x.shape[0], -1, 32) * scale - x.float().view(x.shape[0], -1, 32)).abs()
     assert bool((err <= scale * 2.0**13 * 0.5 + 1e-30).all())  # e5m2: two mantissa bits, largest binade 2^15
+
+
+def test_cfg5_full_size_step_vs_oracle_chunk_by_chunk():
+    # The benchmark's own workload at its own size: bf16 [262144, 8192] (4 GiB) as 8 seeded row chunks, run through
+    # the step the benchmark times (MX cast that delivers the amax, then the tensor-wise cast) and compared with the
+    # C oracle byte for byte, one chunk at a time -- the comparison of the reference's own small tests
+    # (test/test_dynamic_quant.py:28-44, test/test_mx.py:70-94) at full size.  Host memory stays near 3 GB.
+    from driss_torch_b200 import ShardedQuantizer
+
+    chunks, chunk_rows, cols = 8, workloads.CFG5_CHUNK_ROWS, workloads.WORKLOADS["cfg5"].cols
+    x = torch.empty(chunks * chunk_rows, cols, dtype=torch.bfloat16, device="cuda")
+    oracle_amax = 0.0
+    for c in range(chunks):
+        part = workloads.make_cfg5_chunk(c)  # CPU generator: the one source of the values
+        oracle_amax = max(oracle_amax, qo.amax(part).item())
+        x[c * chunk_rows:(c + 1) * chunk_rows].copy_(part)
+        del part
+    payload, amax, scale, mx_payload, mx_scales = ShardedQuantizer().tensorwise_and_mx(x, E4M3)
+    torch.cuda.synchronize()
+    assert amax.item() == oracle_amax
+    bpr = cols // 32
+    sums = [0, 0, 0]
+    for c in range(chunks):
+        r0, r1 = c * chunk_rows, (c + 1) * chunk_rows
+        part = x[r0:r1].cpu()
+        want, want_scale = qo.cast_with_amax(part, oracle_amax, E4M3)
+        _same(payload[r0:r1].cpu(), want, f"cfg5 tensor-wise payload, chunk {c}")
+        assert want_scale.item() == scale.item()
+        want_p, want_s = qo.mx_fp8_quantize(part)
+        _same(mx_payload[r0:r1].cpu(), want_p, f"cfg5 MX payload, chunk {c}")
+        _same(mx_scales[r0 * bpr:r1 * bpr].cpu(), want_s, f"cfg5 MX scales, chunk {c}")
+        for i, t in enumerate((want, want_p, want_s)):
+            sums[i] += int(t.view(torch.uint8).sum(dtype=torch.int64))
+        del part, want, want_p, want_s
+    # the byte sums the benchmark prints as output_checksums, from the oracle's outputs
+    got = [int(t.view(torch.uint8).sum(dtype=torch.int64)) for t in (payload, mx_payload, mx_scales)]
+    assert got == sums

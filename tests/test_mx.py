@@ -128,8 +128,9 @@ def test_errors_and_compile():
     for bad in (
         lambda: dt.mx_fp8_quantize(a.double()),
         lambda: dt.mx_fp8_quantize(a, block_size=16),
-        lambda: dt.mx_fp8_quantize(a, axis=0),
-        lambda: dt.mx_fp8_quantize(a, transpose=True),
+        lambda: dt.mx_fp8_quantize(a, axis=2),
+        lambda: dt.mx_fp8_quantize(a[:48], transpose=True),  # rows not a multiple of 32
+        lambda: dt.mx_fp8_quantize(a, axis=0, ScalarType=torch.float8_e5m2),
         lambda: dt.mx_fp8_quantize(a, ScalarType=torch.float16),
         lambda: dt.mx_fp4_quantize(a[:, :48]),
         lambda: dt.mx_fp4_quantize(a.double()),
@@ -141,10 +142,41 @@ def test_errors_and_compile():
             bad()
     assert dt.mx_cast is dt.mx_fp8_quantize
     torch._dynamo.reset()
-    fn = torch.compile(dt.mx_fp8_quantize, fullgraph=True, backend="aot_eager")
-    p, s = fn(a)
     p0, s0 = dt.mx_fp8_quantize(a)
-    assert torch.equal(as_bytes(p), as_bytes(p0)) and torch.equal(as_bytes(s), as_bytes(s0))
+    for backend in ("aot_eager", "inductor"):  # the reference's tests compile with the default backend
+        torch._dynamo.reset()
+        fn = torch.compile(dt.mx_fp8_quantize, fullgraph=True, backend=backend)
+        p, s = fn(a)
+        assert torch.equal(as_bytes(p), as_bytes(p0)) and torch.equal(as_bytes(s), as_bytes(s0))
+
+
+@pytest.mark.parametrize("rows,cols", [(32, 32), (128, 64), (96, 288), (1024, 512)])
+def test_axis_and_transpose_arguments_of_the_schema(rows, cols):
+    # the reference declares both and ignores them (src/mx_cast.cu:168-171); here: transpose=True is the op on
+    # input.t(), axis=0 puts the blocks down the columns, both together cancel up to the payload's view
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg3(rows=rows, cols=cols)
+    ad = a.cuda()
+    want_p, want_s = qo.mx_fp8_quantize(a)
+    want_pt, want_st = qo.mx_fp8_quantize(a.t().contiguous())
+    p, s = dt.mx_fp8_quantize(ad, transpose=True)
+    assert p.shape == (cols, rows) and p.is_contiguous()
+    assert_fp8_equal(p, want_pt, E4M3, "transpose=True payload")
+    assert torch.equal(as_bytes(s), as_bytes(want_st))
+    p, s = dt.mx_fp8_quantize(ad, axis=0)
+    assert p.shape == (rows, cols)
+    assert_fp8_equal(p.t(), want_pt, E4M3, "axis=0 payload")
+    assert torch.equal(as_bytes(s), as_bytes(want_st))
+    p, s = dt.mx_fp8_quantize(ad, axis=0, transpose=True)
+    assert p.shape == (cols, rows)
+    assert_fp8_equal(p.t(), want_p, E4M3, "axis=0, transpose=True payload")
+    assert torch.equal(as_bytes(s), as_bytes(want_s))
+    torch._dynamo.reset()
+    fn = torch.compile(lambda t: dt.mx_fp8_quantize(t, axis=0), fullgraph=True, backend="aot_eager")
+    q, qs = fn(ad)
+    assert q.shape == (rows, cols) and q.stride() == (1, rows)
+    assert_fp8_equal(q.t(), want_pt, E4M3, "compiled axis=0 payload")
 
 
 # ---- scales in the blocked layout of the MX GEMM ------------------------------------------------------

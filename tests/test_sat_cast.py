@@ -169,8 +169,24 @@ def test_compile_fullgraph_uses_fake_impl():
     torch._dynamo.reset()
     a = torch.rand(64, 127, device="cuda").to(torch.bfloat16)
     s = workloads.tensor_scale(a, torch.float8_e4m3fn)
-    fn = torch.compile(dt.saturated_cast, fullgraph=True, backend="aot_eager")
-    assert_fp8_equal(fn(a, s, torch.float8_e4m3fn), dt.saturated_cast(a, s, torch.float8_e4m3fn))
+    for backend in ("aot_eager", "inductor"):  # the reference compiles with the default backend
+        torch._dynamo.reset()
+        fn = torch.compile(dt.saturated_cast, fullgraph=True, backend=backend)
+        assert_fp8_equal(fn(a, s, torch.float8_e4m3fn), dt.saturated_cast(a, s, torch.float8_e4m3fn))
+
+
+def test_transpose_argument_of_the_operator():
+    # the wrapper keeps the reference's assert (driss_torch/__init__.py:37); the operator's own flag, which the
+    # reference only uses to choose a kernel (src/saturated_cast.cu:168-181), gives the cast of input.t()
+    import driss_torch_b200 as dt
+
+    a = workloads.make_cfg1(rows=160, cols=96)
+    for fp8_dtype in FP8_DTYPES:
+        s = workloads.tensor_scale(a, fp8_dtype)
+        want = qo.saturated_cast(a, s.item(), fp8_dtype)
+        got = torch.ops.DrissTorch.saturated_cast(a.cuda(), s.cuda(), fp8_dtype, True)
+        assert got.shape == (96, 160) and got.is_contiguous()
+        assert_fp8_equal(got, want.t().contiguous(), fp8_dtype, "transpose=True")
 
 
 # ---- transposed output / both orientations from one read -----------------------------------------------

@@ -154,9 +154,55 @@ def test_fused_exchange_single_rank_and_missing_peer_timeout():
     p, s_, am = _cabi.mx_fp8_quantize_amax(xd, ws=ws, peer_ptrs=[mine.data_ptr(), silent_peer.data_ptr()], rank=0, epoch=7,
                                            spin_limit=2000)
     torch.cuda.synchronize()  # returns: nothing hangs
-    assert _cabi.workspace_status(ws) == 5 and am.item() == 0.0
+    assert _cabi.workspace_status(ws) == 5 and torch.isnan(am).all()  # NaN, never a value that could pass for a maximum
     assert torch.equal(as_bytes(p), as_bytes(want_p))  # the MX outputs do not depend on the peers
     # a fresh workspace and the ordinary op still work
     _cabi.check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), stream), "init")
     assert torch.equal(as_bytes(_cabi.dynamic_scaled_quant(xd, E4M3, ws=ws)), as_bytes(want))
     assert _cabi.workspace_status(ws) == 0
+
+
+def test_sharded_quantizer_reports_a_peer_that_never_arrives():
+    # Through the public class, one process: rank 0 of a world of two whose peer buffer nobody writes.  The
+    # bounded wait runs out (a small spin_limit keeps that to milliseconds), the launches return, amax and scale
+    # come back as NaN so that nothing can consume them unnoticed, and the quantizer raises -- from check(),
+    # and by itself at the top of the next exchanging call -- without any GPU fault or hang.
+    import driss_torch_b200 as dt
+    from driss_torch_b200 import _cabi
+    from driss_torch_b200.sharded import ExchangeTimeout
+
+    lib = _cabi.load()
+    x = workloads.make_cfg2(rows=512, cols=1024).cuda()
+    nwords = lib.dtq_p2p_exchange_bytes() // 8
+    mine = torch.zeros(nwords, dtype=torch.int64, device="cuda")
+    silent_peer = torch.zeros_like(mine)
+    side = torch.cuda.Stream()  # its own stream, hence its own workspace: the default stream's stays clean
+    with torch.cuda.stream(side):
+        q = dt.ShardedQuantizer(exchange_buffers=[mine.data_ptr(), silent_peer.data_ptr()], rank=0, spin_limit=2000)
+        assert q.world_size == 2 and q.rank == 0
+        q.check()  # nothing has run yet
+        payload, amax, scale, mx_p, mx_s = q.tensorwise_and_mx(x, E4M3)
+        side.synchronize()
+        assert torch.isnan(amax).all() and torch.isnan(scale).all()
+        want_p, want_s = qo.mx_fp8_quantize(x.cpu())
+        assert torch.equal(as_bytes(mx_p), as_bytes(want_p)) and torch.equal(as_bytes(mx_s), as_bytes(want_s))
+        with pytest.raises(ExchangeTimeout):
+            q.check()  # no synchronisation needed: the pinned mirror was refreshed behind the call
+        with pytest.raises(ExchangeTimeout):
+            q.tensorwise(x, E4M3)  # the next call refuses to build on a broken exchange
+        # the single-launch form reports the same way
+        ws = _cabi.workspace(x.device)
+        _cabi.check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), side.cuda_stream), "init")
+        q2 = dt.ShardedQuantizer(exchange_buffers=[mine.data_ptr(), silent_peer.data_ptr()], rank=0, spin_limit=2000)
+        q2._exchange["epoch"] = 10
+        _, amax2, scale2 = q2.tensorwise(x, E4M3)
+        with pytest.raises(ExchangeTimeout):
+            q2.check(synchronize=True)
+        assert torch.isnan(amax2).all() and torch.isnan(scale2).all()
+        _cabi.check(lib.dtq_workspace_init(ws.data_ptr(), ws.numel(), side.cuda_stream), "init")
+        side.synchronize()
+    # the context is intact and the ordinary ops still work
+    want, want_amax, _ = qo.dynamic_scaled_quant(x.cpu(), E4M3)
+    got, am, _ = dt.dynamic_scaled_quant_with_scale(x, E4M3)
+    assert torch.equal(as_bytes(got), as_bytes(want)) and am.item() == want_amax.item()
+    dt.check_device_status()

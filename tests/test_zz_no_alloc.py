@@ -30,11 +30,14 @@ def test_two_calls_in_a_row_match_the_workspace_entry_point(in_dtype):
     first = (torch.randn(2048, 4096, generator=g) * 3.0).to(in_dtype).cuda()
     second = (torch.randn(777, 1031, generator=g) * 0.01).to(in_dtype).cuda()  # ragged, smaller maximum
     out = torch.full((1,), -7.0, device="cuda")
+    from oracle import quant_oracle as qo
+
     for x in (first, second):
         want = _cabi.amax(x)                       # existing entry point, caller-provided workspace
         got = _cabi.amax_static_scratch(x, out=out)  # new entry point, nothing allocated by the library
         torch.cuda.synchronize()
         assert _bits(got) == _bits(want), f"{tuple(x.shape)} {in_dtype}"
+        assert _bits(got) == _bits(qo.amax(x.cpu())), "against the CPU restatement of the reference kernel"
     # and once more on the first input: the array now holds the second call's partials
     assert _bits(_cabi.amax_static_scratch(first, out=out)) == _bits(_cabi.amax(first))
 
