@@ -95,6 +95,14 @@ def mx_fp8_quantize(
     return ops.mx_fp8_quantize(input, block_size, axis, transpose, ScalarType)
 
 
+def mx_fp8_bf16(a: Tensor, b: Tensor, a_scale: Tensor, b_scale: Tensor) -> Tensor:
+    """Matrix multiplication of two MX-quantised e4m3 operands with E8M0 scales of 32 elements along K
+    (driss_torch/__init__.py:80-95): ``a`` [M, K] row-major, ``b`` [K, N] column-major (``w.t()`` of a
+    row-major [N, K] payload), ``a_scale`` / ``b_scale`` in the blocked layout ``mx_fp8_quantize_blocked``
+    writes; returns bf16 [M, N]."""
+    return ops.mx_fp8_bf16(a, b, a_scale, b_scale)
+
+
 # The north-star text calls the MX op "mx_cast"; the reference symbol is mx_fp8_quantize.
 mx_cast = mx_fp8_quantize
 
@@ -171,6 +179,7 @@ __all__ = [
     "dynamic_scaled_quant",
     "mx_fp8_quantize",
     "mx_cast",
+    "mx_fp8_bf16",
     "dynamic_scaled_quant_with_scale",
     "dynamic_scaled_quant_rowwise",
     "cast_with_amax",

@@ -39,6 +39,11 @@ def mx_fp8_quantize_meta(x: torch.Tensor, block_size: int, axis: int, transpose:
     return (payload.t() if transpose else payload), scales
 
 
+@register_fake("DrissTorch::mx_fp8_bf16")
+def mx_fp8_bf16_meta(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_scale: torch.Tensor):
+    return torch.empty((a.shape[0], b.shape[1]), dtype=torch.bfloat16, device=a.device)
+
+
 @register_fake("DrissTorch::dynamic_scaled_quant_with_scale")
 def dynamic_scaled_quant_with_scale_meta(x: torch.Tensor, dtype: torch.dtype):
     one = lambda: torch.empty(1, dtype=torch.float32, device=x.device)  # noqa: E731

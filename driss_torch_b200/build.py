@@ -40,6 +40,7 @@ KERNEL_SOURCES = [
     "mx_cast_dual.cu",
     "mx_cast_formats.cu",
     "mx_cast_amax.cu",
+    "mx_gemm.cu",
 ]
 
 NVCC_FLAGS = [

@@ -86,6 +86,7 @@ amax_kernel(const void *__restrict__ in, float *__restrict__ out, int64_t numel,
   __shared__ int flag;
   constexpr int kElems = 16 / AbsMax<IN>::kElemBytes;
   pdl_launch_dependents();  // a cast queued behind this launch with launch_after_dependency may become resident early
+  pdl_wait();               // and this launch itself may have started under the tail of its predecessor
   const float identity = -INFINITY;
   AbsMax<IN> acc(identity);
 
@@ -127,10 +128,10 @@ int launch_amax(const void *in, float *out, int64_t numel, int in_dtype, Workspa
   const int grid = amax_grid(numel, eb, dev);
   const int64_t head = head_elems(in, eb, numel);
   if (in_dtype == DTQ_BF16)
-    amax_kernel<DTQ_BF16, kAmaxUnroll><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
-  else
-    amax_kernel<DTQ_F32, kAmaxUnroll><<<grid, kAmaxThreads, 0, st>>>(in, out, numel, head, ws);
-  return cuda_status(cudaGetLastError());
+    return cuda_status(launch_after_dependency(amax_kernel<DTQ_BF16, kAmaxUnroll>, dim3(grid), dim3(kAmaxThreads), 0, st, in,
+                                               out, numel, head, ws));
+  return cuda_status(launch_after_dependency(amax_kernel<DTQ_F32, kAmaxUnroll>, dim3(grid), dim3(kAmaxThreads), 0, st, in, out,
+                                             numel, head, ws));
 }
 
 }  // namespace dtq

@@ -33,6 +33,9 @@ mx_stream_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, ui
                  int64_t nchunks, int64_t kblocks, int64_t katoms) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int64_t kTile = int64_t(kThreads) * kUnroll;
+  // may have become resident under the tail of the kernel before it on the stream: wait for that kernel
+  pdl_launch_dependents();
+  pdl_wait();
   for (int64_t tile = blockIdx.x; tile * kTile < nchunks; tile += gridDim.x) {
     const int64_t warp_first = tile * kTile + int64_t(warp) * (32 * kUnroll);
     uint4 v[kUnroll];
@@ -97,9 +100,9 @@ int launch_mx(const void *in_bf16, void *payload, void *scales_e8m0, int64_t row
     const int64_t nchunks = numel / 8;
     const int64_t tiles = ceil_div64(nchunks, int64_t(kThreads) * kUnroll);
     const int grid = balanced_grid(tiles, max_grid);
-    mx_stream_kernel<BLOCKED><<<grid, kThreads, 0, st>>>(static_cast<const uint4 *>(in_bf16),
-                                                         static_cast<uint8_t *>(payload),
-                                                         static_cast<uint8_t *>(scales_e8m0), nchunks, kblocks, katoms);
+    return cuda_status(launch_after_dependency(mx_stream_kernel<BLOCKED>, dim3(grid), dim3(kThreads), 0, st,
+                                               static_cast<const uint4 *>(in_bf16), static_cast<uint8_t *>(payload),
+                                               static_cast<uint8_t *>(scales_e8m0), nchunks, kblocks, katoms));
   } else {
     const int64_t blocks = ceil_div64(numel / 32, kThreads);
     const int grid = static_cast<int>(blocks < max_grid ? blocks : max_grid);

@@ -1,0 +1,438 @@
+// mx_fp8_bf16: D[M,N] (bf16) = sum_k  A[m,k] * 2^(sa[m,k/32]-127) * B[n,k] * 2^(sb[n,k/32]-127)
+//
+// The consumer of the MX casts: e4m3 operands with one E8M0 scale per 32 elements along K, both
+// scale tensors in the blocked (128 x 4 atoms of 512 bytes) layout that mx_fp8_quantize_blocked
+// emits.  Replaces driss_torch::mx_fp8_bf16 (src/mx_fp8_bf16.cu:42-163 run_gemm, :168-215 validate,
+// :217-241), which instantiates a CUTLASS Sm100 block-scaled collective with 128x128x128 tiles.
+//
+// Hand-written for sm_100a:
+//   * one persistent CTA per SM walks 128 x 256 output tiles; K advances in stages of 128 bytes;
+//   * warp 0 (one lane) is the producer: per stage two tiled TMA loads (A 128 x 128 B, B 256 x 128 B,
+//     128-byte swizzle, out-of-bounds rows and columns filled with zeros) and up to three 512-byte
+//     bulk copies of scale atoms, all counted on the stage's `full` mbarrier; 4 stages = 198 KB;
+//   * warp 1 (one lane) issues the tensor-core work: tcgen05.cp moves the stage's scale atoms from
+//     shared memory into tensor memory (32 rows x 16 bytes, replicated to the four lane quadrants,
+//     which is exactly one blocked atom), then four tcgen05.mma kind::mxf8f6f4.block_scale
+//     instructions (M 128, N 256, K 32), the k-block picking its scale byte through the descriptor's
+//     scale-factor id; tcgen05.commit releases the stage (`empty`) and finally hands the accumulator
+//     (128 lanes x 256 fp32 columns of tensor memory) to the epilogue;
+//   * warps 2..9 are the epilogue: tcgen05.ld 32 columns at a time, fp32 -> bf16, 64-byte row
+//     segments straight to global memory; the accumulator is released as soon as it is in registers,
+//     so the next tile's MMAs overlap the stores.
+// No cluster, no multicast: every CTA loads its own operands (A and B of an 8192^3 problem both fit
+// in L2).  Every wait is bounded: a wait that runs out records DTQ_ERR_TIMEOUT in the status word,
+// raises the CTA's abort flag, the roles drain what they have in flight, tensor memory is freed and
+// the kernel returns.
+#include <cuda.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "dtq_device.cuh"
+#include "dtq_host.h"
+
+namespace dtq {
+namespace {
+
+constexpr int kBM = 128;        // tile rows (M)
+constexpr int kBN = 256;        // tile columns (N)
+constexpr int kBK = 128;        // K bytes per stage: one 128-byte swizzle span = 4 MX blocks of 32
+constexpr int kStagesG = 4;
+constexpr int kGemmThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
+constexpr int kEpilogueWarps = 8;
+constexpr int kAccumCols = kBN;            // fp32 accumulator columns in tensor memory
+constexpr int kSfaCol = kAccumCols;        // 4 columns: scales of 128 rows x 4 k-blocks
+constexpr int kSfbCol = kAccumCols + 8;    // 8 columns: scales of 256 rows x 4 k-blocks
+constexpr int kTmemCols = 512;             // allocation (power of two)
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds of wall time
+
+struct __align__(1024) GemmSmem {
+  uint8_t a[kStagesG][kBM * kBK];      // 16 KB per stage, 1024-byte aligned (swizzle atom = 8 rows x 128 B)
+  uint8_t b[kStagesG][kBN * kBK];      // 32 KB per stage
+  uint8_t sfa[kStagesG][512];          // one blocked atom: 128 rows x 4 k-blocks
+  uint8_t sfb[kStagesG][2 * 512];      // two atoms: 256 rows x 4 k-blocks
+  uint64_t full[kStagesG];
+  uint64_t empty[kStagesG];
+  uint64_t tmem_full;
+  uint64_t tmem_empty;
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// One poll of the phase with the given parity; the thread may sleep up to about a microsecond inside it.
+__device__ __forceinline__ bool mbar_poll(uint32_t addr, unsigned parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(addr), "r"(parity), "r"(1000u)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait for the phase of the given parity: false if it has not completed after kWaitLimitNs of
+// wall time, or if the CTA is aborting (`abort` may be null for a wait that must not be cut short).
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, volatile int *abort) {
+  const uint32_t addr = smem_addr(bar);
+  if (mbar_poll(addr, parity)) return true;
+  const unsigned long long start = global_ns();
+  for (unsigned int spins = 1;; ++spins) {
+    if (mbar_poll(addr, parity)) return true;
+    if ((spins & 63u) == 0) {
+      if (abort && *abort) return false;
+      if (global_ns() - start > kWaitLimitNs) return false;
+    }
+  }
+}
+
+// Tiled TMA load of a box at (x = byte column, y = row) into this CTA's shared memory.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                   smem_addr(dst)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y)
+               : "memory");
+}
+// 1-D bulk copy (16-byte aligned, multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
+               "l"(src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes long and
+// 128-byte swizzled (what the TMA loads above produce): start address, leading byte offset (unused
+// for swizzled K-major tiles, encoded as 1), stride between 8-row groups = 1024 bytes, descriptor
+// version 1, layout type 2 = 128-byte swizzle.  Addresses and offsets are in units of 16 bytes.
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+  return uint64_t((saddr >> 4) & 0x3FFFu) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+         (uint64_t(2) << 61);
+}
+// Descriptor of one scale atom for tcgen05.cp: 32 rows of 16 bytes, no swizzle; 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
+  return uint64_t((saddr >> 4) & 0x3FFFu) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+}
+// Instruction descriptor of tcgen05.mma kind::mxf8f6f4.block_scale: e4m3 x e4m3, both K-major, E8M0 scales,
+// M = 128, N = 256; `k` (0..3) is the byte of the 4-byte scale column that this k-block uses, for A and B.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t k) {
+  return (k << 4) | (uint32_t(kBN >> 3) << 17) | (1u << 23) | (uint32_t(kBM >> 4) << 24) | (k << 29);
+}
+
+__device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// fp32 pair -> packed bf16x2 (lo in the low half).
+__device__ __forceinline__ uint32_t pack_bf16(uint32_t lo, uint32_t hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+  return r;
+}
+
+struct GemmParams {
+  const uint8_t *sfa;  // blocked scales of A: atoms [ceil(M/128)][katoms] of 512 bytes
+  const uint8_t *sfb;  // blocked scales of B: atoms [ceil(N/128)][katoms]
+  uint16_t *out;       // bf16 [M, N]
+  int M, N, K;
+  int m_tiles, n_tiles, k_stages, katoms, n_atoms;
+  int *status;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  GemmSmem &sm = *reinterpret_cast<GemmSmem *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int *abort = &sm.abort;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesG; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 1);
+    }
+    mbar_init(&sm.tmem_full, 1);
+    mbar_init(&sm.tmem_empty, kEpilogueWarps);
+    sm.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // scale staging starts as zeros: an atom that does not exist (N not a multiple of 256) is never copied
+  for (int i = threadIdx.x; i < int(sizeof(sm.sfb) / 4); i += kGemmThreads) reinterpret_cast<uint32_t *>(sm.sfb)[i] = 0;
+  if (warp == 1) {  // the MMA warp owns tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zero fill is read by tcgen05.cp (async proxy)
+  tmem_fence_before();
+  __syncthreads();
+  tmem_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    // ---- producer ---------------------------------------------------------------------------------
+    if (lane == 0) {
+      int64_t it = 0;  // stage uses so far
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;  // consecutive CTAs share a B panel
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = int(it % kStagesG);
+          const unsigned round = unsigned(it / kStagesG);
+          if (*abort || (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1u, abort))) {
+            ok = false;
+            break;
+          }
+          const int atoms_b = min(2, p.n_atoms - nt * 2);
+          mbar_expect_tx(&sm.full[s], kBM * kBK + kBN * kBK + 512 + 512 * atoms_b);
+          tma_load_2d(sm.a[s], &map_a, ks * kBK, mt * kBM, &sm.full[s]);
+          tma_load_2d(sm.b[s], &map_b, ks * kBK, nt * kBN, &sm.full[s]);
+          bulk_load_1d(sm.sfa[s], p.sfa + (int64_t(mt) * p.katoms + ks) * 512, 512, &sm.full[s]);
+          for (int h = 0; h < atoms_b; ++h)
+            bulk_load_1d(sm.sfb[s] + h * 512, p.sfb + (int64_t(nt * 2 + h) * p.katoms + ks) * 512, 512, &sm.full[s]);
+        }
+      }
+      if (!ok) {
+        // Give up, but not with copies on their way into this CTA's shared memory: wait (bounded) for the
+        // newest copy of every stage; they complete without anybody's help.
+        atomicExch(p.status, DTQ_ERR_TIMEOUT);
+        *abort = 1;
+        for (int64_t j = it - 1; j >= 0 && j > it - 1 - kStagesG; --j)
+          mbar_wait(&sm.full[j % kStagesG], unsigned(j / kStagesG) & 1u, nullptr);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -------------------------------------------------------------------------------
+    if (lane == 0) {
+      int64_t it = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+        // the epilogue must have taken the previous tile's accumulator out of tensor memory
+        if (local_tile > 0 && !mbar_wait(&sm.tmem_empty, (local_tile - 1) & 1u, abort)) {
+          ok = false;
+          break;
+        }
+        tmem_fence_after();
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = int(it % kStagesG);
+          if (!mbar_wait(&sm.full[s], unsigned(it / kStagesG) & 1u, abort)) {
+            ok = false;
+            break;
+          }
+          tmem_fence_after();
+          // this stage's scales: shared memory -> tensor memory, ordered before the MMAs below
+          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfaCol),
+                       "l"(scale_desc(smem_addr(sm.sfa[s])))
+                       : "memory");
+          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol),
+                       "l"(scale_desc(smem_addr(sm.sfb[s])))
+                       : "memory");
+          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 4),
+                       "l"(scale_desc(smem_addr(sm.sfb[s] + 512)))
+                       : "memory");
+          const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) {  // four k-blocks of 32 bytes inside the 128-byte swizzle span
+            const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+                :
+                : "r"(tmem), "l"(operand_desc(a_addr + k * 32)), "l"(operand_desc(b_addr + k * 32)), "r"(instr_desc(k)),
+                  "r"(accumulate), "r"((tmem + kSfaCol) | (k << 30)), "r"((tmem + kSfbCol) | (k << 30))
+                : "memory");
+          }
+          umma_commit(&sm.empty[s]);  // the stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(&sm.tmem_full);  // the accumulator is complete once all MMAs so far have finished
+      }
+      if (!ok) {
+        atomicExch(p.status, DTQ_ERR_TIMEOUT);
+        *abort = 1;
+      }
+    }
+  } else {
+    // ---- epilogue: 8 warps; warp w reads lanes 32 (w % 4) .. + 31, column half (w - 2) / 4 -------------------
+    const int quad = warp & 3, half = (warp - 2) >> 2;
+    int local_tile = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
+      const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+      if (!mbar_wait(&sm.tmem_full, local_tile & 1u, abort)) {
+        if (lane == 0) {
+          atomicExch(p.status, DTQ_ERR_TIMEOUT);
+          *abort = 1;
+        }
+        break;
+      }
+      tmem_fence_after();
+      const int64_t row = int64_t(mt) * kBM + quad * 32 + lane;
+      uint32_t packed[4][16];  // this thread's 128 columns of one row as bf16 pairs
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(half * 128 + c * 32);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 16; ++i) packed[c][i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+      }
+      // the accumulator is in registers: hand tensor memory back before storing
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.tmem_empty);
+      if (row < p.M) {
+        uint16_t *dst = p.out + row * p.N + int64_t(nt) * kBN + half * 128;
+        const int64_t col0 = int64_t(nt) * kBN + half * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // 8 columns = 16 bytes per store; N % 8 == 0
+            if (col0 + c * 32 + q * 8 < p.N)
+              *reinterpret_cast<uint4 *>(dst + c * 32 + q * 8) =
+                  make_uint4(packed[c][4 * q], packed[c][4 * q + 1], packed[c][4 * q + 2], packed[c][4 * q + 3]);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: everybody meets, then the warp that allocated tensor memory frees it ----------------------
+  tmem_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort && lane == 0) {
+      // MMAs may still be in flight: a commit that arrives on a barrier nobody else uses, and a bounded wait for it
+      mbar_init(&sm.tmem_full, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      umma_commit(&sm.tmem_full);
+      mbar_wait(&sm.tmem_full, 0u, nullptr);
+    }
+    __syncwarp();
+    tmem_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime (no link against libcuda).
+int encode_tiled_fn(EncodeTiledFn *fn) {
+  static std::atomic<EncodeTiledFn> cached{nullptr};
+  EncodeTiledFn f = cached.load(std::memory_order_acquire);
+  if (!f) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    DTQ_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !sym) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorNotSupported);
+    f = reinterpret_cast<EncodeTiledFn>(sym);
+    cached.store(f, std::memory_order_release);
+  }
+  *fn = f;
+  return DTQ_OK;
+}
+
+// Map of a row-major [rows, k_bytes] byte matrix, boxes of box_rows x 128 bytes, 128-byte swizzle, zero fill.
+int make_operand_map(CUtensorMap *map, const void *base, int64_t rows, int64_t k_bytes, int box_rows) {
+  EncodeTiledFn encode = nullptr;
+  if (int e = encode_tiled_fn(&encode)) return e;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k_bytes), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k_bytes)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DTQ_OK : DTQ_ERR_INVALID_ARGUMENT;
+}
+
+}  // namespace
+}  // namespace dtq
+
+extern "C" size_t dtq_mx_gemm_scale_bytes(int64_t rows, int64_t k) {
+  if (rows <= 0 || k <= 0) return 0;
+  return static_cast<size_t>((rows + 127) / 128) * static_cast<size_t>(((k + 31) / 32 + 3) / 4) * 512;
+}
+
+extern "C" int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
+                               void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
+                               void *stream) {
+  using namespace dtq;
+  if (m < 0 || n < 0 || k < 0) return DTQ_ERR_INVALID_ARGUMENT;
+  if (n % 8 != 0 || k % 32 != 0) return DTQ_ERR_SHAPE;  // 16-byte output vectors; whole MX blocks (also the TMA row pitch)
+  if (m > 0x7FFFFFFF - kBM || n > 0x7FFFFFFF - kBN || k > 0x7FFFFFFF - kBK) return DTQ_ERR_TOO_LARGE;
+  if (!workspace || workspace_bytes < sizeof(Workspace) || !aligned_to(workspace, 256)) return DTQ_ERR_WORKSPACE;
+  if (m == 0 || n == 0) return DTQ_OK;
+  if (!out_bf16 || !aligned_to(out_bf16, 16)) return DTQ_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (k == 0) return cuda_status(cudaMemsetAsync(out_bf16, 0, static_cast<size_t>(m) * n * 2, st));
+  if (!a || !b || !a_scales_blocked || !b_scales_blocked) return DTQ_ERR_INVALID_ARGUMENT;
+  if (!aligned_to(a, 16) || !aligned_to(b, 16) || !aligned_to(a_scales_blocked, 16) || !aligned_to(b_scales_blocked, 16))
+    return DTQ_ERR_INVALID_ARGUMENT;
+  DeviceInfo dev;
+  if (int e = current_device_info(&dev)) return e;
+
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> configured[kMaxDevices];
+  int dev_id = 0;
+  DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
+  if (dev_id < 0 || dev_id >= kMaxDevices) return DTQ_ERR_INVALID_ARGUMENT;
+  const int smem = static_cast<int>(sizeof(GemmSmem)) + 1024;
+  if (!configured[dev_id].load(std::memory_order_acquire)) {  // setting the attribute twice is harmless
+    DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured[dev_id].store(1, std::memory_order_release);
+  }
+
+  CUtensorMap map_a, map_b;
+  if (int e = make_operand_map(&map_a, a, m, k, kBM)) return e;
+  if (int e = make_operand_map(&map_b, b, n, k, kBN)) return e;
+  GemmParams p;
+  p.sfa = static_cast<const uint8_t *>(a_scales_blocked);
+  p.sfb = static_cast<const uint8_t *>(b_scales_blocked);
+  p.out = static_cast<uint16_t *>(out_bf16);
+  p.M = static_cast<int>(m);
+  p.N = static_cast<int>(n);
+  p.K = static_cast<int>(k);
+  p.m_tiles = static_cast<int>(ceil_div64(m, kBM));
+  p.n_tiles = static_cast<int>(ceil_div64(n, kBN));
+  p.k_stages = static_cast<int>(ceil_div64(k, kBK));
+  p.katoms = static_cast<int>(ceil_div64(k / 32, 4));
+  p.n_atoms = static_cast<int>(ceil_div64(n, 128));
+  p.status = &static_cast<Workspace *>(workspace)->status;
+  const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
+  const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+  mx_gemm_kernel<<<grid, kGemmThreads, smem, st>>>(map_a, map_b, p);
+  return cuda_status(cudaGetLastError());
+}

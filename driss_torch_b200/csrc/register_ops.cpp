@@ -15,6 +15,7 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <cstdint>
 #include <mutex>
 #include <tuple>
 #include <unordered_map>
@@ -417,6 +418,43 @@ std::tuple<at::Tensor, at::Tensor> cast_with_amax(const at::Tensor &input, const
   return {out, scale};
 }
 
+// The MX block-scaled GEMM; checks and messages follow the reference's validate() (src/mx_fp8_bf16.cu:168-215).
+at::Tensor mx_fp8_bf16(at::Tensor a, at::Tensor b, at::Tensor a_scale, at::Tensor b_scale) {
+  TORCH_CHECK(a.is_cuda(), "a must be CUDA tensor");
+  TORCH_CHECK(b.is_cuda(), "b must be CUDA tensor");
+  TORCH_CHECK(a_scale.is_cuda(), "a_scale must be CUDA tensor");
+  TORCH_CHECK(b_scale.is_cuda(), "b_scale must be CUDA tensor");
+  TORCH_CHECK(a.dim() == 2, "a must be a matrix");
+  TORCH_CHECK(b.dim() == 2, "b must be a matrix");
+  TORCH_CHECK(a.scalar_type() == at::kFloat8_e4m3fn && b.scalar_type() == at::kFloat8_e4m3fn,
+              "a and b must be float8_e4m3fn, but got ", a.dtype(), " and ", b.dtype());
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(1);
+  TORCH_CHECK(b.size(0) == K, "Incompatible matrix dimensions: a is ", M, "x", K, " but b is ", b.size(0), "x", N);
+  TORCH_CHECK(N % 8 == 0, "N must be a multiple of 16 but got, ", N);
+  TORCH_CHECK(K % 32 == 0, "K must be a multiple of the block size 32, but got ", K);
+  TORCH_CHECK(reinterpret_cast<std::uintptr_t>(a.data_ptr()) % 16 == 0, "Input tensor 'a' must be 16-byte aligned");
+  TORCH_CHECK(reinterpret_cast<std::uintptr_t>(b.data_ptr()) % 16 == 0, "Input tensor 'b' must be 16-byte aligned");
+  const int64_t expected_a = static_cast<int64_t>(dtq_mx_gemm_scale_bytes(M, K));
+  const int64_t expected_b = static_cast<int64_t>(dtq_mx_gemm_scale_bytes(N, K));
+  // the reference checks 128 * ceil(rows / 128) * ceil(K / 32) and its kernel reads whole 4-block atoms; the two
+  // agree whenever K is a multiple of 128, and the blocked casts of this library always produce whole atoms
+  TORCH_CHECK(a_scale.numel() == expected_a || (K % 128 == 0 && a_scale.numel() == 128 * ((M + 127) / 128) * (K / 32)),
+              "Expected a_scale_size to be ", expected_a, " but got ", a_scale.numel());
+  TORCH_CHECK(b_scale.numel() == expected_b || (K % 128 == 0 && b_scale.numel() == 128 * ((N + 127) / 128) * (K / 32)),
+              "Expected b_scale_size to be ", expected_b, " but got ", b_scale.numel());
+  TORCH_CHECK(a_scale.element_size() == 1 && b_scale.element_size() == 1, "scales must be one byte per block (float8_e8m0fnu)");
+  TORCH_CHECK(a_scale.is_contiguous() && b_scale.is_contiguous(), "scale tensors must be contiguous");
+  TORCH_CHECK(a.stride(1) == 1 && a.stride(0) == K, "Input tensor 'a' must be contiguous in the K dimension (row-major)");
+  TORCH_CHECK(b.stride(0) == 1 && b.stride(1) == K, "Input tensor 'b' must be contiguous in the K dimension (column-major)");
+  at::Tensor out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+  c10::cuda::CUDAGuard guard(a.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_mx_fp8_bf16(a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), out.data_ptr(), M, N, K,
+                               workspaces().get(stream), dtq_workspace_bytes(), stream.stream()),
+               "mx_fp8_bf16");
+  return out;
+}
+
 void check_device_status() { workspaces().check_all(); }
 
 }  // namespace
@@ -455,6 +493,9 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("mx_fp8_quantize_dual", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_dual));
   m.def("mx_fp8_quantize_blocked(Tensor input) -> (Tensor, Tensor)");
   m.impl("mx_fp8_quantize_blocked", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_blocked));
+  // the consumer GEMM, the reference's schema verbatim (src/register_ops.cpp:35-36)
+  m.def("mx_fp8_bf16(Tensor a, Tensor b, Tensor a_scale, Tensor b_scale) -> Tensor");
+  m.impl("mx_fp8_bf16", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_bf16));
   m.def("check_device_status() -> ()");
   m.impl("check_device_status", c10::DispatchKey::CompositeExplicitAutograd, TORCH_FN(check_device_status));
 }

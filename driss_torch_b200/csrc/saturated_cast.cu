@@ -66,6 +66,10 @@ __global__ void __launch_bounds__(kThreads)
 saturated_cast_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, const float *__restrict__ scale,
                       int64_t numel) {
   using C = Chunk<IN, OUT>;
+  // launched so that its blocks may become resident under the tail of the kernel before it on the stream
+  // (launch latency and block ramp hidden); nothing is read before that kernel has completed
+  pdl_launch_dependents();
+  pdl_wait();
   const typename C::Scale s = C::load_scale(scale);
   const int64_t nchunks = numel / C::kElems;
   constexpr int64_t kTile = int64_t(kThreads) * UNROLL;
@@ -112,8 +116,8 @@ int launch(const void *in, void *out, const float *scale, int64_t numel, const D
   if (aligned_to(in, 16) && aligned_to(out, 8)) {
     const int64_t tiles = ceil_div64(numel / C::kElems, int64_t(kThreads) * kUnroll);
     const int grid = balanced_grid(tiles, max_grid);
-    saturated_cast_stream<IN, OUT, kUnroll><<<grid, kThreads, 0, st>>>(
-        static_cast<const uint4 *>(in), static_cast<uint8_t *>(out), scale, numel);
+    return cuda_status(launch_after_dependency(saturated_cast_stream<IN, OUT, kUnroll>, dim3(grid), dim3(kThreads), 0, st,
+                                               static_cast<const uint4 *>(in), static_cast<uint8_t *>(out), scale, numel));
   } else {
     const int64_t blocks = ceil_div64(numel, kThreads);
     const int grid = static_cast<int>(blocks < max_grid ? blocks : max_grid);

@@ -315,6 +315,27 @@ size_t dtq_mx_blocked_scale_bytes(int64_t rows, int64_t cols);
 int dtq_mx_fp8_quantize_blocked(const void *in_bf16, void *payload, void *scales_blocked, int64_t rows,
                                 int64_t cols, void *stream);
 
+/*
+ * MX block-scaled GEMM, the consumer of the MX casts above:
+ *   out[m, n] = bf16( sum_k a[m, k] * 2^(sa[m, k/32] - 127) * b[n, k] * 2^(sb[n, k/32] - 127) ),  fp32 accumulation
+ *   a  [m, k] e4m3 bytes, row-major;
+ *   b  [n, k] e4m3 bytes, row-major -- the memory of the reference's column-major [k, n] operand;
+ *   a_scales_blocked / b_scales_blocked: E8M0 bytes in the blocked layout of dtq_mx_fp8_quantize_blocked,
+ *       dtq_mx_gemm_scale_bytes(m, k) and dtq_mx_gemm_scale_bytes(n, k) bytes (bytes that belong to padding
+ *       rows or k-blocks must not be 0xFF; the quantisers here write zeros there);
+ *   out [m, n] bf16, row-major, 16-byte aligned.
+ * n % 8 == 0 and k % 32 == 0; m, n, k need not be multiples of the 128 x 256 x 128 tile (out-of-range
+ * rows and columns are loaded as zeros and not stored).  a, b and the scale arrays 16-byte aligned.
+ * tcgen05 tensor-core kernel with the accumulator in tensor memory, operands staged by TMA; it occupies
+ * each SM exclusively while it runs.  Needs an initialised workspace: a bounded device-side wait that
+ * gives up leaves DTQ_ERR_TIMEOUT in its status word (dtq_workspace_status).
+ * Replaces driss_torch::mx_fp8_bf16: src/mx_fp8_bf16.cu:42-163 (run_gemm), :168-215 (validate), :217-241.
+ */
+size_t dtq_mx_gemm_scale_bytes(int64_t rows, int64_t k);
+int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
+                    void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
+                    void *stream);
+
 #ifdef __cplusplus
 }
 #endif

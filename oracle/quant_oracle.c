@@ -309,6 +309,66 @@ void oracle_mx_quantize(const void *in, int in_dtype, uint8_t *payload, uint8_t 
 }
 
 /* Single-value entry points for exhaustive conversion checks. */
+/* ---- MX block-scaled GEMM (the consumer of the MX casts).
+ * D[m,n] = bf16( sum_k A[m,k] 2^(sa[m,k/32]-127) * B[n,k] 2^(sb[n,k/32]-127) ), the contraction the reference
+ * hands to a CUTLASS block-scaled collective (src/mx_fp8_bf16.cu:42-163: e4m3 operands, ue8m0 scales of 32
+ * elements, fp32 accumulation, bf16 output, alpha 1, beta 0; shapes and scale sizes :168-215).  A is [M,K]
+ * row-major, B is [N,K] row-major (the reference's column-major [K,N] view), both scale arrays in the blocked
+ * layout CUTLASS's Sm1xxBlockScaledConfig gives them (:100-110): 128-row x 4-block atoms of 512 bytes, atoms of
+ * a 128-row band ordered along K, scale (r, c) of an atom at (r % 32) * 16 + (r / 32) * 4 + c.  The tensor core
+ * accumulates in fp32 in an order this restatement does not model: the sum here is exact in double and rounded
+ * once, so equality with the device is expected bit for bit only when every partial sum is exactly
+ * representable in fp32 (small integers times powers of two); otherwise to within bf16 rounding of nearly equal
+ * sums.  Element formats: fmt 0 = e4m3 (one byte per element), fmt 2 = e2m1 (two per byte, lower index in the
+ * low nibble; K counts elements). */
+static double e4m3_to_f64(uint8_t b) {
+  const int sign = b >> 7, be = (b >> 3) & 0xF, man = b & 7;
+  double v;
+  if (be == 0xF && man == 7) return NAN;
+  v = be == 0 ? ldexp((double)man, -9) : ldexp(1.0 + man / 8.0, be - 7);
+  return sign ? -v : v;
+}
+static double e2m1_to_f64(uint8_t nib) {
+  static const double mag[8] = {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0};
+  return (nib & 8) ? -mag[nib & 7] : mag[nib & 7];
+}
+static double e8m0_to_f64(uint8_t b) { return b == 0xFF ? NAN : ldexp(1.0, (int)b - 127); }
+static inline int64_t blocked_scale_offset(int64_t r, int64_t c, int64_t katoms) {
+  return ((r / 128) * katoms + c / 4) * 512 + (r % 32) * 16 + ((r % 128) / 32) * 4 + c % 4;
+}
+
+void oracle_mx_gemm_bf16(const uint8_t *a, const uint8_t *b, const uint8_t *sa_blocked, const uint8_t *sb_blocked,
+                         uint16_t *out, int64_t M, int64_t N, int64_t K, int fmt) {
+  const int64_t kblocks = (K + 31) / 32, katoms = (kblocks + 3) / 4;
+  const int64_t row_bytes = fmt == 2 ? K / 2 : K;
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    for (int64_t n = 0; n < N; ++n) {
+      double acc = 0.0;
+      for (int64_t kb = 0; kb < kblocks; ++kb) {
+        const double s = e8m0_to_f64(sa_blocked[blocked_scale_offset(m, kb, katoms)]) *
+                         e8m0_to_f64(sb_blocked[blocked_scale_offset(n, kb, katoms)]);
+        double part = 0.0;
+        const int64_t k1 = (kb + 1) * 32 < K ? (kb + 1) * 32 : K;
+        for (int64_t k = kb * 32; k < k1; ++k) {
+          double x, y;
+          if (fmt == 2) {
+            const uint8_t xa = a[m * row_bytes + k / 2], xb = b[n * row_bytes + k / 2];
+            x = e2m1_to_f64((k & 1) ? xa >> 4 : xa & 0xF);
+            y = e2m1_to_f64((k & 1) ? xb >> 4 : xb & 0xF);
+          } else {
+            x = e4m3_to_f64(a[m * row_bytes + k]);
+            y = e4m3_to_f64(b[n * row_bytes + k]);
+          }
+          part += x * y;
+        }
+        acc += part * s;
+      }
+      out[m * N + n] = f64_to_bf16_rne(acc);
+    }
+  }
+}
+
 uint16_t oracle_f32_to_bf16(float f) { return f64_to_bf16_rne((double)f); }
 uint16_t oracle_bf16_mul(uint16_t a, uint16_t b) {
   return f64_to_bf16_rne((double)bf16_to_f32(a) * (double)bf16_to_f32(b));

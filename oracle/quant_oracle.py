@@ -69,6 +69,8 @@ def lib() -> C.CDLL:
         L.oracle_mx_fp8_quantize.restype = None
         L.oracle_mx_quantize.argtypes = [vp, i32, vp, vp, i64, i32]
         L.oracle_mx_quantize.restype = None
+        L.oracle_mx_gemm_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32]
+        L.oracle_mx_gemm_bf16.restype = None
         L.oracle_f32_to_e2m1.argtypes = [f32]
         L.oracle_f32_to_e2m1.restype = C.c_uint8
         L.oracle_f16_to_f32.argtypes = [C.c_uint16]
@@ -195,6 +197,25 @@ def mx_quantize(x: torch.Tensor, elem):
     scales = torch.empty(x.numel() // 32, dtype=torch.uint8)
     lib().oracle_mx_quantize(x.data_ptr(), MX_IN[x.dtype], payload.data_ptr(), scales.data_ptr(), x.numel() // 32, fmt)
     return (payload if fmt == 2 else payload.view(elem)), scales.view(torch.float8_e8m0fnu)
+
+
+def mx_gemm_bf16(a: torch.Tensor, b_nk: torch.Tensor, a_scale_blocked: torch.Tensor, b_scale_blocked: torch.Tensor,
+                 fp4: bool = False) -> torch.Tensor:
+    """The MX block-scaled GEMM: ``a`` [M, K] e4m3 (or uint8 [M, K/2] packed e2m1 with ``fp4``), ``b_nk`` [N, K]
+    (the reference's operand ``b`` is its transpose view), scales as blocked e8m0 bytes; returns bf16 [M, N]."""
+    a8 = a.contiguous().view(torch.uint8)
+    b8 = b_nk.contiguous().view(torch.uint8)
+    m, n = a8.shape[0], b8.shape[0]
+    k = a8.shape[1] * (2 if fp4 else 1)
+    assert b8.shape[1] == a8.shape[1]
+    sa = a_scale_blocked.contiguous().view(torch.uint8)
+    sb = b_scale_blocked.contiguous().view(torch.uint8)
+    katoms = ((k + 31) // 32 + 3) // 4
+    assert sa.numel() == ((m + 127) // 128) * katoms * 512 and sb.numel() == ((n + 127) // 128) * katoms * 512
+    out = torch.empty(m, n, dtype=torch.int16)
+    lib().oracle_mx_gemm_bf16(a8.data_ptr(), b8.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(), m, n, k,
+                              2 if fp4 else 0)
+    return out.view(torch.bfloat16)
 
 
 # ---- conversion tables for the exhaustive pins -------------------------------------------------
