@@ -159,6 +159,70 @@ def time_rotating(fn, nsets: int, iters: int, warmup: int = 3):
 
 # ---- the single-GPU per-op table (cfg1..cfg4) ----------------------------------------------------------------
 
+def measured_tensor_peak():
+    """The pool's measured dense bf16 tensor throughput (cuBLAS, burst), TFLOP/s; None if the file is absent."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(p.read_text())["bf16_tflops"])
+    except Exception:
+        return None
+
+
+def gemm_table(dev, iters: int, warmup: int = 3):
+    """The MX block-scaled GEMM that consumes the MX casts (the reference's mx_fp8_bf16), one line per shape:
+    operands from the blocked MX cast of N(0,1) data, device time per launch, TFLOP/s."""
+    import driss_torch_b200 as dtq
+    from driss_torch_b200 import _cabi
+
+    rows = []
+    bf16_peak = measured_tensor_peak()
+    ref = None
+    ref_lib = ROOT / "oracle" / "_ref" / "libdriss_torch_ref_gemm.so"  # the reference's CUTLASS GEMM, if it was built
+    if ref_lib.exists():
+        try:
+            torch.ops.load_library(str(ref_lib))
+            ref = torch.ops.DrissTorchRefGemm
+        except Exception:
+            ref = None
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1100)
+    ws = _cabi.workspace(dev)
+    for (m, n, k) in [(8192, 8192, 8192), (4096, 4096, 4096), (16384, 8192, 4096), (1024, 1024, 1024)]:
+        a = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
+        b = torch.randn(n, k, generator=gen, device=dev).to(torch.bfloat16)
+        pa, sa = dtq.mx_fp8_quantize_blocked(a)
+        pb, sb = dtq.mx_fp8_quantize_blocked(b)
+        del a, b
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        ms, single, single_min = time_rotating(lambda i: _cabi.mx_fp8_bf16(pa, pb, sa, sb, out=out, ws=ws), 1, iters, warmup)
+        flops = 2.0 * m * n * k
+        d = {"config": "gemm", "op": "mx_fp8_bf16", "shape": [m, n, k], "us": round(ms * 1e3, 2),
+             "us_single_launch": round(single * 1e3, 2), "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 1),
+             "note": "e4m3 x e4m3 with E8M0 block scales, fp32 accumulation in tensor memory, bf16 out; back-to-back launches "
+                     "on one buffer set of %d MB (operands + output): %s" % (
+                         (m * k + n * k + 2 * m * n) >> 20,
+                         "larger than L2, no flush" if m * k + n * k + 2 * m * n > 2 * 126e6 else "NOT larger than 2x L2: an "
+                         "L2-warm figure, as behind the casts that produce the operands")}
+        if bf16_peak:
+            d["x_measured_bf16_peak"] = round(flops / (ms * 1e-3) / 1e12 / bf16_peak, 3)
+            d["peak_note"] = (f"against the pool's measured cuBLAS bf16 throughput ({bf16_peak} TFLOP/s, MEASURED_PEAKS.json); "
+                              "no fp8 peak is measured on this pool: nominal dense fp8 is 2x nominal bf16 (4.5 vs 2.25 PFLOP/s)")
+        d["device_status"] = _cabi.workspace_status(ws)
+        if ref is not None:
+            pbt = pb.t()
+            want = ref.mx_fp8_bf16(pa, pbt, sa, sb)
+            d["equals_reference_kernel_bitwise"] = bool(torch.equal(want.view(torch.int16), out.view(torch.int16)))
+            rms, _, _ = time_rotating(lambda i: ref.mx_fp8_bf16(pa, pbt, sa, sb), 1, iters, warmup)
+            d["reference_kernel_us"] = round(rms * 1e3, 2)
+            d["reference_kernel_TFLOPs"] = round(flops / (rms * 1e-3) / 1e12, 1)
+            d["speedup_vs_reference_kernel"] = round(rms / ms, 2)
+            del want
+        rows.append(d)
+        del pa, pb, sa, sb, out
+    torch.cuda.empty_cache()
+    return rows
+
+
 def per_op_table(dev, peak, iters: int, warmup: int = 3):
     import driss_torch_b200  # noqa: F401  (registers the ops; loads the CUDA libraries)
     from driss_torch_b200 import _cabi, workloads
@@ -513,6 +577,7 @@ def main():
                     help="shared-read: the MX cast also delivers the amax (and exchanges it), then the cast: two reads "
                          "of the input; separate: amax, cast and MX cast as independent ops: three reads")
     ap.add_argument("--ops-table-only", action="store_true", help="only the cfg1-cfg4 per-op table (profiling captures)")
+    ap.add_argument("--gemm-only", action="store_true", help="only the MX GEMM lines (profiling captures)")
     ap.add_argument("--op-iters", type=int, default=0, help="timed launches per op in the per-op table (default max(20, steps))")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -543,6 +608,10 @@ def main():
     from driss_torch_b200.host_pipeline import HostQuantizer
 
     peak, peak_kind = measured_peak()
+    if args.gemm_only:
+        iters = args.op_iters or max(20, args.steps)
+        print(json.dumps({"ops": gemm_table(dev, iters=iters, warmup=min(3, iters))}), flush=True)
+        return
     if args.ops_table_only:
         iters = args.op_iters or max(20, args.steps)
         print(json.dumps({"ops": per_op_table(dev, peak, iters=iters, warmup=min(3, iters))}), flush=True)
@@ -830,6 +899,7 @@ def main():
         del x
         torch.cuda.empty_cache()
         ops = per_op_table(dev, peak, iters=args.op_iters or max(20, args.steps))
+        ops += gemm_table(dev, iters=args.op_iters or max(20, args.steps))
 
     if rank == 0:
         out = {

@@ -50,6 +50,7 @@ SIGNATURES = {
     "dtq_mx_blocked_scale_bytes": ([_i64, _i64], _sz),
     "dtq_mx_gemm_scale_bytes": ([_i64, _i64], _sz),
     "dtq_mx_fp8_bf16": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp], _i32),
+    "dtq_mx_fp8_bf16_kernel": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _sz, _vp], _i32),
     "dtq_mx_fp8_quantize_blocked": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
 }
 
@@ -356,14 +357,18 @@ def dynamic_scaled_quant_dual(x, out_dtype, out=None, out_t=None, amax_out=None,
     return out, out_t
 
 
+GEMM_KERNELS = {"auto": 0, "pair": 1, "wide": 2, "narrow": 3}
+
+
 @_on_device_of_first_tensor
-def mx_fp8_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=None, ws=None):
+def mx_fp8_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=None, ws=None, kernel="auto"):
     """MX block-scaled GEMM: ``a`` [M, K] e4m3, ``b_nk`` [N, K] e4m3 (the memory of the reference's column-major
-    [K, N] operand), blocked E8M0 scales -> bf16 [M, N]."""
+    [K, N] operand), blocked E8M0 scales -> bf16 [M, N].  ``kernel``: "auto", or one of "pair", "wide", "narrow"."""
     m, k = a.shape
     n = b_nk.shape[0]
     out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device) if out is None else out
     ws = workspace(a.device) if ws is None else ws
-    check(load().dtq_mx_fp8_bf16(a.data_ptr(), b_nk.data_ptr(), a_scale_blocked.data_ptr(), b_scale_blocked.data_ptr(),
-                                 out.data_ptr(), m, n, k, ws.data_ptr(), ws.numel(), _stream()), "dtq_mx_fp8_bf16")
+    check(load().dtq_mx_fp8_bf16_kernel(a.data_ptr(), b_nk.data_ptr(), a_scale_blocked.data_ptr(),
+                                        b_scale_blocked.data_ptr(), out.data_ptr(), m, n, k, GEMM_KERNELS[kernel],
+                                        ws.data_ptr(), ws.numel(), _stream()), "dtq_mx_fp8_bf16")
     return out

@@ -35,26 +35,38 @@ namespace dtq {
 namespace {
 
 constexpr int kBM = 128;        // tile rows (M)
-constexpr int kBN = 256;        // tile columns (N)
 constexpr int kBK = 128;        // K bytes per stage: one 128-byte swizzle span = 4 MX blocks of 32
-constexpr int kStagesG = 4;
 constexpr int kGemmThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr int kEpilogueWarps = 8;
-constexpr int kAccumCols = kBN;            // fp32 accumulator columns in tensor memory
-constexpr int kSfaCol = kAccumCols;        // 4 columns: scales of 128 rows x 4 k-blocks
-constexpr int kSfbCol = kAccumCols + 8;    // 8 columns: scales of 256 rows x 4 k-blocks
-constexpr int kTmemCols = 512;             // allocation (power of two)
+constexpr int kSfaCol = 256;               // 4 tensor-memory columns: scales of 128 rows x 4 k-blocks
+constexpr int kSfbCol = 256 + 8;           // up to 8 columns: scales of up to 256 rows x 4 k-blocks
+constexpr int kTmemCols = 512;             // allocation (power of two); columns 0..255 hold the accumulator(s)
+
+// Two tile shapes.  Wide: 128 x 256, one accumulator of 256 columns, 4 stages -- least operand traffic per
+// output (every byte of B serves 128 rows, every byte of A 256 columns), the shape for large problems.
+// Narrow: 128 x 128, two accumulators of 128 columns (the epilogue of one tile runs under the MMAs of the
+// next), 6 stages -- twice the tiles, for problems whose wide tiles would leave a large part of the last wave
+// of SMs idle.
+template <int BN_, int STAGES_, int ACC_>
+struct GemmShape {
+  static constexpr int BN = BN_, STAGES = STAGES_, ACC = ACC_;
+  static_assert(BN == 128 || BN == 256, "N tile");
+  static_assert(ACC * BN <= 256, "accumulators live in tensor-memory columns 0..255");
+};
+using WideShape = GemmShape<256, 4, 1>;
+using NarrowShape = GemmShape<128, 6, 2>;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds of wall time
 
+template <typename SH>
 struct __align__(1024) GemmSmem {
-  uint8_t a[kStagesG][kBM * kBK];      // 16 KB per stage, 1024-byte aligned (swizzle atom = 8 rows x 128 B)
-  uint8_t b[kStagesG][kBN * kBK];      // 32 KB per stage
-  uint8_t sfa[kStagesG][512];          // one blocked atom: 128 rows x 4 k-blocks
-  uint8_t sfb[kStagesG][2 * 512];      // two atoms: 256 rows x 4 k-blocks
-  uint64_t full[kStagesG];
-  uint64_t empty[kStagesG];
-  uint64_t tmem_full;
-  uint64_t tmem_empty;
+  uint8_t a[SH::STAGES][kBM * kBK];        // 16 KB per stage, 1024-byte aligned (swizzle atom = 8 rows x 128 B)
+  uint8_t b[SH::STAGES][SH::BN * kBK];     // 16 or 32 KB per stage
+  uint8_t sfa[SH::STAGES][512];            // one blocked atom: 128 rows x 4 k-blocks
+  uint8_t sfb[SH::STAGES][SH::BN / 128 * 512];  // one atom per 128 tile columns
+  uint64_t full[SH::STAGES];
+  uint64_t empty[SH::STAGES];
+  uint64_t tmem_full[SH::ACC];
+  uint64_t tmem_empty[SH::ACC];
   uint32_t tmem_base;
   int abort;
 };
@@ -129,9 +141,9 @@ __device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
   return uint64_t((saddr >> 4) & 0x3FFFu) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
 }
 // Instruction descriptor of tcgen05.mma kind::mxf8f6f4.block_scale: e4m3 x e4m3, both K-major, E8M0 scales,
-// M = 128, N = 256; `k` (0..3) is the byte of the 4-byte scale column that this k-block uses, for A and B.
-__device__ __forceinline__ uint32_t instr_desc(uint32_t k) {
-  return (k << 4) | (uint32_t(kBN >> 3) << 17) | (1u << 23) | (uint32_t(kBM >> 4) << 24) | (k << 29);
+// M = 128, N = `bn`; `k` (0..3) is the byte of the 4-byte scale column that this k-block uses, for A and B.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t k, uint32_t bn) {
+  return (k << 4) | ((bn >> 3) << 17) | (1u << 23) | (uint32_t(kBM >> 4) << 24) | (k << 29);
 }
 
 __device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -148,6 +160,18 @@ __device__ __forceinline__ uint32_t pack_bf16(uint32_t lo, uint32_t hi) {
   return r;
 }
 
+// Tile order: consecutive tile numbers (the tiles that the CTAs of one wave work on together) fill bands of
+// kGroupM tile rows, n-tile by n-tile, so that a wave of 148 tiles touches about 16 x 9 tiles' worth of A
+// and B (34 MB at K = 8192) instead of every row of A: what is re-read from L2 mostly stays there.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int *mt, int *nt) {
+  const int per_group = kGroupM * n_tiles;
+  const int g = tile / per_group, idx = tile - g * per_group;
+  const int rows = min(kGroupM, m_tiles - g * kGroupM);
+  *mt = g * kGroupM + idx % rows;
+  *nt = idx / rows;
+}
+
 struct GemmParams {
   const uint8_t *sfa;  // blocked scales of A: atoms [ceil(M/128)][katoms] of 512 bytes
   const uint8_t *sfb;  // blocked scales of B: atoms [ceil(N/128)][katoms]
@@ -157,10 +181,12 @@ struct GemmParams {
   int *status;
 };
 
+template <typename SH>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  constexpr int kBN = SH::BN, kStagesG = SH::STAGES, kAcc = SH::ACC, kAtomsB = SH::BN / 128;
   extern __shared__ unsigned char smem_raw[];
-  GemmSmem &sm = *reinterpret_cast<GemmSmem *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
+  GemmSmem<SH> &sm = *reinterpret_cast<GemmSmem<SH> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *abort = &sm.abort;
 
@@ -169,12 +195,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
     }
-    mbar_init(&sm.tmem_full, 1);
-    mbar_init(&sm.tmem_empty, kEpilogueWarps);
+    for (int i = 0; i < kAcc; ++i) {
+      mbar_init(&sm.tmem_full[i], 1);
+      mbar_init(&sm.tmem_empty[i], kEpilogueWarps);
+    }
     sm.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // scale staging starts as zeros: an atom that does not exist (N not a multiple of 256) is never copied
+  // scale staging starts as zeros: an atom that does not exist (N not a multiple of the tile) is never copied
   for (int i = threadIdx.x; i < int(sizeof(sm.sfb) / 4); i += kGemmThreads) reinterpret_cast<uint32_t *>(sm.sfb)[i] = 0;
   if (warp == 1) {  // the MMA warp owns tensor memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sm.tmem_base)),
@@ -195,7 +223,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int64_t it = 0;  // stage uses so far
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;  // consecutive CTAs share a B panel
+        int mt, nt;
+        tile_coords(tile, p.m_tiles, p.n_tiles, &mt, &nt);
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           const int s = int(it % kStagesG);
           const unsigned round = unsigned(it / kStagesG);
@@ -203,13 +232,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             ok = false;
             break;
           }
-          const int atoms_b = min(2, p.n_atoms - nt * 2);
+          const int atoms_b = min(kAtomsB, p.n_atoms - nt * kAtomsB);
           mbar_expect_tx(&sm.full[s], kBM * kBK + kBN * kBK + 512 + 512 * atoms_b);
           tma_load_2d(sm.a[s], &map_a, ks * kBK, mt * kBM, &sm.full[s]);
           tma_load_2d(sm.b[s], &map_b, ks * kBK, nt * kBN, &sm.full[s]);
           bulk_load_1d(sm.sfa[s], p.sfa + (int64_t(mt) * p.katoms + ks) * 512, 512, &sm.full[s]);
           for (int h = 0; h < atoms_b; ++h)
-            bulk_load_1d(sm.sfb[s] + h * 512, p.sfb + (int64_t(nt * 2 + h) * p.katoms + ks) * 512, 512, &sm.full[s]);
+            bulk_load_1d(sm.sfb[s] + h * 512, p.sfb + (int64_t(nt * kAtomsB + h) * p.katoms + ks) * 512, 512, &sm.full[s]);
         }
       }
       if (!ok) {
@@ -228,12 +257,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int local_tile = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
-        // the epilogue must have taken the previous tile's accumulator out of tensor memory
-        if (local_tile > 0 && !mbar_wait(&sm.tmem_empty, (local_tile - 1) & 1u, abort)) {
+        // the epilogue must have taken this accumulator's previous tile out of tensor memory
+        const int acc = local_tile % kAcc, use = local_tile / kAcc;
+        if (use > 0 && !mbar_wait(&sm.tmem_empty[acc], (use - 1) & 1u, abort)) {
           ok = false;
           break;
         }
         tmem_fence_after();
+        const uint32_t d_tmem = tmem + uint32_t(acc * kBN);
         for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
           const int s = int(it % kStagesG);
           if (!mbar_wait(&sm.full[s], unsigned(it / kStagesG) & 1u, abort)) {
@@ -248,9 +279,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol),
                        "l"(scale_desc(smem_addr(sm.sfb[s])))
                        : "memory");
-          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 4),
-                       "l"(scale_desc(smem_addr(sm.sfb[s] + 512)))
-                       : "memory");
+          if constexpr (kAtomsB == 2)
+            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 4),
+                         "l"(scale_desc(smem_addr(sm.sfb[s] + 512)))
+                         : "memory");
           const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {  // four k-blocks of 32 bytes inside the 128-byte swizzle span
@@ -259,13 +291,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                 "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
                 :
-                : "r"(tmem), "l"(operand_desc(a_addr + k * 32)), "l"(operand_desc(b_addr + k * 32)), "r"(instr_desc(k)),
+                : "r"(d_tmem), "l"(operand_desc(a_addr + k * 32)), "l"(operand_desc(b_addr + k * 32)), "r"(instr_desc(k, kBN)),
                   "r"(accumulate), "r"((tmem + kSfaCol) | (k << 30)), "r"((tmem + kSfbCol) | (k << 30))
                 : "memory");
           }
           umma_commit(&sm.empty[s]);  // the stage is free once these MMAs have read it
         }
-        if (ok) umma_commit(&sm.tmem_full);  // the accumulator is complete once all MMAs so far have finished
+        if (ok) umma_commit(&sm.tmem_full[acc]);  // the accumulator is complete once all MMAs so far have finished
       }
       if (!ok) {
         atomicExch(p.status, DTQ_ERR_TIMEOUT);
@@ -275,10 +307,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else {
     // ---- epilogue: 8 warps; warp w reads lanes 32 (w % 4) .. + 31, column half (w - 2) / 4 -------------------
     const int quad = warp & 3, half = (warp - 2) >> 2;
+    constexpr int kHalfCols = kBN / 2, kChunks = kHalfCols / 32;  // each warp takes half the tile's columns, 32 at a time
     int local_tile = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
-      const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
-      if (!mbar_wait(&sm.tmem_full, local_tile & 1u, abort)) {
+      int mt, nt;
+      tile_coords(tile, p.m_tiles, p.n_tiles, &mt, &nt);
+      const int acc = local_tile % kAcc, use = local_tile / kAcc;
+      if (!mbar_wait(&sm.tmem_full[acc], use & 1u, abort)) {
         if (lane == 0) {
           atomicExch(p.status, DTQ_ERR_TIMEOUT);
           *abort = 1;
@@ -287,7 +322,287 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       tmem_fence_after();
       const int64_t row = int64_t(mt) * kBM + quad * 32 + lane;
-      uint32_t packed[4][16];  // this thread's 128 columns of one row as bf16 pairs
+      uint32_t packed[kChunks][16];  // this thread's columns of one row as bf16 pairs
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * kBN + half * kHalfCols + c * 32);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < 16; ++i) packed[c][i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+      }
+      // the accumulator is in registers: hand tensor memory back before storing
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.tmem_empty[acc]);
+      if (row < p.M) {
+        uint16_t *dst = p.out + row * p.N + int64_t(nt) * kBN + half * kHalfCols;
+        const int64_t col0 = int64_t(nt) * kBN + half * kHalfCols;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // 8 columns = 16 bytes per store; N % 8 == 0
+            if (col0 + c * 32 + q * 8 < p.N)
+              stg_stream(dst + c * 32 + q * 8,  // streaming store: the output must not push the operands out of L2
+                         make_uint4(packed[c][4 * q], packed[c][4 * q + 1], packed[c][4 * q + 2], packed[c][4 * q + 3]));
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: everybody meets, then the warp that allocated tensor memory frees it ----------------------
+  tmem_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort && lane == 0) {
+      // MMAs may still be in flight: a commit that arrives on a barrier nobody else uses, and a bounded wait for it
+      mbar_init(&sm.tmem_full[0], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      umma_commit(&sm.tmem_full[0]);
+      mbar_wait(&sm.tmem_full[0], 0u, nullptr);
+    }
+    __syncwarp();
+    tmem_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- two SMs on one tile ----------------------------------------------------------------------------------
+// The kernel above is bound by what one SM can pull out of L2 (about 64 bytes per clock): a 128 x 256 tile
+// needs 48 KB of operands per 128 of K.  Here two CTAs of a cluster (an SM pair) share a 256 x 256 tile:
+// tcgen05.mma.cta_group::2 multiplies M = 256 (each CTA supplies 128 rows of A and receives their 128 x 256
+// accumulator in its own tensor memory) by N = 256 (each CTA supplies 128 of the 256 rows of B), so every CTA
+// loads 16 + 16 KB per stage instead of 16 + 32: a third less traffic per flop, and room for 6 stages.
+//   * both CTAs' producers load their own halves (TMA, .cta_group::2, no multicast) and signal the LEADER
+//     CTA's `full` barrier (the even CTA of the pair); the leader alone expects the bytes of both;
+//   * the scale atoms come in through a 3-D tensor map over the blocked scale array ([atom row][atom column]
+//     [512 bytes]), so that a missing atom is simply filled with zeros; every CTA needs its own A atom and
+//     both B atoms (its accumulator spans all 256 columns);
+//   * the leader's MMA thread copies the scales (tcgen05.cp.cta_group::2: each CTA's shared memory into that
+//     CTA's tensor memory), issues the MMAs, and commits twice per barrier, once for each CTA's copy of it;
+//   * the peer's epilogue warps arrive on the leader's `tmem_empty` barrier through the cluster address space.
+// Every wait is bounded as above; an abort is forwarded to the other CTA, and both always meet at the cluster
+// barrier before tensor memory is freed.
+constexpr int kPairStages = 6;
+constexpr int kPairBN = 256;  // tile columns; each CTA holds kPairBN / 2 rows of B
+
+struct __align__(1024) PairSmem {
+  uint8_t a[kPairStages][kBM * kBK];             // this CTA's 128 rows of A
+  uint8_t b[kPairStages][kPairBN / 2 * kBK];     // this CTA's 128 of the tile's 256 rows of B
+  uint8_t sfa[kPairStages][512];                 // scales of this CTA's 128 rows of A
+  uint8_t sfb[kPairStages][2 * 512];             // scales of all 256 rows of B
+  uint64_t full[kPairStages];                    // used in the leader CTA only
+  uint64_t empty[kPairStages];
+  uint64_t tmem_full;
+  uint64_t tmem_empty;                           // used in the leader CTA only
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address, in the cluster's shared address space, of `local` (an address of this CTA's shared memory) in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// TMA loads of the pair kernel: destination in this CTA, completion counted on a barrier given by its cluster address.
+__device__ __forceinline__ void tma_pair_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_addr(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_pair_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_addr(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+// Instruction descriptor as above with M = 256 (two CTAs x 128 rows).
+__device__ __forceinline__ uint32_t instr_desc_pair(uint32_t k) {
+  return (k << 4) | (uint32_t(kPairBN >> 3) << 17) | (1u << 23) | (uint32_t(256 >> 4) << 24) | (k << 29);
+}
+
+struct PairParams {
+  uint16_t *out;  // bf16 [M, N]
+  int M, N;
+  int m_pairs, n_tiles, k_stages;  // 256-row tile rows, 256-column tile columns, 128-byte K stages
+  int *status;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, PairParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  PairSmem &sm = *reinterpret_cast<PairSmem *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool leader = rank == 0;
+  const uint32_t peer = rank ^ 1u;
+  volatile int *abort = &sm.abort;
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int total_tiles = p.m_pairs * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&sm.full[s], 1);   // the leader's producer arrives once, expecting both CTAs' bytes
+      mbar_init(&sm.empty[s], 1);  // one commit of the leader's MMA thread per CTA
+    }
+    mbar_init(&sm.tmem_full, 1);
+    mbar_init(&sm.tmem_empty, 2 * kEpilogueWarps);  // the epilogue warps of both CTAs
+    sm.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // one warp of each CTA, together: 512 columns in both CTAs' tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tmem_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anybody signals them
+  tmem_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  bool failed = false;  // meaningful in the role threads
+
+  if (warp == 0) {
+    // ---- producer (one lane in each CTA) -----------------------------------------------------------------
+    if (lane == 0) {
+      int64_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
+        int mp, nt;
+        tile_coords(tile, p.m_pairs, p.n_tiles, &mp, &nt);
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = int(it % kPairStages);
+          const unsigned round = unsigned(it / kPairStages);
+          if (*abort || (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1u, abort))) {
+            ok = false;
+            break;
+          }
+          const uint32_t bar = map_to_cta(smem_addr(&sm.full[s]), 0);  // the leader's barrier
+          if (leader) mbar_expect_tx(&sm.full[s], 2 * (kBM * kBK + kPairBN / 2 * kBK + 512 + 2 * 512));
+          tma_pair_load_2d(sm.a[s], &map_a, ks * kBK, mp * 256 + int(rank) * kBM, bar);
+          tma_pair_load_2d(sm.b[s], &map_b, ks * kBK, nt * kPairBN + int(rank) * (kPairBN / 2), bar);
+          tma_pair_load_3d(sm.sfa[s], &map_sfa, 0, ks, mp * 2 + int(rank), bar);
+          tma_pair_load_3d(sm.sfb[s], &map_sfb, 0, ks, nt * 2, bar);
+        }
+      }
+      if (!ok) {
+        atomicExch(p.status, DTQ_ERR_TIMEOUT);
+        failed = true;
+        *abort = 1;
+        st_cluster_u32(map_to_cta(smem_addr(&sm.abort), peer), 1u);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the leader's lane 0 drives both SMs' tensor cores ---------------------------------------
+    if (lane == 0 && leader) {
+      int64_t it = 0;
+      int local_tile = 0;
+      bool ok = true;
+      const uint32_t peer_full = map_to_cta(smem_addr(&sm.tmem_full), 1);
+      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++local_tile) {
+        if (local_tile > 0 && !mbar_wait(&sm.tmem_empty, (local_tile - 1) & 1u, abort)) {
+          ok = false;
+          break;
+        }
+        tmem_fence_after();
+        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
+          const int s = int(it % kPairStages);
+          if (!mbar_wait(&sm.full[s], unsigned(it / kPairStages) & 1u, abort)) {
+            ok = false;
+            break;
+          }
+          tmem_fence_after();
+          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfaCol),
+                       "l"(scale_desc(smem_addr(sm.sfa[s])))
+                       : "memory");
+          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol),
+                       "l"(scale_desc(smem_addr(sm.sfb[s])))
+                       : "memory");
+          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 4),
+                       "l"(scale_desc(smem_addr(sm.sfb[s] + 512)))
+                       : "memory");
+          const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) {
+            const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+                :
+                : "r"(tmem), "l"(operand_desc(a_addr + k * 32)), "l"(operand_desc(b_addr + k * 32)), "r"(instr_desc_pair(k)),
+                  "r"(accumulate), "r"((tmem + kSfaCol) | (k << 30)), "r"((tmem + kSfbCol) | (k << 30))
+                : "memory");
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          umma_commit_pair(smem_addr(&sm.empty[s]));
+          umma_commit_pair(map_to_cta(smem_addr(&sm.empty[s]), 1));
+        }
+        if (ok) {  // both CTAs' halves of the accumulator are complete once all MMAs so far have finished
+          umma_commit_pair(smem_addr(&sm.tmem_full));
+          umma_commit_pair(peer_full);
+        }
+      }
+      if (!ok) {
+        atomicExch(p.status, DTQ_ERR_TIMEOUT);
+        failed = true;
+        *abort = 1;
+        st_cluster_u32(map_to_cta(smem_addr(&sm.abort), peer), 1u);
+      }
+    }
+  } else {
+    // ---- epilogue: this CTA's 128 rows of the tile, 8 warps as in the single-CTA kernel --------------------
+    const int quad = warp & 3, half = (warp - 2) >> 2;
+    const uint32_t leader_empty = map_to_cta(smem_addr(&sm.tmem_empty), 0);
+    int local_tile = 0;
+    for (int tile = cluster_id; tile < total_tiles; tile += n_clusters, ++local_tile) {
+      int mp, nt;
+      tile_coords(tile, p.m_pairs, p.n_tiles, &mp, &nt);
+      if (!mbar_wait(&sm.tmem_full, local_tile & 1u, abort)) {
+        if (lane == 0) {
+          atomicExch(p.status, DTQ_ERR_TIMEOUT);
+          failed = true;
+          *abort = 1;
+          st_cluster_u32(map_to_cta(smem_addr(&sm.abort), peer), 1u);
+        }
+        break;
+      }
+      tmem_fence_after();
+      const int64_t row = int64_t(mp) * 256 + int64_t(rank) * kBM + quad * 32 + lane;
+      uint32_t packed[4][16];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
@@ -305,40 +620,39 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 16; ++i) packed[c][i] = pack_bf16(v[2 * i], v[2 * i + 1]);
       }
-      // the accumulator is in registers: hand tensor memory back before storing
       tmem_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.tmem_empty);
+      if (lane == 0) mbar_arrive_cluster(leader_empty);
       if (row < p.M) {
-        uint16_t *dst = p.out + row * p.N + int64_t(nt) * kBN + half * 128;
-        const int64_t col0 = int64_t(nt) * kBN + half * 128;
+        uint16_t *dst = p.out + row * p.N + int64_t(nt) * kPairBN + half * 128;
+        const int64_t col0 = int64_t(nt) * kPairBN + half * 128;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {  // 8 columns = 16 bytes per store; N % 8 == 0
+          for (int q = 0; q < 4; ++q) {
             if (col0 + c * 32 + q * 8 < p.N)
-              *reinterpret_cast<uint4 *>(dst + c * 32 + q * 8) =
-                  make_uint4(packed[c][4 * q], packed[c][4 * q + 1], packed[c][4 * q + 2], packed[c][4 * q + 3]);
+              stg_stream(dst + c * 32 + q * 8,
+                         make_uint4(packed[c][4 * q], packed[c][4 * q + 1], packed[c][4 * q + 2], packed[c][4 * q + 3]));
           }
         }
       }
     }
   }
 
-  // ---- teardown: everybody meets, then the warp that allocated tensor memory frees it ----------------------
+  // ---- teardown ---------------------------------------------------------------------------------------------
+  (void)failed;  // whoever gave up has already raised both CTAs' abort flags
   tmem_fence_before();
   __syncthreads();
+  if (*abort) {
+    // Copies and MMAs may still be in flight into or out of this CTA's memories.  Loads complete by themselves
+    // within microseconds and the leader's MMAs within a tile's time; neither CTA leaves before the other
+    // (cluster barrier below), and a short sleep here covers what was issued last.
+    __nanosleep(200000);
+  }
+  cluster_sync_all();  // nobody's shared or tensor memory goes away while the other CTA may still touch it
   if (warp == 1) {
-    if (*abort && lane == 0) {
-      // MMAs may still be in flight: a commit that arrives on a barrier nobody else uses, and a bounded wait for it
-      mbar_init(&sm.tmem_full, 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      umma_commit(&sm.tmem_full);
-      mbar_wait(&sm.tmem_full, 0u, nullptr);
-    }
-    __syncwarp();
     tmem_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -378,6 +692,114 @@ int make_operand_map(CUtensorMap *map, const void *base, int64_t rows, int64_t k
   return r == CUDA_SUCCESS ? DTQ_OK : DTQ_ERR_INVALID_ARGUMENT;
 }
 
+// Map of a blocked scale array as [atom rows][atoms along K][512 bytes]: boxes of `box_rows` atoms of one K position.
+// Atoms past the end are delivered as zeros.
+int make_scale_map(CUtensorMap *map, const void *base, int64_t atom_rows, int64_t katoms, int box_rows) {
+  EncodeTiledFn encode = nullptr;
+  if (int e = encode_tiled_fn(&encode)) return e;
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(katoms), static_cast<cuuint64_t>(atom_rows)};
+  const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(512 * katoms)};
+  const cuuint32_t box[3] = {128, 1, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void *>(base), dims, strides, box, elem_strides,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? DTQ_OK : DTQ_ERR_INVALID_ARGUMENT;
+}
+
+// The SM-pair kernel: clusters of two CTAs, as many as the device can hold at once (at most one CTA per SM).
+// *max_clusters (cached per device) is 0 where cluster launches of this kernel are not possible.
+int pair_cluster_capacity(int dev_id, int *max_clusters) {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> ready[kMaxDevices];
+  static int capacity[kMaxDevices];
+  if (dev_id < 0 || dev_id >= kMaxDevices) return DTQ_ERR_INVALID_ARGUMENT;
+  if (!ready[dev_id].load(std::memory_order_acquire)) {
+    static std::mutex mutex;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!ready[dev_id].load(std::memory_order_relaxed)) {
+      const int smem = static_cast<int>(sizeof(PairSmem)) + 1024;
+      int n = 0;
+      if (cudaFuncSetAttribute(mx_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, mx_gemm_pair_kernel, &cfg) != cudaSuccess) n = 0;
+      }
+      (void)cudaGetLastError();  // a device without cluster support is not an error of this call
+      capacity[dev_id] = n;
+      ready[dev_id].store(1, std::memory_order_release);
+    }
+  }
+  *max_clusters = capacity[dev_id];
+  return DTQ_OK;
+}
+
+int launch_pair(const void *a, const void *b, const void *sfa, const void *sfb, void *out, int64_t m, int64_t n, int64_t k,
+                int max_clusters, int *status, cudaStream_t st) {
+  CUtensorMap map_a, map_b, map_sfa, map_sfb;
+  const int64_t katoms = ceil_div64(k / 32, 4);
+  if (int e = make_operand_map(&map_a, a, m, k, kBM)) return e;
+  if (int e = make_operand_map(&map_b, b, n, k, kPairBN / 2)) return e;
+  if (int e = make_scale_map(&map_sfa, sfa, ceil_div64(m, 128), katoms, 1)) return e;
+  if (int e = make_scale_map(&map_sfb, sfb, ceil_div64(n, 128), katoms, 2)) return e;
+  PairParams p;
+  p.out = static_cast<uint16_t *>(out);
+  p.M = static_cast<int>(m);
+  p.N = static_cast<int>(n);
+  p.m_pairs = static_cast<int>(ceil_div64(m, 256));
+  p.n_tiles = static_cast<int>(ceil_div64(n, kPairBN));
+  p.k_stages = static_cast<int>(ceil_div64(k, kBK));
+  p.status = status;
+  const int64_t tiles = int64_t(p.m_pairs) * p.n_tiles;
+  const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = sizeof(PairSmem) + 1024;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, mx_gemm_pair_kernel, map_a, map_b, map_sfa, map_sfb, p));
+}
+
+// Launches one tile shape.  `configured` remembers, per device, that the kernel's shared-memory limit was raised.
+template <typename SH>
+int launch_shape(const void *a, const void *b, GemmParams p, int64_t m, int64_t n, int64_t k, const DeviceInfo &dev,
+                 cudaStream_t st) {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> configured[kMaxDevices];
+  int dev_id = 0;
+  DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
+  if (dev_id < 0 || dev_id >= kMaxDevices) return DTQ_ERR_INVALID_ARGUMENT;
+  const int smem = static_cast<int>(sizeof(GemmSmem<SH>)) + 1024;
+  if (!configured[dev_id].load(std::memory_order_acquire)) {  // setting the attribute twice is harmless
+    DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_gemm_kernel<SH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured[dev_id].store(1, std::memory_order_release);
+  }
+  CUtensorMap map_a, map_b;
+  if (int e = make_operand_map(&map_a, a, m, k, kBM)) return e;
+  if (int e = make_operand_map(&map_b, b, n, k, SH::BN)) return e;
+  p.n_tiles = static_cast<int>(ceil_div64(n, SH::BN));
+  const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
+  const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
+  mx_gemm_kernel<SH><<<grid, kGemmThreads, smem, st>>>(map_a, map_b, p);
+  return cuda_status(cudaGetLastError());
+}
+
 }  // namespace
 }  // namespace dtq
 
@@ -389,10 +811,18 @@ extern "C" size_t dtq_mx_gemm_scale_bytes(int64_t rows, int64_t k) {
 extern "C" int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
                                void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
                                void *stream) {
+  return dtq_mx_fp8_bf16_kernel(a, b, a_scales_blocked, b_scales_blocked, out_bf16, m, n, k, DTQ_GEMM_AUTO, workspace,
+                                workspace_bytes, stream);
+}
+
+extern "C" int dtq_mx_fp8_bf16_kernel(const void *a, const void *b, const void *a_scales_blocked,
+                                      const void *b_scales_blocked, void *out_bf16, int64_t m, int64_t n, int64_t k,
+                                      int kernel, void *workspace, size_t workspace_bytes, void *stream) {
   using namespace dtq;
+  if (kernel < DTQ_GEMM_AUTO || kernel > DTQ_GEMM_NARROW) return DTQ_ERR_INVALID_ARGUMENT;
   if (m < 0 || n < 0 || k < 0) return DTQ_ERR_INVALID_ARGUMENT;
   if (n % 8 != 0 || k % 32 != 0) return DTQ_ERR_SHAPE;  // 16-byte output vectors; whole MX blocks (also the TMA row pitch)
-  if (m > 0x7FFFFFFF - kBM || n > 0x7FFFFFFF - kBN || k > 0x7FFFFFFF - kBK) return DTQ_ERR_TOO_LARGE;
+  if (m > 0x7FFFFFFF - kBM || n > 0x7FFFFFFF - 256 || k > 0x7FFFFFFF - kBK) return DTQ_ERR_TOO_LARGE;
   if (!workspace || workspace_bytes < sizeof(Workspace) || !aligned_to(workspace, 256)) return DTQ_ERR_WORKSPACE;
   if (m == 0 || n == 0) return DTQ_OK;
   if (!out_bf16 || !aligned_to(out_bf16, 16)) return DTQ_ERR_INVALID_ARGUMENT;
@@ -404,20 +834,6 @@ extern "C" int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scale
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
 
-  constexpr int kMaxDevices = 64;
-  static std::atomic<int> configured[kMaxDevices];
-  int dev_id = 0;
-  DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
-  if (dev_id < 0 || dev_id >= kMaxDevices) return DTQ_ERR_INVALID_ARGUMENT;
-  const int smem = static_cast<int>(sizeof(GemmSmem)) + 1024;
-  if (!configured[dev_id].load(std::memory_order_acquire)) {  // setting the attribute twice is harmless
-    DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured[dev_id].store(1, std::memory_order_release);
-  }
-
-  CUtensorMap map_a, map_b;
-  if (int e = make_operand_map(&map_a, a, m, k, kBM)) return e;
-  if (int e = make_operand_map(&map_b, b, n, k, kBN)) return e;
   GemmParams p;
   p.sfa = static_cast<const uint8_t *>(a_scales_blocked);
   p.sfb = static_cast<const uint8_t *>(b_scales_blocked);
@@ -426,13 +842,27 @@ extern "C" int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scale
   p.N = static_cast<int>(n);
   p.K = static_cast<int>(k);
   p.m_tiles = static_cast<int>(ceil_div64(m, kBM));
-  p.n_tiles = static_cast<int>(ceil_div64(n, kBN));
+  p.n_tiles = 0;  // set by the launcher of the chosen tile shape
   p.k_stages = static_cast<int>(ceil_div64(k, kBK));
   p.katoms = static_cast<int>(ceil_div64(k / 32, 4));
   p.n_atoms = static_cast<int>(ceil_div64(n, 128));
   p.status = &static_cast<Workspace *>(workspace)->status;
-  const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
-  const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-  mx_gemm_kernel<<<grid, kGemmThreads, smem, st>>>(map_a, map_b, p);
-  return cuda_status(cudaGetLastError());
+  // Which kernel.  All of them are bound by what an SM can pull out of L2, so the estimate is rounds of tiles on
+  // the busiest SM times the operand bytes a CTA loads per round: 48 KB per stage for a wide tile, 32 KB for a
+  // narrow one, 32 KB for a CTA's half of an SM pair's 256 x 256 tile (which is worth a wide tile of output).
+  const double wide = static_cast<double>(ceil_div64(int64_t(p.m_tiles) * ceil_div64(n, 256), dev.sm_count)) * 48.0;
+  const double narrow = static_cast<double>(ceil_div64(int64_t(p.m_tiles) * ceil_div64(n, 128), dev.sm_count)) * 32.0 * 1.15;
+  int dev_id = 0, max_clusters = 0;
+  DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
+  if (int e = pair_cluster_capacity(dev_id, &max_clusters)) return e;
+  const double pair = max_clusters > 0
+                          ? static_cast<double>(ceil_div64(ceil_div64(m, 256) * ceil_div64(n, 256), max_clusters)) * 32.0 * 1.05
+                          : 1e30;
+  if (kernel == DTQ_GEMM_PAIR && max_clusters <= 0) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorNotSupported);
+  if (kernel == DTQ_GEMM_AUTO)
+    kernel = (pair <= wide && pair <= narrow) ? DTQ_GEMM_PAIR : (narrow < wide ? DTQ_GEMM_NARROW : DTQ_GEMM_WIDE);
+  if (kernel == DTQ_GEMM_PAIR)
+    return launch_pair(a, b, a_scales_blocked, b_scales_blocked, out_bf16, m, n, k, max_clusters, p.status, st);
+  if (kernel == DTQ_GEMM_NARROW) return launch_shape<NarrowShape>(a, b, p, m, n, k, dev, st);
+  return launch_shape<WideShape>(a, b, p, m, n, k, dev, st);
 }

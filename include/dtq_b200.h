@@ -335,6 +335,21 @@ size_t dtq_mx_gemm_scale_bytes(int64_t rows, int64_t k);
 int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
                     void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
                     void *stream);
+/*
+ * The same with the kernel named instead of chosen from the problem size (for benchmarks, and for tests that run
+ * every kernel on every size; results are bit-identical between them):
+ *   DTQ_GEMM_PAIR    two CTAs of a cluster (an SM pair) per 256 x 256 tile, tcgen05.mma.cta_group::2: least
+ *                    operand traffic per SM, what large problems use;
+ *   DTQ_GEMM_WIDE    one CTA per 128 x 256 tile;
+ *   DTQ_GEMM_NARROW  one CTA per 128 x 128 tile, two accumulators (epilogue under the next tile's MMAs).
+ */
+#define DTQ_GEMM_AUTO 0
+#define DTQ_GEMM_PAIR 1
+#define DTQ_GEMM_WIDE 2
+#define DTQ_GEMM_NARROW 3
+int dtq_mx_fp8_bf16_kernel(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
+                           void *out_bf16, int64_t m, int64_t n, int64_t k, int kernel, void *workspace,
+                           size_t workspace_bytes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -44,6 +44,15 @@ def _small_int_operands(m, n, k, seed):
     return a, b, sa, sb
 
 
+_ORACLE_CACHE = {}
+
+
+def _oracle_cached(a, b, sab, sbb, key):
+    if key not in _ORACLE_CACHE:
+        _ORACLE_CACHE[key] = qo.mx_gemm_bf16(a, b, sab, sbb)
+    return _ORACLE_CACHE[key]
+
+
 # ---- CPU: the oracle itself ----------------------------------------------------------------------------
 
 def test_oracle_decoders_match_pytorch_casts():
@@ -105,15 +114,20 @@ def test_reference_size_grid_sqnr(size):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["pair", "wide", "narrow"])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 128, 128), (256, 512, 512), (129, 256, 384), (133, 528, 512),
-                                   (384, 384, 384), (64, 8, 32), (300, 520, 96), (1, 8, 64), (1024, 1024, 1024)])
-def test_exact_against_the_oracle_on_exactly_summable_inputs(m, n, k):
+                                   (384, 384, 384), (64, 8, 32), (300, 520, 96), (1, 8, 64), (1024, 1024, 1024),
+                                   (2560, 4096, 256),    # several rounds of tiles per SM: accumulator and stage reuse
+                                   (18944, 504, 128),    # many tile rows, a ragged last tile column
+                                   (9472, 376, 160)])    # a last tile column whose second scale atom does not exist
+def test_exact_against_the_oracle_on_exactly_summable_inputs(m, n, k, kernel):
+    # every kernel (an SM pair per 256 x 256 tile; one CTA per 128 x 256 or per 128 x 128 tile) on every size
     from driss_torch_b200 import _cabi
 
     a, b, sa, sb = _small_int_operands(m, n, k, seed=m + n + k)
     sab, sbb = qo.to_blocked(sa, m, k // 32), qo.to_blocked(sb, n, k // 32)
-    out = _cabi.mx_fp8_bf16(a.cuda(), b.cuda(), sab.cuda(), sbb.cuda())
-    want = qo.mx_gemm_bf16(a, b, sab, sbb)
+    want = _oracle_cached(a, b, sab, sbb, (m, n, k))
+    out = _cabi.mx_fp8_bf16(a.cuda(), b.cuda(), sab.cuda(), sbb.cuda(), kernel=kernel)
     got = out.cpu()
     assert torch.equal(got.view(torch.int16), want.view(torch.int16)), \
         f"{(got.view(torch.int16) != want.view(torch.int16)).sum().item()} of {got.numel()} outputs differ"
@@ -135,9 +149,10 @@ def test_every_scale_position_is_used_where_it_belongs():
         sa[:, kb] = (120 + torch.arange(m) % 13).to(torch.uint8)
         sb[:, kb] = (122 + torch.arange(n) % 11).to(torch.uint8)
         sab, sbb = qo.to_blocked(sa, m, k // 32), qo.to_blocked(sb, n, k // 32)
-        out = _cabi.mx_fp8_bf16(ones_a.cuda(), ones_b.cuda(), sab.cuda(), sbb.cuda()).cpu()
         want = qo.mx_gemm_bf16(ones_a, ones_b, sab, sbb)
-        assert torch.equal(out.view(torch.int16), want.view(torch.int16)), f"k-block {kb}"
+        for kernel in ("pair", "wide", "narrow"):
+            out = _cabi.mx_fp8_bf16(ones_a.cuda(), ones_b.cuda(), sab.cuda(), sbb.cuda(), kernel=kernel).cpu()
+            assert torch.equal(out.view(torch.int16), want.view(torch.int16)), f"k-block {kb}, {kernel} kernel"
 
 
 @pytest.mark.gpu
