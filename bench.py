@@ -187,32 +187,38 @@ def gemm_table(dev, iters: int, warmup: int = 3):
     gen = torch.Generator(device=dev)
     gen.manual_seed(1100)
     ws = _cabi.workspace(dev)
-    for (m, n, k) in [(8192, 8192, 8192), (4096, 4096, 4096), (16384, 8192, 4096), (1024, 1024, 1024)]:
+    for (m, n, k, fp4) in [(8192, 8192, 8192, False), (4096, 4096, 4096, False), (16384, 8192, 4096, False),
+                           (1024, 1024, 1024, False), (8192, 8192, 8192, True)]:
         a = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
         b = torch.randn(n, k, generator=gen, device=dev).to(torch.bfloat16)
-        pa, sa = dtq.mx_fp8_quantize_blocked(a)
-        pb, sb = dtq.mx_fp8_quantize_blocked(b)
+        quantize = (lambda t: dtq.mx_fp4_quantize(t, blocked=True)) if fp4 else dtq.mx_fp8_quantize_blocked
+        pa, sa = quantize(a)
+        pb, sb = quantize(b)
         del a, b
         out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
-        ms, single, single_min = time_rotating(lambda i: _cabi.mx_fp8_bf16(pa, pb, sa, sb, out=out, ws=ws), 1, iters, warmup)
+        ms, single, single_min = time_rotating(lambda i: _cabi.mx_fp8_bf16(pa, pb, sa, sb, out=out, ws=ws, fp4=fp4), 1, iters,
+                                               warmup)
         flops = 2.0 * m * n * k
-        d = {"config": "gemm", "op": "mx_fp8_bf16", "shape": [m, n, k], "us": round(ms * 1e3, 2),
+        set_bytes = pa.numel() + pb.numel() + 2 * m * n
+        d = {"config": "gemm", "op": "mx_fp4_bf16" if fp4 else "mx_fp8_bf16", "shape": [m, n, k], "us": round(ms * 1e3, 2),
              "us_single_launch": round(single * 1e3, 2), "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 1),
-             "note": "e4m3 x e4m3 with E8M0 block scales, fp32 accumulation in tensor memory, bf16 out; back-to-back launches "
+             "note": "%s with E8M0 block scales, fp32 accumulation in tensor memory, bf16 out; back-to-back launches "
                      "on one buffer set of %d MB (operands + output): %s" % (
-                         (m * k + n * k + 2 * m * n) >> 20,
-                         "larger than L2, no flush" if m * k + n * k + 2 * m * n > 2 * 126e6 else "NOT larger than 2x L2: an "
+                         "e2m1 x e2m1 (packed two per byte)" if fp4 else "e4m3 x e4m3", set_bytes >> 20,
+                         "larger than L2, no flush" if set_bytes > 126e6 else "NOT larger than L2: an "
                          "L2-warm figure, as behind the casts that produce the operands")}
         if bf16_peak:
             d["x_measured_bf16_peak"] = round(flops / (ms * 1e-3) / 1e12 / bf16_peak, 3)
             d["peak_note"] = (f"against the pool's measured cuBLAS bf16 throughput ({bf16_peak} TFLOP/s, MEASURED_PEAKS.json); "
-                              "no fp8 peak is measured on this pool: nominal dense fp8 is 2x nominal bf16 (4.5 vs 2.25 PFLOP/s)")
+                              "no fp8 / fp4 peak is measured on this pool: nominal dense fp8 is 2x, fp4 4x nominal bf16 "
+                              "(4.5 / 9 vs 2.25 PFLOP/s)")
         d["device_status"] = _cabi.workspace_status(ws)
         if ref is not None:
             pbt = pb.t()
-            want = ref.mx_fp8_bf16(pa, pbt, sa, sb)
+            ref_fn = ref.mx_fp4_bf16 if fp4 else ref.mx_fp8_bf16
+            want = ref_fn(pa, pbt, sa, sb)
             d["equals_reference_kernel_bitwise"] = bool(torch.equal(want.view(torch.int16), out.view(torch.int16)))
-            rms, _, _ = time_rotating(lambda i: ref.mx_fp8_bf16(pa, pbt, sa, sb), 1, iters, warmup)
+            rms, _, _ = time_rotating(lambda i: ref_fn(pa, pbt, sa, sb), 1, iters, warmup)
             d["reference_kernel_us"] = round(rms * 1e3, 2)
             d["reference_kernel_TFLOPs"] = round(flops / (rms * 1e-3) / 1e12, 1)
             d["speedup_vs_reference_kernel"] = round(rms / ms, 2)

@@ -103,6 +103,14 @@ def mx_fp8_bf16(a: Tensor, b: Tensor, a_scale: Tensor, b_scale: Tensor) -> Tenso
     return ops.mx_fp8_bf16(a, b, a_scale, b_scale)
 
 
+def mx_fp4_bf16(a: Tensor, b: Tensor, a_scale: Tensor, b_scale: Tensor) -> Tensor:
+    """Matrix multiplication of two MXFP4 operands (e2m1 values packed two per byte, the lower index in the low
+    nibble; E8M0 scales of 32 elements along K, blocked layout) (driss_torch/__init__.py:98-111): ``a`` [M, K/2]
+    bytes row-major, ``b`` [K/2, N] column-major (``w.t()`` of a row-major [N, K/2] payload); returns bf16 [M, N].
+    ``mx_fp4_quantize`` produces the payloads; its row-major scales go through ``mx_blocked_scales``."""
+    return ops.mx_fp4_bf16(a, b, a_scale, b_scale)
+
+
 # The north-star text calls the MX op "mx_cast"; the reference symbol is mx_fp8_quantize.
 mx_cast = mx_fp8_quantize
 
@@ -145,11 +153,12 @@ def mx_fp8_quantize_with_amax(input: Tensor) -> tuple[Tensor, Tensor, Tensor]:
     return ops.mx_fp8_quantize_with_amax(input)
 
 
-def mx_fp4_quantize(input: Tensor) -> tuple[Tensor, Tensor]:
+def mx_fp4_quantize(input: Tensor, blocked: bool = False) -> tuple[Tensor, Tensor]:
     """MXFP4: ``(uint8 [M, N/2], E8M0 scales [M * N / 32])``; e2m1 values packed two per byte, the
     lower index in the low nibble -- the operands of the reference's ``mx_fp4_bf16``, which has no
-    producer kernel there.  Same scale rule as ``mx_fp8_quantize`` with e2m1's largest exponent 2."""
-    return ops.mx_fp4_quantize(input)
+    producer kernel there.  Same scale rule as ``mx_fp8_quantize`` with e2m1's largest exponent 2.
+    ``blocked``: the scales in the blocked layout ``mx_fp4_bf16`` takes (as ``mx_fp8_quantize_blocked``)."""
+    return ops.mx_fp4_quantize(input, blocked)
 
 
 def mx_fp8_quantize_dual(input: Tensor, blocked: bool = False) -> tuple[Tensor, Tensor, Tensor, Tensor]:
@@ -180,6 +189,7 @@ __all__ = [
     "mx_fp8_quantize",
     "mx_cast",
     "mx_fp8_bf16",
+    "mx_fp4_bf16",
     "dynamic_scaled_quant_with_scale",
     "dynamic_scaled_quant_rowwise",
     "cast_with_amax",

@@ -44,13 +44,15 @@ SIGNATURES = {
     "dtq_mx_fp8_quantize_amax": ([_vp, _vp, _vp, _vp, _i64, _i64, _vp, _sz, _vp], _i32),
     "dtq_mx_fp8_quantize_amax_p2p": ([_vp, _vp, _vp, _vp, _i64, _i64, _vp, _sz, _vp, _i32, _i32, C.c_uint32, C.c_uint32, _vp], _i32),
     "dtq_mx_quantize": ([_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
+    "dtq_mx_quantize_blocked": ([_vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp], _i32),
     "dtq_mx_fp8_quantize_dual": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp], _i32),
     "dtq_mx_fp8_quantize_dual_blocked": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp], _i32),
     "dtq_mx_fp8_quantize_tma": ([_vp, _vp, _vp, _i64, _i64, _vp, _vp], _i32),
     "dtq_mx_blocked_scale_bytes": ([_i64, _i64], _sz),
     "dtq_mx_gemm_scale_bytes": ([_i64, _i64], _sz),
     "dtq_mx_fp8_bf16": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp], _i32),
-    "dtq_mx_fp8_bf16_kernel": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _sz, _vp], _i32),
+    "dtq_mx_fp4_bf16": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp], _i32),
+    "dtq_mx_gemm_bf16": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _sz, _vp], _i32),
     "dtq_mx_fp8_quantize_blocked": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
 }
 
@@ -295,13 +297,21 @@ MX_FMT_CODE = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1, torch.float4_e2m1fn
 
 
 @_on_device_of_first_tensor
-def mx_quantize(x, elem, payload=None, scales=None):
-    """MX block-32 cast of bf16 / fp16 / fp32 to e4m3 / e5m2 (payload [M, N]) or e2m1 (uint8 [M, N/2])."""
+def mx_quantize(x, elem, payload=None, scales=None, blocked=False):
+    """MX block-32 cast of bf16 / fp16 / fp32 to e4m3 / e5m2 (payload [M, N]) or e2m1 (uint8 [M, N/2]);
+    ``blocked``: the scales in the MX GEMM's blocked layout (zero-filled padding)."""
     rows, cols = x.shape
     fmt = MX_FMT_CODE[elem]
     if payload is None:
         payload = (torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device) if fmt == 2
                    else torch.empty(rows, cols, dtype=elem, device=x.device))
+    if blocked:
+        if scales is None:
+            nbytes = load().dtq_mx_blocked_scale_bytes(rows, cols)
+            scales = torch.zeros(nbytes, dtype=torch.uint8, device=x.device).view(torch.float8_e8m0fnu)
+        check(load().dtq_mx_quantize_blocked(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols,
+                                             MX_IN_CODE[x.dtype], fmt, _stream()), "dtq_mx_quantize_blocked")
+        return payload, scales
     scales = torch.empty(rows * (cols // 32), dtype=torch.float8_e8m0fnu, device=x.device) if scales is None else scales
     check(load().dtq_mx_quantize(x.data_ptr(), payload.data_ptr(), scales.data_ptr(), rows, cols, MX_IN_CODE[x.dtype], fmt,
                                  _stream()), "dtq_mx_quantize")
@@ -361,14 +371,21 @@ GEMM_KERNELS = {"auto": 0, "pair": 1, "wide": 2, "narrow": 3}
 
 
 @_on_device_of_first_tensor
-def mx_fp8_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=None, ws=None, kernel="auto"):
+def mx_fp8_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=None, ws=None, kernel="auto", fp4=False):
     """MX block-scaled GEMM: ``a`` [M, K] e4m3, ``b_nk`` [N, K] e4m3 (the memory of the reference's column-major
-    [K, N] operand), blocked E8M0 scales -> bf16 [M, N].  ``kernel``: "auto", or one of "pair", "wide", "narrow"."""
-    m, k = a.shape
+    [K, N] operand), blocked E8M0 scales -> bf16 [M, N].  ``fp4``: the operands are packed e2m1 bytes, [M, K/2] and
+    [N, K/2].  ``kernel``: "auto", or one of "pair", "wide", "narrow"."""
+    m = a.shape[0]
+    k = a.shape[1] * (2 if fp4 else 1)
     n = b_nk.shape[0]
     out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device) if out is None else out
     ws = workspace(a.device) if ws is None else ws
-    check(load().dtq_mx_fp8_bf16_kernel(a.data_ptr(), b_nk.data_ptr(), a_scale_blocked.data_ptr(),
-                                        b_scale_blocked.data_ptr(), out.data_ptr(), m, n, k, GEMM_KERNELS[kernel],
-                                        ws.data_ptr(), ws.numel(), _stream()), "dtq_mx_fp8_bf16")
+    check(load().dtq_mx_gemm_bf16(a.data_ptr(), b_nk.data_ptr(), a_scale_blocked.data_ptr(), b_scale_blocked.data_ptr(),
+                                  out.data_ptr(), m, n, k, 2 if fp4 else 0, GEMM_KERNELS[kernel], ws.data_ptr(), ws.numel(),
+                                  _stream()), "dtq_mx_gemm_bf16")
     return out
+
+
+def mx_fp4_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=None, ws=None, kernel="auto"):
+    """The MXFP4 GEMM: packed e2m1 operands ``a`` [M, K/2], ``b_nk`` [N, K/2] (uint8), blocked E8M0 scales -> bf16."""
+    return mx_fp8_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=out, ws=ws, kernel=kernel, fp4=True)

@@ -44,6 +44,11 @@ def mx_fp8_bf16_meta(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_
     return torch.empty((a.shape[0], b.shape[1]), dtype=torch.bfloat16, device=a.device)
 
 
+@register_fake("DrissTorch::mx_fp4_bf16")
+def mx_fp4_bf16_meta(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_scale: torch.Tensor):
+    return torch.empty((a.shape[0], b.shape[1]), dtype=torch.bfloat16, device=a.device)
+
+
 @register_fake("DrissTorch::dynamic_scaled_quant_with_scale")
 def dynamic_scaled_quant_with_scale_meta(x: torch.Tensor, dtype: torch.dtype):
     one = lambda: torch.empty(1, dtype=torch.float32, device=x.device)  # noqa: E731
@@ -93,10 +98,11 @@ def saturated_cast_dual_meta(x: torch.Tensor, scale: torch.Tensor, dtype: torch.
 
 
 @register_fake("DrissTorch::mx_fp4_quantize")
-def mx_fp4_quantize_meta(x: torch.Tensor):
+def mx_fp4_quantize_meta(x: torch.Tensor, blocked: bool = False):
     m, n = x.shape
+    nscales = ((m + 127) // 128) * ((n // 32 + 3) // 4) * 512 if blocked else m * (n // 32)
     return (torch.empty((m, n // 2), dtype=torch.uint8, device=x.device),
-            torch.empty(m * (n // 32), dtype=torch.float8_e8m0fnu, device=x.device))
+            torch.empty(nscales, dtype=torch.float8_e8m0fnu, device=x.device))
 
 
 @register_fake("DrissTorch::mx_fp8_quantize_with_amax")

@@ -146,7 +146,7 @@ __device__ __forceinline__ void convert_store(const float (&f)[N], float inv, ui
 template <int IN, int FMT>
 __global__ void __launch_bounds__(kThreadsF, 2048 / kThreadsF)
 mx_formats_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
-                  int64_t nchunks) {
+                  int64_t nchunks, int64_t kblocks) {  // kblocks > 0: scales in the MX GEMM's blocked layout, that many per row
   using I = MxIn<IN>;
   using O = MxOut<FMT>;
   constexpr int kLanes = 32 / I::kElems;                        // lanes per MX block
@@ -172,14 +172,18 @@ mx_formats_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, u
         float f[I::kElems];
         I::unpack(v[u], f);
         convert_store<I::kElems, FMT>(f, inverse_scale_wide(biased), payload + c * kChunkBytesOut);
-        if ((lane & (kLanes - 1)) == 0) scales[c / kLanes] = static_cast<uint8_t>(biased);
+        if ((lane & (kLanes - 1)) == 0) {
+          const int64_t blk = c / kLanes;
+          scales[kblocks > 0 ? scale_offset<true>(blk, kblocks, (kblocks + 3) / 4) : blk] = static_cast<uint8_t>(biased);
+        }
       }
     }
   }
 }
 
 template <int IN, int FMT>
-int launch_formats(const void *in, void *payload, void *scales, int64_t numel, const DeviceInfo &dev, cudaStream_t st) {
+int launch_formats(const void *in, void *payload, void *scales, int64_t numel, int64_t kblocks, const DeviceInfo &dev,
+                   cudaStream_t st) {
   using I = MxIn<IN>;
   constexpr int kChunkBytesOut = I::kElems * MxOut<FMT>::kBitsPerElem / 8;
   if (!aligned_to(in, 16) || !aligned_to(payload, kChunkBytesOut)) return DTQ_ERR_INVALID_ARGUMENT;
@@ -187,26 +191,22 @@ int launch_formats(const void *in, void *payload, void *scales, int64_t numel, c
   const int64_t tiles = ceil_div64(nchunks, int64_t(kThreadsF) * kUnrollF);
   const int grid = balanced_grid(tiles, int64_t(dev.sm_count) * (1 << 20));
   mx_formats_kernel<IN, FMT><<<grid, kThreadsF, 0, st>>>(static_cast<const uint4 *>(in), static_cast<uint8_t *>(payload),
-                                                         static_cast<uint8_t *>(scales), nchunks);
+                                                         static_cast<uint8_t *>(scales), nchunks, kblocks);
   return cuda_status(cudaGetLastError());
 }
 
 template <int IN>
-int launch_by_format(int fmt, const void *in, void *payload, void *scales, int64_t numel, const DeviceInfo &dev,
-                     cudaStream_t st) {
+int launch_by_format(int fmt, const void *in, void *payload, void *scales, int64_t numel, int64_t kblocks,
+                     const DeviceInfo &dev, cudaStream_t st) {
   switch (fmt) {
-    case DTQ_E4M3: return launch_formats<IN, DTQ_E4M3>(in, payload, scales, numel, dev, st);
-    case DTQ_E5M2: return launch_formats<IN, DTQ_E5M2>(in, payload, scales, numel, dev, st);
-    default: return launch_formats<IN, DTQ_E2M1>(in, payload, scales, numel, dev, st);
+    case DTQ_E4M3: return launch_formats<IN, DTQ_E4M3>(in, payload, scales, numel, kblocks, dev, st);
+    case DTQ_E5M2: return launch_formats<IN, DTQ_E5M2>(in, payload, scales, numel, kblocks, dev, st);
+    default: return launch_formats<IN, DTQ_E2M1>(in, payload, scales, numel, kblocks, dev, st);
   }
 }
 
-}  // namespace
-}  // namespace dtq
-
-extern "C" int dtq_mx_quantize(const void *in, void *payload, void *scales_e8m0, int64_t rows, int64_t cols,
-                               int in_dtype, int elem_format, void *stream) {
-  using namespace dtq;
+int mx_quantize_any(const void *in, void *payload, void *scales_e8m0, int64_t rows, int64_t cols, int in_dtype, int elem_format,
+                    bool blocked, void *stream) {
   if (rows < 0 || cols < 0) return DTQ_ERR_INVALID_ARGUMENT;
   if (in_dtype != DTQ_BF16 && in_dtype != DTQ_F32 && in_dtype != DTQ_F16) return DTQ_ERR_UNSUPPORTED_DTYPE;
   if (elem_format != DTQ_E4M3 && elem_format != DTQ_E5M2 && elem_format != DTQ_E2M1) return DTQ_ERR_UNSUPPORTED_DTYPE;
@@ -217,9 +217,23 @@ extern "C" int dtq_mx_quantize(const void *in, void *payload, void *scales_e8m0,
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t kblocks = blocked ? cols / 32 : 0;
   switch (in_dtype) {
-    case DTQ_BF16: return launch_by_format<DTQ_BF16>(elem_format, in, payload, scales_e8m0, numel, dev, st);
-    case DTQ_F16: return launch_by_format<DTQ_F16>(elem_format, in, payload, scales_e8m0, numel, dev, st);
-    default: return launch_by_format<DTQ_F32>(elem_format, in, payload, scales_e8m0, numel, dev, st);
+    case DTQ_BF16: return launch_by_format<DTQ_BF16>(elem_format, in, payload, scales_e8m0, numel, kblocks, dev, st);
+    case DTQ_F16: return launch_by_format<DTQ_F16>(elem_format, in, payload, scales_e8m0, numel, kblocks, dev, st);
+    default: return launch_by_format<DTQ_F32>(elem_format, in, payload, scales_e8m0, numel, kblocks, dev, st);
   }
+}
+
+}  // namespace
+}  // namespace dtq
+
+extern "C" int dtq_mx_quantize(const void *in, void *payload, void *scales_e8m0, int64_t rows, int64_t cols,
+                               int in_dtype, int elem_format, void *stream) {
+  return dtq::mx_quantize_any(in, payload, scales_e8m0, rows, cols, in_dtype, elem_format, false, stream);
+}
+
+extern "C" int dtq_mx_quantize_blocked(const void *in, void *payload, void *scales_blocked, int64_t rows, int64_t cols,
+                                       int in_dtype, int elem_format, void *stream) {
+  return dtq::mx_quantize_any(in, payload, scales_blocked, rows, cols, in_dtype, elem_format, true, stream);
 }

@@ -38,8 +38,21 @@ constexpr int kBM = 128;        // tile rows (M)
 constexpr int kBK = 128;        // K bytes per stage: one 128-byte swizzle span = 4 MX blocks of 32
 constexpr int kGemmThreads = 320;  // producer warp, MMA warp, 8 epilogue warps
 constexpr int kEpilogueWarps = 8;
-constexpr int kSfaCol = 256;               // 4 tensor-memory columns: scales of 128 rows x 4 k-blocks
-constexpr int kSfbCol = 256 + 8;           // up to 8 columns: scales of up to 256 rows x 4 k-blocks
+constexpr int kSfaCol = 256;               // scales of A: 4 tensor-memory columns per atom (128 rows x 4 k-blocks)
+constexpr int kSfbCol = 256 + 16;          // scales of B: 4 columns per atom, up to 2 (N) x 2 (K) atoms
+// Element formats.  e4m3: one byte per element, a 128-byte stage is 128 elements = 4 MX blocks = one scale atom
+// along K, tcgen05.mma kind::mxf8f6f4 (K = 32 per instruction, one scale byte each for A and B).  e2m1 (MXFP4): two
+// elements per byte, a 128-byte stage is 256 elements = 8 MX blocks = two scale atoms along K, kind::mxf4 with
+// block32 scaling (K = 64 per instruction, which uses two consecutive scale bytes).  Either way an instruction
+// reads 32 bytes of every operand row, so the operand descriptors are the same.
+template <bool FP4>
+struct Format {
+  static constexpr int kKAtoms = FP4 ? 2 : 1;  // scale atoms along K per stage
+  // k (0..3) = the instruction within a stage: which atom along K, and which byte (pair) of its 4-byte scale columns
+  __device__ static constexpr uint32_t k_atom(uint32_t k) { return FP4 ? k >> 1 : 0u; }
+  __device__ static constexpr uint32_t sf_id(uint32_t k) { return FP4 ? (k & 1u) * 2u : k; }
+  static constexpr uint32_t kFormatBits = FP4 ? ((1u << 7) | (1u << 10)) : 0u;  // a_format, b_format: e2m1 (kind::mxf4) or e4m3
+};
 constexpr int kTmemCols = 512;             // allocation (power of two); columns 0..255 hold the accumulator(s)
 
 // Two tile shapes.  Wide: 128 x 256, one accumulator of 256 columns, 4 stages -- least operand traffic per
@@ -57,12 +70,12 @@ using WideShape = GemmShape<256, 4, 1>;
 using NarrowShape = GemmShape<128, 6, 2>;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds of wall time
 
-template <typename SH>
+template <typename SH, bool FP4>
 struct __align__(1024) GemmSmem {
   uint8_t a[SH::STAGES][kBM * kBK];        // 16 KB per stage, 1024-byte aligned (swizzle atom = 8 rows x 128 B)
   uint8_t b[SH::STAGES][SH::BN * kBK];     // 16 or 32 KB per stage
-  uint8_t sfa[SH::STAGES][512];            // one blocked atom: 128 rows x 4 k-blocks
-  uint8_t sfb[SH::STAGES][SH::BN / 128 * 512];  // one atom per 128 tile columns
+  uint8_t sfa[SH::STAGES][Format<FP4>::kKAtoms * 512];                  // blocked atoms of 128 rows x 4 k-blocks
+  uint8_t sfb[SH::STAGES][SH::BN / 128 * Format<FP4>::kKAtoms * 512];  // [128 tile columns][atom along K]
   uint64_t full[SH::STAGES];
   uint64_t empty[SH::STAGES];
   uint64_t tmem_full[SH::ACC];
@@ -142,8 +155,32 @@ __device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
 }
 // Instruction descriptor of tcgen05.mma kind::mxf8f6f4.block_scale: e4m3 x e4m3, both K-major, E8M0 scales,
 // M = 128, N = `bn`; `k` (0..3) is the byte of the 4-byte scale column that this k-block uses, for A and B.
-__device__ __forceinline__ uint32_t instr_desc(uint32_t k, uint32_t bn) {
-  return (k << 4) | ((bn >> 3) << 17) | (1u << 23) | (uint32_t(kBM >> 4) << 24) | (k << 29);
+__device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id, uint32_t bn, uint32_t m, uint32_t format_bits) {
+  return (sf_id << 4) | format_bits | ((bn >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_id << 29);
+}
+// One block-scaled MMA: D (tensor memory) (+)= A x B with the scales found at the two tensor-memory addresses.
+template <bool FP4, bool PAIR>
+__device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem) {
+#define DTQ_MMA(GROUP, KIND)                                                                                         \
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                     \
+               "tcgen05.mma.cta_group::" GROUP ".kind::" KIND " [%0], %1, %2, %3, [%5], [%6], p;\n\t}"                \
+               :                                                                                                     \
+               : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)    \
+               : "memory")
+  if constexpr (FP4 && PAIR) DTQ_MMA("2", "mxf4.block_scale.block32");
+  else if constexpr (FP4) DTQ_MMA("1", "mxf4.block_scale.block32");
+  else if constexpr (PAIR) DTQ_MMA("2", "mxf8f6f4.block_scale");
+  else DTQ_MMA("1", "mxf8f6f4.block_scale");
+#undef DTQ_MMA
+}
+// One scale atom, shared memory -> 4 tensor-memory columns (32 rows x 16 bytes, replicated to the four lane quadrants).
+template <bool PAIR>
+__device__ __forceinline__ void copy_scale_atom(uint32_t tmem_col_addr, uint32_t smem_atom_addr) {
+  if constexpr (PAIR)
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col_addr), "l"(scale_desc(smem_atom_addr)) : "memory");
+  else
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col_addr), "l"(scale_desc(smem_atom_addr)) : "memory");
 }
 
 __device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -181,12 +218,14 @@ struct GemmParams {
   int *status;
 };
 
-template <typename SH>
+template <typename SH, bool FP4>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
   constexpr int kBN = SH::BN, kStagesG = SH::STAGES, kAcc = SH::ACC, kAtomsB = SH::BN / 128;
+  constexpr int kKAtoms = Format<FP4>::kKAtoms;
   extern __shared__ unsigned char smem_raw[];
-  GemmSmem<SH> &sm = *reinterpret_cast<GemmSmem<SH> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
+  GemmSmem<SH, FP4> &sm =
+      *reinterpret_cast<GemmSmem<SH, FP4> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *abort = &sm.abort;
 
@@ -202,8 +241,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     sm.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // scale staging starts as zeros: an atom that does not exist (N not a multiple of the tile) is never copied
+  // scale staging starts as zeros: an atom that does not exist (N or K not a multiple of the tile) is never copied
   for (int i = threadIdx.x; i < int(sizeof(sm.sfb) / 4); i += kGemmThreads) reinterpret_cast<uint32_t *>(sm.sfb)[i] = 0;
+  for (int i = threadIdx.x; i < int(sizeof(sm.sfa) / 4); i += kGemmThreads) reinterpret_cast<uint32_t *>(sm.sfa)[i] = 0;
   if (warp == 1) {  // the MMA warp owns tensor memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sm.tmem_base)),
                  "r"(kTmemCols)
@@ -233,12 +273,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           const int atoms_b = min(kAtomsB, p.n_atoms - nt * kAtomsB);
-          mbar_expect_tx(&sm.full[s], kBM * kBK + kBN * kBK + 512 + 512 * atoms_b);
+          const unsigned sf_bytes = 512u * min(kKAtoms, p.katoms - ks * kKAtoms);  // the atoms along K are adjacent in memory
+          mbar_expect_tx(&sm.full[s], kBM * kBK + kBN * kBK + sf_bytes * (1 + atoms_b));
           tma_load_2d(sm.a[s], &map_a, ks * kBK, mt * kBM, &sm.full[s]);
           tma_load_2d(sm.b[s], &map_b, ks * kBK, nt * kBN, &sm.full[s]);
-          bulk_load_1d(sm.sfa[s], p.sfa + (int64_t(mt) * p.katoms + ks) * 512, 512, &sm.full[s]);
+          bulk_load_1d(sm.sfa[s], p.sfa + (int64_t(mt) * p.katoms + ks * kKAtoms) * 512, sf_bytes, &sm.full[s]);
           for (int h = 0; h < atoms_b; ++h)
-            bulk_load_1d(sm.sfb[s] + h * 512, p.sfb + (int64_t(nt * kAtomsB + h) * p.katoms + ks) * 512, 512, &sm.full[s]);
+            bulk_load_1d(sm.sfb[s] + h * kKAtoms * 512, p.sfb + (int64_t(nt * kAtomsB + h) * p.katoms + ks * kKAtoms) * 512,
+                         sf_bytes, &sm.full[s]);
         }
       }
       if (!ok) {
@@ -272,28 +314,23 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           tmem_fence_after();
-          // this stage's scales: shared memory -> tensor memory, ordered before the MMAs below
-          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfaCol),
-                       "l"(scale_desc(smem_addr(sm.sfa[s])))
-                       : "memory");
-          asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol),
-                       "l"(scale_desc(smem_addr(sm.sfb[s])))
-                       : "memory");
-          if constexpr (kAtomsB == 2)
-            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 4),
-                         "l"(scale_desc(smem_addr(sm.sfb[s] + 512)))
-                         : "memory");
+          // this stage's scales: shared memory -> tensor memory, ordered before the MMAs below.  Tensor-memory
+          // columns: A's atom j along K at kSfaCol + 4 j; B's at kSfbCol + j * 4 kAtomsB + 4 h (h = 128 tile columns)
+#pragma unroll
+          for (int j = 0; j < kKAtoms; ++j) {
+            copy_scale_atom<false>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[s] + j * 512));
+#pragma unroll
+            for (int h = 0; h < kAtomsB; ++h)
+              copy_scale_atom<false>(tmem + kSfbCol + j * 4 * kAtomsB + 4 * h, smem_addr(sm.sfb[s] + (h * kKAtoms + j) * 512));
+          }
           const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) {  // four k-blocks of 32 bytes inside the 128-byte swizzle span
+          for (uint32_t k = 0; k < 4; ++k) {  // four instructions of 32 operand bytes inside the 128-byte swizzle span
             const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
-            asm volatile(
-                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-                :
-                : "r"(d_tmem), "l"(operand_desc(a_addr + k * 32)), "l"(operand_desc(b_addr + k * 32)), "r"(instr_desc(k, kBN)),
-                  "r"(accumulate), "r"((tmem + kSfaCol) | (k << 30)), "r"((tmem + kSfbCol) | (k << 30))
-                : "memory");
+            const uint32_t j = Format<FP4>::k_atom(k), id = Format<FP4>::sf_id(k);
+            issue_mma<FP4, false>(d_tmem, operand_desc(a_addr + k * 32), operand_desc(b_addr + k * 32),
+                                  instr_desc(id, kBN, kBM, Format<FP4>::kFormatBits), accumulate,
+                                  (tmem + kSfaCol + 4 * j) | (id << 30), (tmem + kSfbCol + j * 4 * kAtomsB) | (id << 30));
           }
           umma_commit(&sm.empty[s]);  // the stage is free once these MMAs have read it
         }
@@ -396,11 +433,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 constexpr int kPairStages = 6;
 constexpr int kPairBN = 256;  // tile columns; each CTA holds kPairBN / 2 rows of B
 
+template <bool FP4>
 struct __align__(1024) PairSmem {
   uint8_t a[kPairStages][kBM * kBK];             // this CTA's 128 rows of A
   uint8_t b[kPairStages][kPairBN / 2 * kBK];     // this CTA's 128 of the tile's 256 rows of B
-  uint8_t sfa[kPairStages][512];                 // scales of this CTA's 128 rows of A
-  uint8_t sfb[kPairStages][2 * 512];             // scales of all 256 rows of B
+  uint8_t sfa[kPairStages][Format<FP4>::kKAtoms * 512];      // scales of this CTA's 128 rows of A
+  uint8_t sfb[kPairStages][2 * Format<FP4>::kKAtoms * 512];  // scales of all 256 rows of B: [128 columns][atom along K]
   uint64_t full[kPairStages];                    // used in the leader CTA only
   uint64_t empty[kPairStages];
   uint64_t tmem_full;
@@ -448,10 +486,6 @@ __device__ __forceinline__ void tma_pair_load_3d(void *dst, const CUtensorMap *m
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
-// Instruction descriptor as above with M = 256 (two CTAs x 128 rows).
-__device__ __forceinline__ uint32_t instr_desc_pair(uint32_t k) {
-  return (k << 4) | (uint32_t(kPairBN >> 3) << 17) | (1u << 23) | (uint32_t(256 >> 4) << 24) | (k << 29);
-}
 
 struct PairParams {
   uint16_t *out;  // bf16 [M, N]
@@ -460,11 +494,13 @@ struct PairParams {
   int *status;
 };
 
+template <bool FP4>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, PairParams p) {
+  constexpr int kKAtoms = Format<FP4>::kKAtoms;
   extern __shared__ unsigned char smem_raw[];
-  PairSmem &sm = *reinterpret_cast<PairSmem *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
+  PairSmem<FP4> &sm = *reinterpret_cast<PairSmem<FP4> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const bool leader = rank == 0;
@@ -512,11 +548,11 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             break;
           }
           const uint32_t bar = map_to_cta(smem_addr(&sm.full[s]), 0);  // the leader's barrier
-          if (leader) mbar_expect_tx(&sm.full[s], 2 * (kBM * kBK + kPairBN / 2 * kBK + 512 + 2 * 512));
+          if (leader) mbar_expect_tx(&sm.full[s], 2 * (kBM * kBK + kPairBN / 2 * kBK + 3 * kKAtoms * 512));
           tma_pair_load_2d(sm.a[s], &map_a, ks * kBK, mp * 256 + int(rank) * kBM, bar);
           tma_pair_load_2d(sm.b[s], &map_b, ks * kBK, nt * kPairBN + int(rank) * (kPairBN / 2), bar);
-          tma_pair_load_3d(sm.sfa[s], &map_sfa, 0, ks, mp * 2 + int(rank), bar);
-          tma_pair_load_3d(sm.sfb[s], &map_sfb, 0, ks, nt * 2, bar);
+          tma_pair_load_3d(sm.sfa[s], &map_sfa, 0, ks * kKAtoms, mp * 2 + int(rank), bar);
+          tma_pair_load_3d(sm.sfb[s], &map_sfb, 0, ks * kKAtoms, nt * 2, bar);
         }
       }
       if (!ok) {
@@ -546,26 +582,21 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             break;
           }
           tmem_fence_after();
-          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfaCol),
-                       "l"(scale_desc(smem_addr(sm.sfa[s])))
-                       : "memory");
-          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol),
-                       "l"(scale_desc(smem_addr(sm.sfb[s])))
-                       : "memory");
-          asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem + kSfbCol + 4),
-                       "l"(scale_desc(smem_addr(sm.sfb[s] + 512)))
-                       : "memory");
+#pragma unroll
+          for (int j = 0; j < kKAtoms; ++j) {  // each CTA's shared memory -> that CTA's tensor memory, columns as above
+            copy_scale_atom<true>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[s] + j * 512));
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              copy_scale_atom<true>(tmem + kSfbCol + j * 8 + 4 * h, smem_addr(sm.sfb[s] + (h * kKAtoms + j) * 512));
+          }
           const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {
             const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
-            asm volatile(
-                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-                :
-                : "r"(tmem), "l"(operand_desc(a_addr + k * 32)), "l"(operand_desc(b_addr + k * 32)), "r"(instr_desc_pair(k)),
-                  "r"(accumulate), "r"((tmem + kSfaCol) | (k << 30)), "r"((tmem + kSfbCol) | (k << 30))
-                : "memory");
+            const uint32_t j = Format<FP4>::k_atom(k), id = Format<FP4>::sf_id(k);
+            issue_mma<FP4, true>(tmem, operand_desc(a_addr + k * 32), operand_desc(b_addr + k * 32),
+                                 instr_desc(id, kPairBN, 256, Format<FP4>::kFormatBits), accumulate,
+                                 (tmem + kSfaCol + 4 * j) | (id << 30), (tmem + kSfbCol + j * 8) | (id << 30));
           }
           // the stage is free in both CTAs once these MMAs have read it
           umma_commit_pair(smem_addr(&sm.empty[s]));
@@ -692,14 +723,14 @@ int make_operand_map(CUtensorMap *map, const void *base, int64_t rows, int64_t k
   return r == CUDA_SUCCESS ? DTQ_OK : DTQ_ERR_INVALID_ARGUMENT;
 }
 
-// Map of a blocked scale array as [atom rows][atoms along K][512 bytes]: boxes of `box_rows` atoms of one K position.
+// Map of a blocked scale array as [atom rows][atoms along K][512 bytes]: boxes of `box_rows` x `box_katoms` atoms.
 // Atoms past the end are delivered as zeros.
-int make_scale_map(CUtensorMap *map, const void *base, int64_t atom_rows, int64_t katoms, int box_rows) {
+int make_scale_map(CUtensorMap *map, const void *base, int64_t atom_rows, int64_t katoms, int box_rows, int box_katoms) {
   EncodeTiledFn encode = nullptr;
   if (int e = encode_tiled_fn(&encode)) return e;
   const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(katoms), static_cast<cuuint64_t>(atom_rows)};
   const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(512 * katoms)};
-  const cuuint32_t box[3] = {128, 1, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t box[3] = {128, static_cast<cuuint32_t>(box_katoms), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void *>(base), dims, strides, box, elem_strides,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -707,32 +738,40 @@ int make_scale_map(CUtensorMap *map, const void *base, int64_t atom_rows, int64_
   return r == CUDA_SUCCESS ? DTQ_OK : DTQ_ERR_INVALID_ARGUMENT;
 }
 
+constexpr int kMaxGemmDevices = 64;
+
+void cluster_launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int grid, size_t smem, cudaStream_t st) {
+  *cfg = cudaLaunchConfig_t{};
+  cfg->gridDim = dim3(grid);
+  cfg->blockDim = dim3(kGemmThreads);
+  cfg->dynamicSmemBytes = smem;
+  cfg->stream = st;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+}
+
 // The SM-pair kernel: clusters of two CTAs, as many as the device can hold at once (at most one CTA per SM).
-// *max_clusters (cached per device) is 0 where cluster launches of this kernel are not possible.
+// *max_clusters (cached per device and format) is 0 where cluster launches of this kernel are not possible.
+template <bool FP4>
 int pair_cluster_capacity(int dev_id, int *max_clusters) {
-  constexpr int kMaxDevices = 64;
-  static std::atomic<int> ready[kMaxDevices];
-  static int capacity[kMaxDevices];
-  if (dev_id < 0 || dev_id >= kMaxDevices) return DTQ_ERR_INVALID_ARGUMENT;
+  static std::atomic<int> ready[kMaxGemmDevices];
+  static int capacity[kMaxGemmDevices];
+  if (dev_id < 0 || dev_id >= kMaxGemmDevices) return DTQ_ERR_INVALID_ARGUMENT;
   if (!ready[dev_id].load(std::memory_order_acquire)) {
     static std::mutex mutex;
     std::lock_guard<std::mutex> lock(mutex);
     if (!ready[dev_id].load(std::memory_order_relaxed)) {
-      const int smem = static_cast<int>(sizeof(PairSmem)) + 1024;
+      const int smem = static_cast<int>(sizeof(PairSmem<FP4>)) + 1024;
       int n = 0;
-      if (cudaFuncSetAttribute(mx_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2);
-        cfg.blockDim = dim3(kGemmThreads);
-        cfg.dynamicSmemBytes = smem;
+      if (cudaFuncSetAttribute(mx_gemm_pair_kernel<FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
+        cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        if (cudaOccupancyMaxActiveClusters(&n, mx_gemm_pair_kernel, &cfg) != cudaSuccess) n = 0;
+        cluster_launch_config(&cfg, attr, 2, smem, nullptr);
+        if (cudaOccupancyMaxActiveClusters(&n, mx_gemm_pair_kernel<FP4>, &cfg) != cudaSuccess) n = 0;
       }
       (void)cudaGetLastError();  // a device without cluster support is not an error of this call
       capacity[dev_id] = n;
@@ -743,61 +782,93 @@ int pair_cluster_capacity(int dev_id, int *max_clusters) {
   return DTQ_OK;
 }
 
-int launch_pair(const void *a, const void *b, const void *sfa, const void *sfb, void *out, int64_t m, int64_t n, int64_t k,
-                int max_clusters, int *status, cudaStream_t st) {
+// What every launcher needs: operand pointers, sizes (k_bytes = bytes per operand row), where the status word is.
+struct GemmCall {
+  const void *a, *b, *sfa, *sfb;
+  void *out;
+  int64_t m, n, k_bytes, katoms;
+  int *status;
+  cudaStream_t st;
+};
+
+template <bool FP4>
+int launch_pair(const GemmCall &c, int max_clusters) {
   CUtensorMap map_a, map_b, map_sfa, map_sfb;
-  const int64_t katoms = ceil_div64(k / 32, 4);
-  if (int e = make_operand_map(&map_a, a, m, k, kBM)) return e;
-  if (int e = make_operand_map(&map_b, b, n, k, kPairBN / 2)) return e;
-  if (int e = make_scale_map(&map_sfa, sfa, ceil_div64(m, 128), katoms, 1)) return e;
-  if (int e = make_scale_map(&map_sfb, sfb, ceil_div64(n, 128), katoms, 2)) return e;
+  constexpr int kKAtoms = Format<FP4>::kKAtoms;
+  if (int e = make_operand_map(&map_a, c.a, c.m, c.k_bytes, kBM)) return e;
+  if (int e = make_operand_map(&map_b, c.b, c.n, c.k_bytes, kPairBN / 2)) return e;
+  if (int e = make_scale_map(&map_sfa, c.sfa, ceil_div64(c.m, 128), c.katoms, 1, kKAtoms)) return e;
+  if (int e = make_scale_map(&map_sfb, c.sfb, ceil_div64(c.n, 128), c.katoms, 2, kKAtoms)) return e;
   PairParams p;
-  p.out = static_cast<uint16_t *>(out);
-  p.M = static_cast<int>(m);
-  p.N = static_cast<int>(n);
-  p.m_pairs = static_cast<int>(ceil_div64(m, 256));
-  p.n_tiles = static_cast<int>(ceil_div64(n, kPairBN));
-  p.k_stages = static_cast<int>(ceil_div64(k, kBK));
-  p.status = status;
+  p.out = static_cast<uint16_t *>(c.out);
+  p.M = static_cast<int>(c.m);
+  p.N = static_cast<int>(c.n);
+  p.m_pairs = static_cast<int>(ceil_div64(c.m, 256));
+  p.n_tiles = static_cast<int>(ceil_div64(c.n, kPairBN));
+  p.k_stages = static_cast<int>(ceil_div64(c.k_bytes, kBK));
+  p.status = c.status;
   const int64_t tiles = int64_t(p.m_pairs) * p.n_tiles;
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * clusters);
-  cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = sizeof(PairSmem) + 1024;
-  cfg.stream = st;
+  cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, mx_gemm_pair_kernel, map_a, map_b, map_sfa, map_sfb, p));
+  cluster_launch_config(&cfg, attr, 2 * clusters, sizeof(PairSmem<FP4>) + 1024, c.st);
+  return cuda_status(cudaLaunchKernelEx(&cfg, mx_gemm_pair_kernel<FP4>, map_a, map_b, map_sfa, map_sfb, p));
 }
 
-// Launches one tile shape.  `configured` remembers, per device, that the kernel's shared-memory limit was raised.
-template <typename SH>
-int launch_shape(const void *a, const void *b, GemmParams p, int64_t m, int64_t n, int64_t k, const DeviceInfo &dev,
-                 cudaStream_t st) {
-  constexpr int kMaxDevices = 64;
-  static std::atomic<int> configured[kMaxDevices];
+// One CTA per tile, tile shape SH.
+template <typename SH, bool FP4>
+int launch_shape(const GemmCall &c, const DeviceInfo &dev) {
+  static std::atomic<int> configured[kMaxGemmDevices];
   int dev_id = 0;
   DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
-  if (dev_id < 0 || dev_id >= kMaxDevices) return DTQ_ERR_INVALID_ARGUMENT;
-  const int smem = static_cast<int>(sizeof(GemmSmem<SH>)) + 1024;
+  if (dev_id < 0 || dev_id >= kMaxGemmDevices) return DTQ_ERR_INVALID_ARGUMENT;
+  const int smem = static_cast<int>(sizeof(GemmSmem<SH, FP4>)) + 1024;
   if (!configured[dev_id].load(std::memory_order_acquire)) {  // setting the attribute twice is harmless
-    DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_gemm_kernel<SH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_gemm_kernel<SH, FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev_id].store(1, std::memory_order_release);
   }
   CUtensorMap map_a, map_b;
-  if (int e = make_operand_map(&map_a, a, m, k, kBM)) return e;
-  if (int e = make_operand_map(&map_b, b, n, k, SH::BN)) return e;
-  p.n_tiles = static_cast<int>(ceil_div64(n, SH::BN));
+  if (int e = make_operand_map(&map_a, c.a, c.m, c.k_bytes, kBM)) return e;
+  if (int e = make_operand_map(&map_b, c.b, c.n, c.k_bytes, SH::BN)) return e;
+  GemmParams p;
+  p.sfa = static_cast<const uint8_t *>(c.sfa);
+  p.sfb = static_cast<const uint8_t *>(c.sfb);
+  p.out = static_cast<uint16_t *>(c.out);
+  p.M = static_cast<int>(c.m);
+  p.N = static_cast<int>(c.n);
+  p.K = static_cast<int>(c.k_bytes);
+  p.m_tiles = static_cast<int>(ceil_div64(c.m, kBM));
+  p.n_tiles = static_cast<int>(ceil_div64(c.n, SH::BN));
+  p.k_stages = static_cast<int>(ceil_div64(c.k_bytes, kBK));
+  p.katoms = static_cast<int>(c.katoms);
+  p.n_atoms = static_cast<int>(ceil_div64(c.n, 128));
+  p.status = c.status;
   const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
   const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-  mx_gemm_kernel<SH><<<grid, kGemmThreads, smem, st>>>(map_a, map_b, p);
+  mx_gemm_kernel<SH, FP4><<<grid, kGemmThreads, smem, c.st>>>(map_a, map_b, p);
   return cuda_status(cudaGetLastError());
+}
+
+template <bool FP4>
+int launch_gemm(const GemmCall &c, int kernel, const DeviceInfo &dev) {
+  // Which kernel.  All of them are bound by what an SM can pull out of L2, so the estimate is rounds of tiles on
+  // the busiest SM times the operand bytes a CTA loads per round: 48 KB per stage for a wide tile, 32 KB for a
+  // narrow one, 32 KB for a CTA's half of an SM pair's 256 x 256 tile (which is worth a wide tile of output).
+  const int64_t m_tiles = ceil_div64(c.m, kBM);
+  const double wide = static_cast<double>(ceil_div64(m_tiles * ceil_div64(c.n, 256), dev.sm_count)) * 48.0;
+  const double narrow = static_cast<double>(ceil_div64(m_tiles * ceil_div64(c.n, 128), dev.sm_count)) * 32.0 * 1.15;
+  int dev_id = 0, max_clusters = 0;
+  DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
+  if (int e = pair_cluster_capacity<FP4>(dev_id, &max_clusters)) return e;
+  const double pair =
+      max_clusters > 0 ? static_cast<double>(ceil_div64(ceil_div64(c.m, 256) * ceil_div64(c.n, 256), max_clusters)) * 32.0 * 1.05
+                       : 1e30;
+  if (kernel == DTQ_GEMM_PAIR && max_clusters <= 0) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorNotSupported);
+  if (kernel == DTQ_GEMM_AUTO)
+    kernel = (pair <= wide && pair <= narrow) ? DTQ_GEMM_PAIR : (narrow < wide ? DTQ_GEMM_NARROW : DTQ_GEMM_WIDE);
+  if (kernel == DTQ_GEMM_PAIR) return launch_pair<FP4>(c, max_clusters);
+  if (kernel == DTQ_GEMM_NARROW) return launch_shape<NarrowShape, FP4>(c, dev);
+  return launch_shape<WideShape, FP4>(c, dev);
 }
 
 }  // namespace
@@ -808,21 +879,15 @@ extern "C" size_t dtq_mx_gemm_scale_bytes(int64_t rows, int64_t k) {
   return static_cast<size_t>((rows + 127) / 128) * static_cast<size_t>(((k + 31) / 32 + 3) / 4) * 512;
 }
 
-extern "C" int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
-                               void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
-                               void *stream) {
-  return dtq_mx_fp8_bf16_kernel(a, b, a_scales_blocked, b_scales_blocked, out_bf16, m, n, k, DTQ_GEMM_AUTO, workspace,
-                                workspace_bytes, stream);
-}
-
-extern "C" int dtq_mx_fp8_bf16_kernel(const void *a, const void *b, const void *a_scales_blocked,
-                                      const void *b_scales_blocked, void *out_bf16, int64_t m, int64_t n, int64_t k,
-                                      int kernel, void *workspace, size_t workspace_bytes, void *stream) {
+extern "C" int dtq_mx_gemm_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
+                                void *out_bf16, int64_t m, int64_t n, int64_t k, int elem_format, int kernel, void *workspace,
+                                size_t workspace_bytes, void *stream) {
   using namespace dtq;
-  if (kernel < DTQ_GEMM_AUTO || kernel > DTQ_GEMM_NARROW) return DTQ_ERR_INVALID_ARGUMENT;
   if (m < 0 || n < 0 || k < 0) return DTQ_ERR_INVALID_ARGUMENT;
+  if (elem_format != DTQ_E4M3 && elem_format != DTQ_E2M1) return DTQ_ERR_UNSUPPORTED_DTYPE;
+  if (kernel < DTQ_GEMM_AUTO || kernel > DTQ_GEMM_NARROW) return DTQ_ERR_INVALID_ARGUMENT;
   if (n % 8 != 0 || k % 32 != 0) return DTQ_ERR_SHAPE;  // 16-byte output vectors; whole MX blocks (also the TMA row pitch)
-  if (m > 0x7FFFFFFF - kBM || n > 0x7FFFFFFF - 256 || k > 0x7FFFFFFF - kBK) return DTQ_ERR_TOO_LARGE;
+  if (m > 0x7FFFFFFF - 256 || n > 0x7FFFFFFF - 256 || k > 0x7FFFFFFF - 256) return DTQ_ERR_TOO_LARGE;
   if (!workspace || workspace_bytes < sizeof(Workspace) || !aligned_to(workspace, 256)) return DTQ_ERR_WORKSPACE;
   if (m == 0 || n == 0) return DTQ_OK;
   if (!out_bf16 || !aligned_to(out_bf16, 16)) return DTQ_ERR_INVALID_ARGUMENT;
@@ -833,36 +898,31 @@ extern "C" int dtq_mx_fp8_bf16_kernel(const void *a, const void *b, const void *
     return DTQ_ERR_INVALID_ARGUMENT;
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
+  GemmCall c;
+  c.a = a;
+  c.b = b;
+  c.sfa = a_scales_blocked;
+  c.sfb = b_scales_blocked;
+  c.out = out_bf16;
+  c.m = m;
+  c.n = n;
+  c.k_bytes = elem_format == DTQ_E2M1 ? k / 2 : k;
+  c.katoms = ceil_div64(k / 32, 4);
+  c.status = &static_cast<Workspace *>(workspace)->status;
+  c.st = st;
+  return elem_format == DTQ_E2M1 ? launch_gemm<true>(c, kernel, dev) : launch_gemm<false>(c, kernel, dev);
+}
 
-  GemmParams p;
-  p.sfa = static_cast<const uint8_t *>(a_scales_blocked);
-  p.sfb = static_cast<const uint8_t *>(b_scales_blocked);
-  p.out = static_cast<uint16_t *>(out_bf16);
-  p.M = static_cast<int>(m);
-  p.N = static_cast<int>(n);
-  p.K = static_cast<int>(k);
-  p.m_tiles = static_cast<int>(ceil_div64(m, kBM));
-  p.n_tiles = 0;  // set by the launcher of the chosen tile shape
-  p.k_stages = static_cast<int>(ceil_div64(k, kBK));
-  p.katoms = static_cast<int>(ceil_div64(k / 32, 4));
-  p.n_atoms = static_cast<int>(ceil_div64(n, 128));
-  p.status = &static_cast<Workspace *>(workspace)->status;
-  // Which kernel.  All of them are bound by what an SM can pull out of L2, so the estimate is rounds of tiles on
-  // the busiest SM times the operand bytes a CTA loads per round: 48 KB per stage for a wide tile, 32 KB for a
-  // narrow one, 32 KB for a CTA's half of an SM pair's 256 x 256 tile (which is worth a wide tile of output).
-  const double wide = static_cast<double>(ceil_div64(int64_t(p.m_tiles) * ceil_div64(n, 256), dev.sm_count)) * 48.0;
-  const double narrow = static_cast<double>(ceil_div64(int64_t(p.m_tiles) * ceil_div64(n, 128), dev.sm_count)) * 32.0 * 1.15;
-  int dev_id = 0, max_clusters = 0;
-  DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
-  if (int e = pair_cluster_capacity(dev_id, &max_clusters)) return e;
-  const double pair = max_clusters > 0
-                          ? static_cast<double>(ceil_div64(ceil_div64(m, 256) * ceil_div64(n, 256), max_clusters)) * 32.0 * 1.05
-                          : 1e30;
-  if (kernel == DTQ_GEMM_PAIR && max_clusters <= 0) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorNotSupported);
-  if (kernel == DTQ_GEMM_AUTO)
-    kernel = (pair <= wide && pair <= narrow) ? DTQ_GEMM_PAIR : (narrow < wide ? DTQ_GEMM_NARROW : DTQ_GEMM_WIDE);
-  if (kernel == DTQ_GEMM_PAIR)
-    return launch_pair(a, b, a_scales_blocked, b_scales_blocked, out_bf16, m, n, k, max_clusters, p.status, st);
-  if (kernel == DTQ_GEMM_NARROW) return launch_shape<NarrowShape>(a, b, p, m, n, k, dev, st);
-  return launch_shape<WideShape>(a, b, p, m, n, k, dev, st);
+extern "C" int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
+                               void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
+                               void *stream) {
+  return dtq_mx_gemm_bf16(a, b, a_scales_blocked, b_scales_blocked, out_bf16, m, n, k, DTQ_E4M3, DTQ_GEMM_AUTO, workspace,
+                          workspace_bytes, stream);
+}
+
+extern "C" int dtq_mx_fp4_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
+                               void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
+                               void *stream) {
+  return dtq_mx_gemm_bf16(a, b, a_scales_blocked, b_scales_blocked, out_bf16, m, n, k, DTQ_E2M1, DTQ_GEMM_AUTO, workspace,
+                          workspace_bytes, stream);
 }

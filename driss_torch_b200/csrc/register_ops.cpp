@@ -310,7 +310,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> mx_fp8_quantize_with_amax(at::Ten
 
 // MXFP4: e2m1 payload packed two per byte ([M, N/2] uint8, lower index in the low nibble: the operand
 // layout of the reference's mx_fp4_bf16, which reads K as a.size(1) * 2) + E8M0 scales.
-std::tuple<at::Tensor, at::Tensor> mx_fp4_quantize(at::Tensor input) {
+std::tuple<at::Tensor, at::Tensor> mx_fp4_quantize(at::Tensor input, bool blocked) {
   TORCH_CHECK(input.is_cuda(), "Input tensor must be a CUDA tensor");
   TORCH_CHECK(input.is_contiguous(), "Input tensor must be contiguous");
   TORCH_CHECK(input.dim() == 2, "Input tensor must be 2D");
@@ -320,9 +320,17 @@ std::tuple<at::Tensor, at::Tensor> mx_fp4_quantize(at::Tensor input) {
   const int64_t m = input.size(0), n = input.size(1);
   TORCH_CHECK(n % 32 == 0, "The last dimension must be a multiple of the block size 32, but got ", n);
   at::Tensor out = at::empty({m, n / 2}, input.options().dtype(at::kByte));
-  at::Tensor scale = at::empty({m * (n / 32)}, input.options().dtype(at::kFloat8_e8m0fnu));
   c10::cuda::CUDAGuard guard(input.device());
   auto stream = c10::cuda::getCurrentCUDAStream();
+  if (blocked) {  // scales in the layout mx_fp4_bf16 takes, zero in the padding
+    at::Tensor scale = at::zeros({static_cast<int64_t>(dtq_mx_blocked_scale_bytes(m, n))}, input.options().dtype(at::kByte))
+                           .view(at::kFloat8_e8m0fnu);
+    check_status(dtq_mx_quantize_blocked(input.data_ptr(), out.data_ptr(), scale.data_ptr(), m, n, mx_in_code(in_type),
+                                         DTQ_E2M1, stream.stream()),
+                 "mx_fp4_quantize");
+    return {out, scale};
+  }
+  at::Tensor scale = at::empty({m * (n / 32)}, input.options().dtype(at::kFloat8_e8m0fnu));
   check_status(dtq_mx_quantize(input.data_ptr(), out.data_ptr(), scale.data_ptr(), m, n, mx_in_code(in_type), DTQ_E2M1,
                                stream.stream()),
                "mx_fp4_quantize");
@@ -455,6 +463,38 @@ at::Tensor mx_fp8_bf16(at::Tensor a, at::Tensor b, at::Tensor a_scale, at::Tenso
   return out;
 }
 
+// The MXFP4 GEMM (src/mx_fp8_bf16.cu:243-271): e2m1 operands packed two per byte, K = 2 * a.size(1).  The reference
+// runs no checks of its own here; the ones below are mx_fp8_bf16's applied to the packed shapes.
+at::Tensor mx_fp4_bf16(at::Tensor a, at::Tensor b, at::Tensor a_scale, at::Tensor b_scale) {
+  TORCH_CHECK(a.is_cuda(), "a must be CUDA tensor");
+  TORCH_CHECK(b.is_cuda(), "b must be CUDA tensor");
+  TORCH_CHECK(a_scale.is_cuda(), "a_scale must be CUDA tensor");
+  TORCH_CHECK(b_scale.is_cuda(), "b_scale must be CUDA tensor");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "a and b must be matrices");
+  TORCH_CHECK(a.element_size() == 1 && b.element_size() == 1, "a and b must hold two e2m1 values per byte (uint8 or float4_e2m1fn_x2)");
+  const int64_t M = a.size(0), Kb = a.size(1), K = Kb * 2, N = b.size(1);
+  TORCH_CHECK(b.size(0) == Kb, "Incompatible matrix dimensions: a is ", M, "x", Kb, " but b is ", b.size(0), "x", N, " (packed bytes)");
+  TORCH_CHECK(N % 8 == 0, "N must be a multiple of 16 but got, ", N);
+  TORCH_CHECK(K % 32 == 0, "K must be a multiple of the block size 32, but got ", K);
+  TORCH_CHECK(reinterpret_cast<std::uintptr_t>(a.data_ptr()) % 16 == 0, "Input tensor 'a' must be 16-byte aligned");
+  TORCH_CHECK(reinterpret_cast<std::uintptr_t>(b.data_ptr()) % 16 == 0, "Input tensor 'b' must be 16-byte aligned");
+  TORCH_CHECK(a_scale.numel() == static_cast<int64_t>(dtq_mx_gemm_scale_bytes(M, K)), "Expected a_scale_size to be ",
+              dtq_mx_gemm_scale_bytes(M, K), " but got ", a_scale.numel());
+  TORCH_CHECK(b_scale.numel() == static_cast<int64_t>(dtq_mx_gemm_scale_bytes(N, K)), "Expected b_scale_size to be ",
+              dtq_mx_gemm_scale_bytes(N, K), " but got ", b_scale.numel());
+  TORCH_CHECK(a_scale.element_size() == 1 && b_scale.element_size() == 1, "scales must be one byte per block (float8_e8m0fnu)");
+  TORCH_CHECK(a_scale.is_contiguous() && b_scale.is_contiguous(), "scale tensors must be contiguous");
+  TORCH_CHECK(a.stride(1) == 1 && a.stride(0) == Kb, "Input tensor 'a' must be contiguous in the K dimension (row-major)");
+  TORCH_CHECK(b.stride(0) == 1 && b.stride(1) == Kb, "Input tensor 'b' must be contiguous in the K dimension (column-major)");
+  at::Tensor out = at::empty({M, N}, a.options().dtype(at::kBFloat16));
+  c10::cuda::CUDAGuard guard(a.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_mx_fp4_bf16(a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(), out.data_ptr(), M, N, K,
+                               workspaces().get(stream), dtq_workspace_bytes(), stream.stream()),
+               "mx_fp4_bf16");
+  return out;
+}
+
 void check_device_status() { workspaces().check_all(); }
 
 }  // namespace
@@ -487,7 +527,7 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("saturated_cast_dual", c10::DispatchKey::CUDA, TORCH_FN(saturated_cast_dual));
   m.def("mx_fp8_quantize_with_amax(Tensor input) -> (Tensor, Tensor, Tensor)");
   m.impl("mx_fp8_quantize_with_amax", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_with_amax));
-  m.def("mx_fp4_quantize(Tensor input) -> (Tensor, Tensor)");
+  m.def("mx_fp4_quantize(Tensor input, bool blocked=False) -> (Tensor, Tensor)");
   m.impl("mx_fp4_quantize", c10::DispatchKey::CUDA, TORCH_FN(mx_fp4_quantize));
   m.def("mx_fp8_quantize_dual(Tensor input, bool blocked=False) -> (Tensor, Tensor, Tensor, Tensor)");
   m.impl("mx_fp8_quantize_dual", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_quantize_dual));
@@ -496,6 +536,8 @@ TORCH_LIBRARY(DrissTorch, m) {
   // the consumer GEMM, the reference's schema verbatim (src/register_ops.cpp:35-36)
   m.def("mx_fp8_bf16(Tensor a, Tensor b, Tensor a_scale, Tensor b_scale) -> Tensor");
   m.impl("mx_fp8_bf16", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_bf16));
+  m.def("mx_fp4_bf16(Tensor a, Tensor b, Tensor a_scale, Tensor b_scale) -> Tensor");  // src/register_ops.cpp:37-38
+  m.impl("mx_fp4_bf16", c10::DispatchKey::CUDA, TORCH_FN(mx_fp4_bf16));
   m.def("check_device_status() -> ()");
   m.impl("check_device_status", c10::DispatchKey::CompositeExplicitAutograd, TORCH_FN(check_device_status));
 }

@@ -261,6 +261,13 @@ int dtq_mx_fp8_quantize_amax_p2p(const void *in_bf16, void *payload, void *scale
  */
 int dtq_mx_quantize(const void *in, void *payload, void *scales_e8m0, int64_t rows, int64_t cols, int in_dtype,
                     int elem_format, void *stream);
+/*
+ * The same with the scales in the blocked layout of dtq_mx_fp8_quantize_blocked (dtq_mx_blocked_scale_bytes(rows,
+ * cols) bytes; bytes of padding rows / blocks are not written: zero the buffer first if the shape is not a
+ * multiple of (128, 128)): the operands of dtq_mx_fp4_bf16 straight from the cast.
+ */
+int dtq_mx_quantize_blocked(const void *in, void *payload, void *scales_blocked, int64_t rows, int64_t cols, int in_dtype,
+                            int elem_format, void *stream);
 
 /*
  * Both orientations from one read of a contiguous bf16 [rows, cols] matrix (rows % 32 == 0,
@@ -336,20 +343,32 @@ int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scales_blocked, 
                     void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
                     void *stream);
 /*
- * The same with the kernel named instead of chosen from the problem size (for benchmarks, and for tests that run
- * every kernel on every size; results are bit-identical between them):
+ * The MXFP4 GEMM: as dtq_mx_fp8_bf16 with e2m1 operands packed two per byte (lower index in the low nibble,
+ * what dtq_mx_quantize writes for DTQ_E2M1): a [m, k/2] bytes, b [n, k/2] bytes; k counts elements, k % 32 == 0.
+ * tcgen05.mma kind::mxf4 with one scale per 32 elements.
+ * Replaces driss_torch::mx_fp4_bf16: src/mx_fp8_bf16.cu:243-271.
+ */
+int dtq_mx_fp4_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
+                    void *out_bf16, int64_t m, int64_t n, int64_t k, void *workspace, size_t workspace_bytes,
+                    void *stream);
+
+/*
+ * Both GEMMs with the element format (DTQ_E4M3 or DTQ_E2M1) and the kernel named instead of chosen from the
+ * problem size (for benchmarks, and for tests that run every kernel on every size; the results of the kernels are
+ * bit-identical):
  *   DTQ_GEMM_PAIR    two CTAs of a cluster (an SM pair) per 256 x 256 tile, tcgen05.mma.cta_group::2: least
  *                    operand traffic per SM, what large problems use;
  *   DTQ_GEMM_WIDE    one CTA per 128 x 256 tile;
  *   DTQ_GEMM_NARROW  one CTA per 128 x 128 tile, two accumulators (epilogue under the next tile's MMAs).
+ * No reference counterpart (the reference fixes one CUTLASS tile shape, src/mx_fp8_bf16.cu:231-233).
  */
 #define DTQ_GEMM_AUTO 0
 #define DTQ_GEMM_PAIR 1
 #define DTQ_GEMM_WIDE 2
 #define DTQ_GEMM_NARROW 3
-int dtq_mx_fp8_bf16_kernel(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
-                           void *out_bf16, int64_t m, int64_t n, int64_t k, int kernel, void *workspace,
-                           size_t workspace_bytes, void *stream);
+int dtq_mx_gemm_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,
+                     void *out_bf16, int64_t m, int64_t n, int64_t k, int elem_format, int kernel, void *workspace,
+                     size_t workspace_bytes, void *stream);
 
 #ifdef __cplusplus
 }

@@ -185,3 +185,79 @@ def test_operator_checks_fake_and_repeatability():
 
     assert driss_torch.mx_fp8_bf16 is dt.mx_fp8_bf16
     dt.check_device_status()
+
+
+# ---- MXFP4 (e2m1 packed two per byte): mx_fp4_bf16 -----------------------------------------------------------------
+
+def test_oracle_fp4_against_an_independent_evaluation():
+    g = torch.Generator().manual_seed(44)
+    m, n, k = 40, 24, 192
+    a = torch.randint(0, 256, (m, k // 2), generator=g).to(torch.uint8)
+    b = torch.randint(0, 256, (n, k // 2), generator=g).to(torch.uint8)
+    sa = torch.randint(120, 134, (m, k // 32), generator=g).to(torch.uint8)
+    sb = torch.randint(120, 134, (n, k // 32), generator=g).to(torch.uint8)
+    out = qo.mx_gemm_bf16(a, b, qo.to_blocked(sa, m, k // 32), qo.to_blocked(sb, n, k // 32), fp4=True)
+    table = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], dtype=torch.float64)
+
+    def unpack(p, s, rows):
+        lo, hi = table[(p & 0xF).long()], table[(p >> 4).long()]
+        vals = torch.stack([lo, hi], dim=-1).view(rows, k)  # the lower index in the low nibble
+        return (vals.view(rows, k // 32, 32) * torch.exp2(s.double() - 127).view(rows, k // 32, 1)).view(rows, k)
+
+    want = (unpack(a, sa, m) @ unpack(b, sb, n).t()).to(torch.bfloat16)
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["pair", "wide", "narrow"])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (128, 128, 128), (256, 512, 1024), (129, 256, 384), (133, 528, 512),
+                                   (64, 8, 32), (300, 520, 96), (1024, 1024, 1024), (2560, 2048, 512), (9472, 376, 320)])
+def test_fp4_exact_against_the_oracle(m, n, k, kernel):
+    # every product of two e2m1 values is a multiple of 1/4 below 64 and the scales span a few binades, so all
+    # partial sums are exact in fp32 and the device must agree with the oracle bit for bit; K = 128, 384, 96, 320
+    # leave the second scale atom of a 256-element stage partly or wholly outside the matrix
+    from driss_torch_b200 import _cabi
+
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
+    a = torch.randint(0, 256, (m, k // 2), generator=g).to(torch.uint8)
+    b = torch.randint(0, 256, (n, k // 2), generator=g).to(torch.uint8)
+    sa = torch.randint(125, 130, (m, k // 32), generator=g).to(torch.uint8)
+    sb = torch.randint(125, 130, (n, k // 32), generator=g).to(torch.uint8)
+    sab, sbb = qo.to_blocked(sa, m, k // 32), qo.to_blocked(sb, n, k // 32)
+    key = ("fp4", m, n, k)
+    if key not in _ORACLE_CACHE:
+        _ORACLE_CACHE[key] = qo.mx_gemm_bf16(a, b, sab, sbb, fp4=True)
+    want = _ORACLE_CACHE[key]
+    got = _cabi.mx_fp4_bf16(a.cuda(), b.cuda(), sab.cuda(), sbb.cuda(), kernel=kernel).cpu()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16)), \
+        f"{(got.view(torch.int16) != want.view(torch.int16)).sum().item()} of {got.numel()} outputs differ"
+    assert _cabi.workspace_status(_cabi.workspace(torch.device("cuda", torch.cuda.current_device()))) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("size", REFERENCE_SIZES, ids=lambda s: f"{s[0]}x{s[1]}x{s[2]}")
+def test_fp4_reference_size_grid_sqnr(size):
+    # test/test_mx.py:36-67 with format "fp4": operands from the MXFP4 cast (scales straight in the blocked layout),
+    # result against a bf16 matmul of the dequantised operands, SQNR above 80 dB
+    import driss_torch_b200 as dt
+
+    m, k, n = size
+    a = torch.rand(m, k, device="cuda").to(torch.bfloat16)
+    b = torch.rand(n, k, device="cuda").to(torch.bfloat16)
+    a_data, a_scale = dt.mx_fp4_quantize(a, blocked=True)
+    b_data, b_scale = dt.mx_fp4_quantize(b, blocked=True)
+    out = dt.mx_fp4_bf16(a_data, b_data.t(), a_scale, b_scale)
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16
+    table = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], device="cuda")
+
+    def dequant(x, rows):
+        p, s = dt.mx_fp4_quantize(x)
+        vals = torch.stack([table[(p & 0xF).long()], table[(p >> 4).long()]], dim=-1).view(rows, k)
+        return (vals.view(rows, k // 32, 32) * torch.exp2(s.view(torch.uint8).float() - 127).view(rows, k // 32, 1)).view(rows, k)
+
+    out_hp = dequant(a, m).to(torch.bfloat16) @ dequant(b, n).to(torch.bfloat16).t()
+    assert _sqnr(out_hp, out) > 80, f"SQNR {_sqnr(out_hp, out)} dB"
+    # the blocked scales are the row-major ones rearranged
+    _, s_rm = dt.mx_fp4_quantize(a)
+    assert torch.equal(as_bytes(a_scale), qo.to_blocked(s_rm.cpu(), m, k // 32))
+    dt.check_device_status()
