@@ -12,6 +12,7 @@ libraries have not been built (``python driss_torch_b200/build.py``) the import 
 from __future__ import annotations
 
 from pathlib import Path
+from typing import Optional
 
 import torch
 
@@ -103,6 +104,29 @@ def mx_fp8_bf16(a: Tensor, b: Tensor, a_scale: Tensor, b_scale: Tensor) -> Tenso
     return ops.mx_fp8_bf16(a, b, a_scale, b_scale)
 
 
+def sweep_mm(
+    x: Tensor,
+    w: Tensor,
+    x_scale: Tensor,
+    w_scale: Tensor,
+    bias: Optional[Tensor],
+    out_dtype: torch.dtype,
+    use_fast_accum: bool,
+    cluster_shape_x: int,
+    cluster_shape_y: int,
+    cluster_shape_z: int,
+    transposed: bool,
+    swizzle: int,
+) -> Tensor:
+    """Row-wise scaled fp8 matrix multiplication (driss_torch/__init__.py:50-77): ``x`` [M, K] e4m3 / e5m2
+    row-major, ``w`` [K, N] e4m3 column-major, ``x_scale`` [M, 1] and ``w_scale`` [1, N] fp32 dequantisation scales
+    (the reciprocals of ``dynamic_scaled_quant_rowwise``'s), optional ``bias`` [N]; returns
+    ``bf16((acc * x_scale) * w_scale + bias)``.  The arguments after ``out_dtype`` tune the reference's Hopper
+    kernels and have no effect here."""
+    return ops.sweep_mm(x, w, x_scale, w_scale, bias, out_dtype, use_fast_accum, cluster_shape_x, cluster_shape_y,
+                        cluster_shape_z, transposed, swizzle)
+
+
 def mx_fp4_bf16(a: Tensor, b: Tensor, a_scale: Tensor, b_scale: Tensor) -> Tensor:
     """Matrix multiplication of two MXFP4 operands (e2m1 values packed two per byte, the lower index in the low
     nibble; E8M0 scales of 32 elements along K, blocked layout) (driss_torch/__init__.py:98-111): ``a`` [M, K/2]
@@ -190,6 +214,7 @@ __all__ = [
     "mx_cast",
     "mx_fp8_bf16",
     "mx_fp4_bf16",
+    "sweep_mm",
     "dynamic_scaled_quant_with_scale",
     "dynamic_scaled_quant_rowwise",
     "cast_with_amax",

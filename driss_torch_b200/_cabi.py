@@ -52,6 +52,7 @@ SIGNATURES = {
     "dtq_mx_gemm_scale_bytes": ([_i64, _i64], _sz),
     "dtq_mx_fp8_bf16": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp], _i32),
     "dtq_mx_fp4_bf16": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _sz, _vp], _i32),
+    "dtq_rowwise_fp8_bf16": ([_vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _sz, _vp], _i32),
     "dtq_mx_gemm_bf16": ([_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _sz, _vp], _i32),
     "dtq_mx_fp8_quantize_blocked": ([_vp, _vp, _vp, _i64, _i64, _vp], _i32),
 }
@@ -389,3 +390,18 @@ def mx_fp8_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=None, ws=None, ke
 def mx_fp4_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=None, ws=None, kernel="auto"):
     """The MXFP4 GEMM: packed e2m1 operands ``a`` [M, K/2], ``b_nk`` [N, K/2] (uint8), blocked E8M0 scales -> bf16."""
     return mx_fp8_bf16(a, b_nk, a_scale_blocked, b_scale_blocked, out=out, ws=ws, kernel=kernel, fp4=True)
+
+
+@_on_device_of_first_tensor
+def rowwise_fp8_bf16(a, b_nk, a_row_scale, b_row_scale, bias=None, out=None, ws=None, kernel="auto"):
+    """Row-wise scaled fp8 GEMM: ``a`` [M, K] e4m3 / e5m2, ``b_nk`` [N, K] e4m3, fp32 dequantisation scales [M] and
+    [N], optional bias [N] (fp32 or bf16) -> bf16 [M, N]."""
+    m, k = a.shape
+    n = b_nk.shape[0]
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device) if out is None else out
+    ws = workspace(a.device) if ws is None else ws
+    bias_code = 0 if bias is None or bias.dtype == torch.bfloat16 else 1
+    check(load().dtq_rowwise_fp8_bf16(a.data_ptr(), b_nk.data_ptr(), a_row_scale.data_ptr(), b_row_scale.data_ptr(), _ptr(bias),
+                                      bias_code, out.data_ptr(), m, n, k, OUT_CODE[a.dtype], GEMM_KERNELS[kernel], ws.data_ptr(),
+                                      ws.numel(), _stream()), "dtq_rowwise_fp8_bf16")
+    return out

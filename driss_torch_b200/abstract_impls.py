@@ -44,6 +44,12 @@ def mx_fp8_bf16_meta(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_
     return torch.empty((a.shape[0], b.shape[1]), dtype=torch.bfloat16, device=a.device)
 
 
+@register_fake("DrissTorch::sweep_mm")
+def sweep_mm_meta(x, w, x_scale, w_scale, bias, out_dtype, use_fast_accum, cluster_shape_x, cluster_shape_y, cluster_shape_z,
+                  transposed, swizzle):
+    return torch.empty((x.shape[0], w.shape[1]), dtype=out_dtype, device=x.device)
+
+
 @register_fake("DrissTorch::mx_fp4_bf16")
 def mx_fp4_bf16_meta(a: torch.Tensor, b: torch.Tensor, a_scale: torch.Tensor, b_scale: torch.Tensor):
     return torch.empty((a.shape[0], b.shape[1]), dtype=torch.bfloat16, device=a.device)

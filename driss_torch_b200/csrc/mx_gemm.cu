@@ -45,13 +45,22 @@ constexpr int kSfbCol = 256 + 16;          // scales of B: 4 columns per atom, u
 // elements per byte, a 128-byte stage is 256 elements = 8 MX blocks = two scale atoms along K, kind::mxf4 with
 // block32 scaling (K = 64 per instruction, which uses two consecutive scale bytes).  Either way an instruction
 // reads 32 bytes of every operand row, so the operand descriptors are the same.
-template <bool FP4>
+//
+// A third mode has no block scales at all: fp8 operands (e4m3, or e5m2 for A) through kind::f8f6f4, with one fp32
+// scale per row of A and per row of B (and an optional bias per column) applied to the fp32 accumulator in the
+// epilogue -- the row-wise scaled GEMM that consumes dtq_dynamic_scaled_quant_rowwise's scales.
+constexpr int kMxFp8 = 0, kMxFp4 = 1, kRowwise = 2;
+template <int MODE>
 struct Format {
-  static constexpr int kKAtoms = FP4 ? 2 : 1;  // scale atoms along K per stage
+  static constexpr bool kScaled = MODE != kRowwise;            // block scales travel with the operands
+  static constexpr int kKAtoms = MODE == kMxFp4 ? 2 : 1;      // scale atoms along K per stage (staging is sized for them)
   // k (0..3) = the instruction within a stage: which atom along K, and which byte (pair) of its 4-byte scale columns
-  __device__ static constexpr uint32_t k_atom(uint32_t k) { return FP4 ? k >> 1 : 0u; }
-  __device__ static constexpr uint32_t sf_id(uint32_t k) { return FP4 ? (k & 1u) * 2u : k; }
-  static constexpr uint32_t kFormatBits = FP4 ? ((1u << 7) | (1u << 10)) : 0u;  // a_format, b_format: e2m1 (kind::mxf4) or e4m3
+  __device__ static constexpr uint32_t k_atom(uint32_t k) { return MODE == kMxFp4 ? k >> 1 : 0u; }
+  __device__ static constexpr uint32_t sf_id(uint32_t k) { return MODE == kMxFp4 ? (k & 1u) * 2u : (MODE == kMxFp8 ? k : 0u); }
+  // instruction-descriptor bits besides the shape: block-scaled kinds carry the scale format (bit 23 = E8M0) and for
+  // kind::mxf4 the e2m1 operand format; kind::f8f6f4 carries the accumulator format (bits 4-5 = fp32), the operand
+  // formats come with the call (e4m3 = 0 or e5m2 = 1 in bits 7-9 / 10-12)
+  static constexpr uint32_t kFormatBits = MODE == kMxFp4 ? ((1u << 7) | (1u << 10) | (1u << 23)) : (MODE == kMxFp8 ? (1u << 23) : (1u << 4));
 };
 constexpr int kTmemCols = 512;             // allocation (power of two); columns 0..255 hold the accumulator(s)
 
@@ -70,12 +79,12 @@ using WideShape = GemmShape<256, 4, 1>;
 using NarrowShape = GemmShape<128, 6, 2>;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // a wait gives up after two seconds of wall time
 
-template <typename SH, bool FP4>
+template <typename SH, int MODE>
 struct __align__(1024) GemmSmem {
   uint8_t a[SH::STAGES][kBM * kBK];        // 16 KB per stage, 1024-byte aligned (swizzle atom = 8 rows x 128 B)
   uint8_t b[SH::STAGES][SH::BN * kBK];     // 16 or 32 KB per stage
-  uint8_t sfa[SH::STAGES][Format<FP4>::kKAtoms * 512];                  // blocked atoms of 128 rows x 4 k-blocks
-  uint8_t sfb[SH::STAGES][SH::BN / 128 * Format<FP4>::kKAtoms * 512];  // [128 tile columns][atom along K]
+  uint8_t sfa[SH::STAGES][Format<MODE>::kKAtoms * 512];                  // blocked atoms of 128 rows x 4 k-blocks
+  uint8_t sfb[SH::STAGES][SH::BN / 128 * Format<MODE>::kKAtoms * 512];  // [128 tile columns][atom along K]
   uint64_t full[SH::STAGES];
   uint64_t empty[SH::STAGES];
   uint64_t tmem_full[SH::ACC];
@@ -156,10 +165,10 @@ __device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
 // Instruction descriptor of tcgen05.mma kind::mxf8f6f4.block_scale: e4m3 x e4m3, both K-major, E8M0 scales,
 // M = 128, N = `bn`; `k` (0..3) is the byte of the 4-byte scale column that this k-block uses, for A and B.
 __device__ __forceinline__ uint32_t instr_desc(uint32_t sf_id, uint32_t bn, uint32_t m, uint32_t format_bits) {
-  return (sf_id << 4) | format_bits | ((bn >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (sf_id << 29);
+  return (sf_id << 4) | format_bits | ((bn >> 3) << 17) | ((m >> 4) << 24) | (sf_id << 29);
 }
-// One block-scaled MMA: D (tensor memory) (+)= A x B with the scales found at the two tensor-memory addresses.
-template <bool FP4, bool PAIR>
+// One MMA: D (tensor memory) (+)= A x B, block-scaled kinds with the scales found at the two tensor-memory addresses.
+template <int MODE, bool PAIR>
 __device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
                                           uint32_t sfa_tmem, uint32_t sfb_tmem) {
 #define DTQ_MMA(GROUP, KIND)                                                                                         \
@@ -168,10 +177,22 @@ __device__ __forceinline__ void issue_mma(uint32_t d_tmem, uint64_t a_desc, uint
                :                                                                                                     \
                : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)    \
                : "memory")
-  if constexpr (FP4 && PAIR) DTQ_MMA("2", "mxf4.block_scale.block32");
-  else if constexpr (FP4) DTQ_MMA("1", "mxf4.block_scale.block32");
-  else if constexpr (PAIR) DTQ_MMA("2", "mxf8f6f4.block_scale");
-  else DTQ_MMA("1", "mxf8f6f4.block_scale");
+  if constexpr (MODE == kMxFp4 && PAIR) DTQ_MMA("2", "mxf4.block_scale.block32");
+  else if constexpr (MODE == kMxFp4) DTQ_MMA("1", "mxf4.block_scale.block32");
+  else if constexpr (MODE == kMxFp8 && PAIR) DTQ_MMA("2", "mxf8f6f4.block_scale");
+  else if constexpr (MODE == kMxFp8) DTQ_MMA("1", "mxf8f6f4.block_scale");
+  else if constexpr (PAIR)  // no block scales; the braces hold the (unused) mask of output lanes to leave alone
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                 :
+                 : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+                 : "memory");
+  else
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 :
+                 : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+                 : "memory");
 #undef DTQ_MMA
 }
 // One scale atom, shared memory -> 4 tensor-memory columns (32 rows x 16 bytes, replicated to the four lane quadrants).
@@ -209,23 +230,50 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   *nt = idx / rows;
 }
 
+// The row-wise mode's epilogue: out = bf16(fp32(fp32(acc * row_scale[m]) * col_scale[n]) + bias[n]), every step rounded
+// to fp32 (src/scaled_mm_kernels/f8f8bf16_rowwise_kernel.h:151-175: Multiply(WScale, Multiply(XScale, Acc)), Add(Bias), Cast).
+struct RowwiseEpilogue {
+  const float *row_scale;  // [M]
+  const float *col_scale;  // [N]
+  const void *bias;        // [N] fp32 or bf16, or null
+  int bias_is_bf16;
+  uint32_t operand_format_bits;  // a_format << 7 | b_format << 10 (e4m3 = 0, e5m2 = 1)
+};
+// 32 consecutive accumulator columns of one row (fp32 bit patterns) through the row-wise epilogue, in place.
+__device__ __forceinline__ void apply_rowwise(uint32_t (&v)[32], const RowwiseEpilogue &e, int64_t row, int64_t col0, int M, int N) {
+  const float xs = row < M ? __ldg(e.row_scale + row) : 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int64_t col = col0 + i;
+    float f = 0.0f;
+    if (col < N) {
+      f = __fmul_rn(__fmul_rn(__uint_as_float(v[i]), xs), __ldg(e.col_scale + col));
+      if (e.bias)
+        f = __fadd_rn(f, e.bias_is_bf16 ? __uint_as_float(uint32_t(__ldg(static_cast<const uint16_t *>(e.bias) + col)) << 16)
+                                        : __ldg(static_cast<const float *>(e.bias) + col));
+    }
+    v[i] = __float_as_uint(f);
+  }
+}
+
 struct GemmParams {
   const uint8_t *sfa;  // blocked scales of A: atoms [ceil(M/128)][katoms] of 512 bytes
   const uint8_t *sfb;  // blocked scales of B: atoms [ceil(N/128)][katoms]
+  RowwiseEpilogue rowwise;
   uint16_t *out;       // bf16 [M, N]
   int M, N, K;
   int m_tiles, n_tiles, k_stages, katoms, n_atoms;
   int *status;
 };
 
-template <typename SH, bool FP4>
+template <typename SH, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
   constexpr int kBN = SH::BN, kStagesG = SH::STAGES, kAcc = SH::ACC, kAtomsB = SH::BN / 128;
-  constexpr int kKAtoms = Format<FP4>::kKAtoms;
+  constexpr int kKAtoms = Format<MODE>::kKAtoms;
   extern __shared__ unsigned char smem_raw[];
-  GemmSmem<SH, FP4> &sm =
-      *reinterpret_cast<GemmSmem<SH, FP4> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
+  GemmSmem<SH, MODE> &sm =
+      *reinterpret_cast<GemmSmem<SH, MODE> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *abort = &sm.abort;
 
@@ -272,15 +320,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             ok = false;
             break;
           }
-          const int atoms_b = min(kAtomsB, p.n_atoms - nt * kAtomsB);
-          const unsigned sf_bytes = 512u * min(kKAtoms, p.katoms - ks * kKAtoms);  // the atoms along K are adjacent in memory
-          mbar_expect_tx(&sm.full[s], kBM * kBK + kBN * kBK + sf_bytes * (1 + atoms_b));
+          const int atoms_b = Format<MODE>::kScaled ? min(kAtomsB, p.n_atoms - nt * kAtomsB) : 0;
+          // the atoms along K are adjacent in memory
+          const unsigned sf_bytes = Format<MODE>::kScaled ? 512u * min(kKAtoms, p.katoms - ks * kKAtoms) : 0u;
+          mbar_expect_tx(&sm.full[s], kBM * kBK + kBN * kBK + (Format<MODE>::kScaled ? sf_bytes * (1 + atoms_b) : 0u));
           tma_load_2d(sm.a[s], &map_a, ks * kBK, mt * kBM, &sm.full[s]);
           tma_load_2d(sm.b[s], &map_b, ks * kBK, nt * kBN, &sm.full[s]);
-          bulk_load_1d(sm.sfa[s], p.sfa + (int64_t(mt) * p.katoms + ks * kKAtoms) * 512, sf_bytes, &sm.full[s]);
-          for (int h = 0; h < atoms_b; ++h)
-            bulk_load_1d(sm.sfb[s] + h * kKAtoms * 512, p.sfb + (int64_t(nt * kAtomsB + h) * p.katoms + ks * kKAtoms) * 512,
-                         sf_bytes, &sm.full[s]);
+          if constexpr (Format<MODE>::kScaled) {
+            bulk_load_1d(sm.sfa[s], p.sfa + (int64_t(mt) * p.katoms + ks * kKAtoms) * 512, sf_bytes, &sm.full[s]);
+            for (int h = 0; h < atoms_b; ++h)
+              bulk_load_1d(sm.sfb[s] + h * kKAtoms * 512, p.sfb + (int64_t(nt * kAtomsB + h) * p.katoms + ks * kKAtoms) * 512,
+                           sf_bytes, &sm.full[s]);
+          }
         }
       }
       if (!ok) {
@@ -316,20 +367,22 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tmem_fence_after();
           // this stage's scales: shared memory -> tensor memory, ordered before the MMAs below.  Tensor-memory
           // columns: A's atom j along K at kSfaCol + 4 j; B's at kSfbCol + j * 4 kAtomsB + 4 h (h = 128 tile columns)
+          if constexpr (Format<MODE>::kScaled) {
 #pragma unroll
-          for (int j = 0; j < kKAtoms; ++j) {
-            copy_scale_atom<false>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[s] + j * 512));
+            for (int j = 0; j < kKAtoms; ++j) {
+              copy_scale_atom<false>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[s] + j * 512));
 #pragma unroll
-            for (int h = 0; h < kAtomsB; ++h)
-              copy_scale_atom<false>(tmem + kSfbCol + j * 4 * kAtomsB + 4 * h, smem_addr(sm.sfb[s] + (h * kKAtoms + j) * 512));
+              for (int h = 0; h < kAtomsB; ++h)
+                copy_scale_atom<false>(tmem + kSfbCol + j * 4 * kAtomsB + 4 * h, smem_addr(sm.sfb[s] + (h * kKAtoms + j) * 512));
+            }
           }
           const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {  // four instructions of 32 operand bytes inside the 128-byte swizzle span
             const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
-            const uint32_t j = Format<FP4>::k_atom(k), id = Format<FP4>::sf_id(k);
-            issue_mma<FP4, false>(d_tmem, operand_desc(a_addr + k * 32), operand_desc(b_addr + k * 32),
-                                  instr_desc(id, kBN, kBM, Format<FP4>::kFormatBits), accumulate,
+            const uint32_t j = Format<MODE>::k_atom(k), id = Format<MODE>::sf_id(k);
+            issue_mma<MODE, false>(d_tmem, operand_desc(a_addr + k * 32), operand_desc(b_addr + k * 32),
+                                  instr_desc(id, kBN, kBM, Format<MODE>::kFormatBits | p.rowwise.operand_format_bits), accumulate,
                                   (tmem + kSfaCol + 4 * j) | (id << 30), (tmem + kSfbCol + j * 4 * kAtomsB) | (id << 30));
           }
           umma_commit(&sm.empty[s]);  // the stage is free once these MMAs have read it
@@ -374,6 +427,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if constexpr (MODE == kRowwise)
+          apply_rowwise(v, p.rowwise, row, int64_t(nt) * kBN + half * kHalfCols + c * 32, p.M, p.N);
 #pragma unroll
         for (int i = 0; i < 16; ++i) packed[c][i] = pack_bf16(v[2 * i], v[2 * i + 1]);
       }
@@ -433,12 +488,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 constexpr int kPairStages = 6;
 constexpr int kPairBN = 256;  // tile columns; each CTA holds kPairBN / 2 rows of B
 
-template <bool FP4>
+template <int MODE>
 struct __align__(1024) PairSmem {
   uint8_t a[kPairStages][kBM * kBK];             // this CTA's 128 rows of A
   uint8_t b[kPairStages][kPairBN / 2 * kBK];     // this CTA's 128 of the tile's 256 rows of B
-  uint8_t sfa[kPairStages][Format<FP4>::kKAtoms * 512];      // scales of this CTA's 128 rows of A
-  uint8_t sfb[kPairStages][2 * Format<FP4>::kKAtoms * 512];  // scales of all 256 rows of B: [128 columns][atom along K]
+  uint8_t sfa[kPairStages][Format<MODE>::kKAtoms * 512];      // scales of this CTA's 128 rows of A
+  uint8_t sfb[kPairStages][2 * Format<MODE>::kKAtoms * 512];  // scales of all 256 rows of B: [128 columns][atom along K]
   uint64_t full[kPairStages];                    // used in the leader CTA only
   uint64_t empty[kPairStages];
   uint64_t tmem_full;
@@ -488,19 +543,20 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
 }
 
 struct PairParams {
+  RowwiseEpilogue rowwise;
   uint16_t *out;  // bf16 [M, N]
   int M, N;
   int m_pairs, n_tiles, k_stages;  // 256-row tile rows, 256-column tile columns, 128-byte K stages
   int *status;
 };
 
-template <bool FP4>
+template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, PairParams p) {
-  constexpr int kKAtoms = Format<FP4>::kKAtoms;
+  constexpr int kKAtoms = Format<MODE>::kKAtoms;
   extern __shared__ unsigned char smem_raw[];
-  PairSmem<FP4> &sm = *reinterpret_cast<PairSmem<FP4> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
+  PairSmem<MODE> &sm = *reinterpret_cast<PairSmem<MODE> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const bool leader = rank == 0;
@@ -548,11 +604,14 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             break;
           }
           const uint32_t bar = map_to_cta(smem_addr(&sm.full[s]), 0);  // the leader's barrier
-          if (leader) mbar_expect_tx(&sm.full[s], 2 * (kBM * kBK + kPairBN / 2 * kBK + 3 * kKAtoms * 512));
+          if (leader)
+            mbar_expect_tx(&sm.full[s], 2 * (kBM * kBK + kPairBN / 2 * kBK + (Format<MODE>::kScaled ? 3 * kKAtoms * 512 : 0)));
           tma_pair_load_2d(sm.a[s], &map_a, ks * kBK, mp * 256 + int(rank) * kBM, bar);
           tma_pair_load_2d(sm.b[s], &map_b, ks * kBK, nt * kPairBN + int(rank) * (kPairBN / 2), bar);
-          tma_pair_load_3d(sm.sfa[s], &map_sfa, 0, ks * kKAtoms, mp * 2 + int(rank), bar);
-          tma_pair_load_3d(sm.sfb[s], &map_sfb, 0, ks * kKAtoms, nt * 2, bar);
+          if constexpr (Format<MODE>::kScaled) {
+            tma_pair_load_3d(sm.sfa[s], &map_sfa, 0, ks * kKAtoms, mp * 2 + int(rank), bar);
+            tma_pair_load_3d(sm.sfb[s], &map_sfb, 0, ks * kKAtoms, nt * 2, bar);
+          }
         }
       }
       if (!ok) {
@@ -582,20 +641,22 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             break;
           }
           tmem_fence_after();
+          if constexpr (Format<MODE>::kScaled) {
 #pragma unroll
-          for (int j = 0; j < kKAtoms; ++j) {  // each CTA's shared memory -> that CTA's tensor memory, columns as above
-            copy_scale_atom<true>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[s] + j * 512));
+            for (int j = 0; j < kKAtoms; ++j) {  // each CTA's shared memory -> that CTA's tensor memory, columns as above
+              copy_scale_atom<true>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[s] + j * 512));
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
-              copy_scale_atom<true>(tmem + kSfbCol + j * 8 + 4 * h, smem_addr(sm.sfb[s] + (h * kKAtoms + j) * 512));
+              for (int h = 0; h < 2; ++h)
+                copy_scale_atom<true>(tmem + kSfbCol + j * 8 + 4 * h, smem_addr(sm.sfb[s] + (h * kKAtoms + j) * 512));
+            }
           }
           const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {
             const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
-            const uint32_t j = Format<FP4>::k_atom(k), id = Format<FP4>::sf_id(k);
-            issue_mma<FP4, true>(tmem, operand_desc(a_addr + k * 32), operand_desc(b_addr + k * 32),
-                                 instr_desc(id, kPairBN, 256, Format<FP4>::kFormatBits), accumulate,
+            const uint32_t j = Format<MODE>::k_atom(k), id = Format<MODE>::sf_id(k);
+            issue_mma<MODE, true>(tmem, operand_desc(a_addr + k * 32), operand_desc(b_addr + k * 32),
+                                 instr_desc(id, kPairBN, 256, Format<MODE>::kFormatBits | p.rowwise.operand_format_bits), accumulate,
                                  (tmem + kSfaCol + 4 * j) | (id << 30), (tmem + kSfbCol + j * 8) | (id << 30));
           }
           // the stage is free in both CTAs once these MMAs have read it
@@ -648,6 +709,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if constexpr (MODE == kRowwise) apply_rowwise(v, p.rowwise, row, int64_t(nt) * kPairBN + half * 128 + c * 32, p.M, p.N);
 #pragma unroll
         for (int i = 0; i < 16; ++i) packed[c][i] = pack_bf16(v[2 * i], v[2 * i + 1]);
       }
@@ -756,7 +818,7 @@ void cluster_launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, i
 
 // The SM-pair kernel: clusters of two CTAs, as many as the device can hold at once (at most one CTA per SM).
 // *max_clusters (cached per device and format) is 0 where cluster launches of this kernel are not possible.
-template <bool FP4>
+template <int MODE>
 int pair_cluster_capacity(int dev_id, int *max_clusters) {
   static std::atomic<int> ready[kMaxGemmDevices];
   static int capacity[kMaxGemmDevices];
@@ -765,13 +827,13 @@ int pair_cluster_capacity(int dev_id, int *max_clusters) {
     static std::mutex mutex;
     std::lock_guard<std::mutex> lock(mutex);
     if (!ready[dev_id].load(std::memory_order_relaxed)) {
-      const int smem = static_cast<int>(sizeof(PairSmem<FP4>)) + 1024;
+      const int smem = static_cast<int>(sizeof(PairSmem<MODE>)) + 1024;
       int n = 0;
-      if (cudaFuncSetAttribute(mx_gemm_pair_kernel<FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
+      if (cudaFuncSetAttribute(mx_gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];
         cluster_launch_config(&cfg, attr, 2, smem, nullptr);
-        if (cudaOccupancyMaxActiveClusters(&n, mx_gemm_pair_kernel<FP4>, &cfg) != cudaSuccess) n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, mx_gemm_pair_kernel<MODE>, &cfg) != cudaSuccess) n = 0;
       }
       (void)cudaGetLastError();  // a device without cluster support is not an error of this call
       capacity[dev_id] = n;
@@ -784,6 +846,7 @@ int pair_cluster_capacity(int dev_id, int *max_clusters) {
 
 // What every launcher needs: operand pointers, sizes (k_bytes = bytes per operand row), where the status word is.
 struct GemmCall {
+  RowwiseEpilogue rowwise;  // all zero for the block-scaled modes
   const void *a, *b, *sfa, *sfb;
   void *out;
   int64_t m, n, k_bytes, katoms;
@@ -791,15 +854,21 @@ struct GemmCall {
   cudaStream_t st;
 };
 
-template <bool FP4>
+template <int MODE>
 int launch_pair(const GemmCall &c, int max_clusters) {
   CUtensorMap map_a, map_b, map_sfa, map_sfb;
-  constexpr int kKAtoms = Format<FP4>::kKAtoms;
+  constexpr int kKAtoms = Format<MODE>::kKAtoms;
   if (int e = make_operand_map(&map_a, c.a, c.m, c.k_bytes, kBM)) return e;
   if (int e = make_operand_map(&map_b, c.b, c.n, c.k_bytes, kPairBN / 2)) return e;
-  if (int e = make_scale_map(&map_sfa, c.sfa, ceil_div64(c.m, 128), c.katoms, 1, kKAtoms)) return e;
-  if (int e = make_scale_map(&map_sfb, c.sfb, ceil_div64(c.n, 128), c.katoms, 2, kKAtoms)) return e;
+  if constexpr (Format<MODE>::kScaled) {
+    if (int e = make_scale_map(&map_sfa, c.sfa, ceil_div64(c.m, 128), c.katoms, 1, kKAtoms)) return e;
+    if (int e = make_scale_map(&map_sfb, c.sfb, ceil_div64(c.n, 128), c.katoms, 2, kKAtoms)) return e;
+  } else {  // never dereferenced by the kernel
+    map_sfa = map_a;
+    map_sfb = map_a;
+  }
   PairParams p;
+  p.rowwise = c.rowwise;
   p.out = static_cast<uint16_t *>(c.out);
   p.M = static_cast<int>(c.m);
   p.N = static_cast<int>(c.n);
@@ -811,26 +880,27 @@ int launch_pair(const GemmCall &c, int max_clusters) {
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   cudaLaunchConfig_t cfg;
   cudaLaunchAttribute attr[1];
-  cluster_launch_config(&cfg, attr, 2 * clusters, sizeof(PairSmem<FP4>) + 1024, c.st);
-  return cuda_status(cudaLaunchKernelEx(&cfg, mx_gemm_pair_kernel<FP4>, map_a, map_b, map_sfa, map_sfb, p));
+  cluster_launch_config(&cfg, attr, 2 * clusters, sizeof(PairSmem<MODE>) + 1024, c.st);
+  return cuda_status(cudaLaunchKernelEx(&cfg, mx_gemm_pair_kernel<MODE>, map_a, map_b, map_sfa, map_sfb, p));
 }
 
 // One CTA per tile, tile shape SH.
-template <typename SH, bool FP4>
+template <typename SH, int MODE>
 int launch_shape(const GemmCall &c, const DeviceInfo &dev) {
   static std::atomic<int> configured[kMaxGemmDevices];
   int dev_id = 0;
   DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
   if (dev_id < 0 || dev_id >= kMaxGemmDevices) return DTQ_ERR_INVALID_ARGUMENT;
-  const int smem = static_cast<int>(sizeof(GemmSmem<SH, FP4>)) + 1024;
+  const int smem = static_cast<int>(sizeof(GemmSmem<SH, MODE>)) + 1024;
   if (!configured[dev_id].load(std::memory_order_acquire)) {  // setting the attribute twice is harmless
-    DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_gemm_kernel<SH, FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_gemm_kernel<SH, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev_id].store(1, std::memory_order_release);
   }
   CUtensorMap map_a, map_b;
   if (int e = make_operand_map(&map_a, c.a, c.m, c.k_bytes, kBM)) return e;
   if (int e = make_operand_map(&map_b, c.b, c.n, c.k_bytes, SH::BN)) return e;
   GemmParams p;
+  p.rowwise = c.rowwise;
   p.sfa = static_cast<const uint8_t *>(c.sfa);
   p.sfb = static_cast<const uint8_t *>(c.sfb);
   p.out = static_cast<uint16_t *>(c.out);
@@ -845,11 +915,11 @@ int launch_shape(const GemmCall &c, const DeviceInfo &dev) {
   p.status = c.status;
   const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
   const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-  mx_gemm_kernel<SH, FP4><<<grid, kGemmThreads, smem, c.st>>>(map_a, map_b, p);
+  mx_gemm_kernel<SH, MODE><<<grid, kGemmThreads, smem, c.st>>>(map_a, map_b, p);
   return cuda_status(cudaGetLastError());
 }
 
-template <bool FP4>
+template <int MODE>
 int launch_gemm(const GemmCall &c, int kernel, const DeviceInfo &dev) {
   // Which kernel.  All of them are bound by what an SM can pull out of L2, so the estimate is rounds of tiles on
   // the busiest SM times the operand bytes a CTA loads per round: 48 KB per stage for a wide tile, 32 KB for a
@@ -859,16 +929,16 @@ int launch_gemm(const GemmCall &c, int kernel, const DeviceInfo &dev) {
   const double narrow = static_cast<double>(ceil_div64(m_tiles * ceil_div64(c.n, 128), dev.sm_count)) * 32.0 * 1.15;
   int dev_id = 0, max_clusters = 0;
   DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
-  if (int e = pair_cluster_capacity<FP4>(dev_id, &max_clusters)) return e;
+  if (int e = pair_cluster_capacity<MODE>(dev_id, &max_clusters)) return e;
   const double pair =
       max_clusters > 0 ? static_cast<double>(ceil_div64(ceil_div64(c.m, 256) * ceil_div64(c.n, 256), max_clusters)) * 32.0 * 1.05
                        : 1e30;
   if (kernel == DTQ_GEMM_PAIR && max_clusters <= 0) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorNotSupported);
   if (kernel == DTQ_GEMM_AUTO)
     kernel = (pair <= wide && pair <= narrow) ? DTQ_GEMM_PAIR : (narrow < wide ? DTQ_GEMM_NARROW : DTQ_GEMM_WIDE);
-  if (kernel == DTQ_GEMM_PAIR) return launch_pair<FP4>(c, max_clusters);
-  if (kernel == DTQ_GEMM_NARROW) return launch_shape<NarrowShape, FP4>(c, dev);
-  return launch_shape<WideShape, FP4>(c, dev);
+  if (kernel == DTQ_GEMM_PAIR) return launch_pair<MODE>(c, max_clusters);
+  if (kernel == DTQ_GEMM_NARROW) return launch_shape<NarrowShape, MODE>(c, dev);
+  return launch_shape<WideShape, MODE>(c, dev);
 }
 
 }  // namespace
@@ -899,6 +969,7 @@ extern "C" int dtq_mx_gemm_bf16(const void *a, const void *b, const void *a_scal
   DeviceInfo dev;
   if (int e = current_device_info(&dev)) return e;
   GemmCall c;
+  c.rowwise = RowwiseEpilogue{};
   c.a = a;
   c.b = b;
   c.sfa = a_scales_blocked;
@@ -910,7 +981,43 @@ extern "C" int dtq_mx_gemm_bf16(const void *a, const void *b, const void *a_scal
   c.katoms = ceil_div64(k / 32, 4);
   c.status = &static_cast<Workspace *>(workspace)->status;
   c.st = st;
-  return elem_format == DTQ_E2M1 ? launch_gemm<true>(c, kernel, dev) : launch_gemm<false>(c, kernel, dev);
+  return elem_format == DTQ_E2M1 ? launch_gemm<kMxFp4>(c, kernel, dev) : launch_gemm<kMxFp8>(c, kernel, dev);
+}
+
+extern "C" int dtq_rowwise_fp8_bf16(const void *a, const void *b, const float *a_row_scale, const float *b_row_scale,
+                                    const void *bias, int bias_dtype, void *out_bf16, int64_t m, int64_t n, int64_t k,
+                                    int a_format, int kernel, void *workspace, size_t workspace_bytes, void *stream) {
+  using namespace dtq;
+  if (m < 0 || n < 0 || k < 0) return DTQ_ERR_INVALID_ARGUMENT;
+  if (a_format != DTQ_E4M3 && a_format != DTQ_E5M2) return DTQ_ERR_UNSUPPORTED_DTYPE;
+  if (bias && bias_dtype != DTQ_F32 && bias_dtype != DTQ_BF16) return DTQ_ERR_UNSUPPORTED_DTYPE;
+  if (kernel < DTQ_GEMM_AUTO || kernel > DTQ_GEMM_NARROW) return DTQ_ERR_INVALID_ARGUMENT;
+  if (n % 8 != 0 || k % 16 != 0) return DTQ_ERR_SHAPE;  // 16-byte output vectors; 16-byte operand row pitch (TMA)
+  if (m > 0x7FFFFFFF - 256 || n > 0x7FFFFFFF - 256 || k > 0x7FFFFFFF - 256) return DTQ_ERR_TOO_LARGE;
+  if (!workspace || workspace_bytes < sizeof(Workspace) || !aligned_to(workspace, 256)) return DTQ_ERR_WORKSPACE;
+  if (m == 0 || n == 0) return DTQ_OK;
+  if (!out_bf16 || !aligned_to(out_bf16, 16) || !a_row_scale || !b_row_scale) return DTQ_ERR_INVALID_ARGUMENT;
+  if (k > 0 && (!a || !b || !aligned_to(a, 16) || !aligned_to(b, 16))) return DTQ_ERR_INVALID_ARGUMENT;
+  DeviceInfo dev;
+  if (int e = current_device_info(&dev)) return e;
+  GemmCall c;
+  c.rowwise.row_scale = a_row_scale;
+  c.rowwise.col_scale = b_row_scale;
+  c.rowwise.bias = bias;
+  c.rowwise.bias_is_bf16 = bias_dtype == DTQ_BF16;
+  c.rowwise.operand_format_bits = a_format == DTQ_E5M2 ? (1u << 7) : 0u;
+  c.a = a;
+  c.b = b;
+  c.sfa = nullptr;
+  c.sfb = nullptr;
+  c.out = out_bf16;
+  c.m = m;
+  c.n = n;
+  c.k_bytes = k;
+  c.katoms = 0;
+  c.status = &static_cast<Workspace *>(workspace)->status;
+  c.st = static_cast<cudaStream_t>(stream);
+  return launch_gemm<kRowwise>(c, kernel, dev);
 }
 
 extern "C" int dtq_mx_fp8_bf16(const void *a, const void *b, const void *a_scales_blocked, const void *b_scales_blocked,

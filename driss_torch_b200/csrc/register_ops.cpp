@@ -17,6 +17,7 @@
 
 #include <cstdint>
 #include <mutex>
+#include <optional>
 #include <tuple>
 #include <unordered_map>
 
@@ -495,6 +496,46 @@ at::Tensor mx_fp4_bf16(at::Tensor a, at::Tensor b, at::Tensor a_scale, at::Tenso
   return out;
 }
 
+// The row-wise scaled fp8 GEMM under the reference's name and schema; checks as src/sweep_mm.cu:11-58.
+at::Tensor sweep_mm(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor w_scale, std::optional<at::Tensor> bias,
+                    at::ScalarType out_dtype, bool use_fast_accum, int64_t cluster_shape_x, int64_t cluster_shape_y,
+                    int64_t cluster_shape_z, bool transposed, int64_t swizzle) {
+  // tuning arguments of the reference's CUTLASS kernels (no effect on the result): accepted, not used
+  (void)use_fast_accum, (void)cluster_shape_x, (void)cluster_shape_y, (void)cluster_shape_z, (void)transposed, (void)swizzle;
+  TORCH_CHECK(XQ.is_cuda());
+  TORCH_CHECK(XQ.device() == WQ.device() && x_scale.device() == XQ.device() && w_scale.device() == WQ.device());
+  TORCH_CHECK(XQ.scalar_type() == at::kFloat8_e4m3fn || XQ.scalar_type() == at::kFloat8_e5m2);
+  TORCH_CHECK(WQ.scalar_type() == at::kFloat8_e4m3fn);
+  TORCH_CHECK(x_scale.scalar_type() == at::kFloat && w_scale.scalar_type() == at::kFloat);
+  TORCH_CHECK(out_dtype == at::kBFloat16, "out_dtype must be bfloat16");
+  TORCH_CHECK(XQ.dim() == 2 && WQ.dim() == 2 && XQ.size(1) == WQ.size(0));
+  const int64_t M = XQ.size(0), K = XQ.size(1), N = WQ.size(1);
+  TORCH_CHECK(x_scale.dim() == 2 && w_scale.dim() == 2);
+  TORCH_CHECK(x_scale.size(0) == M && x_scale.size(1) == 1);
+  TORCH_CHECK(w_scale.size(0) == 1 && w_scale.size(1) == N);
+  TORCH_CHECK(XQ.stride(1) == 1 && XQ.stride(0) == K, "x must be row-major and dense");
+  TORCH_CHECK(WQ.stride(0) == 1 && WQ.stride(1) == K, "w must be column-major and dense");
+  TORCH_CHECK(x_scale.stride(0) == 1 && w_scale.stride(1) == 1);
+  TORCH_CHECK(N % 8 == 0 && K % 16 == 0, "N must be a multiple of 8 and K of 16");
+  const void *bias_ptr = nullptr;
+  int bias_code = DTQ_F32;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->device() == WQ.device());
+    TORCH_CHECK(bias->scalar_type() == at::kFloat || bias->scalar_type() == at::kBFloat16);
+    TORCH_CHECK(bias->dim() == 1 && bias->size(0) == N && bias->stride(0) == 1);
+    bias_ptr = bias->data_ptr();
+    bias_code = bias->scalar_type() == at::kBFloat16 ? DTQ_BF16 : DTQ_F32;
+  }
+  at::Tensor out = at::empty({M, N}, XQ.options().dtype(out_dtype));
+  c10::cuda::CUDAGuard guard(XQ.device());
+  auto stream = c10::cuda::getCurrentCUDAStream();
+  check_status(dtq_rowwise_fp8_bf16(XQ.data_ptr(), WQ.data_ptr(), x_scale.data_ptr<float>(), w_scale.data_ptr<float>(), bias_ptr,
+                                    bias_code, out.data_ptr(), M, N, K, out_code(XQ.scalar_type()), DTQ_GEMM_AUTO,
+                                    workspaces().get(stream), dtq_workspace_bytes(), stream.stream()),
+               "sweep_mm");
+  return out;
+}
+
 void check_device_status() { workspaces().check_all(); }
 
 }  // namespace
@@ -538,6 +579,9 @@ TORCH_LIBRARY(DrissTorch, m) {
   m.impl("mx_fp8_bf16", c10::DispatchKey::CUDA, TORCH_FN(mx_fp8_bf16));
   m.def("mx_fp4_bf16(Tensor a, Tensor b, Tensor a_scale, Tensor b_scale) -> Tensor");  // src/register_ops.cpp:37-38
   m.impl("mx_fp4_bf16", c10::DispatchKey::CUDA, TORCH_FN(mx_fp4_bf16));
+  // src/register_ops.cpp:32-33
+  m.def("sweep_mm(Tensor x, Tensor w, Tensor x_scale, Tensor w_scale, Tensor? bias , ScalarType out_dtype, bool use_fast_accum, int cluster_shape_x, int cluster_shape_y, int cluster_shape_z, bool transposed, int swizzle) -> Tensor");
+  m.impl("sweep_mm", c10::DispatchKey::CUDA, TORCH_FN(sweep_mm));
   m.def("check_device_status() -> ()");
   m.impl("check_device_status", c10::DispatchKey::CompositeExplicitAutograd, TORCH_FN(check_device_status));
 }

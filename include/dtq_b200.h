@@ -370,6 +370,22 @@ int dtq_mx_gemm_bf16(const void *a, const void *b, const void *a_scales_blocked,
                      void *out_bf16, int64_t m, int64_t n, int64_t k, int elem_format, int kernel, void *workspace,
                      size_t workspace_bytes, void *stream);
 
+/*
+ * Row-wise scaled fp8 GEMM, the consumer of dtq_dynamic_scaled_quant_rowwise's scales:
+ *   out[m, n] = bf16( fp32( fp32(acc[m, n] * a_row_scale[m]) * b_row_scale[n] ) + bias[n] ),
+ *   acc[m, n] = sum_k a[m, k] * b[n, k] in fp32 on the tensor cores (tcgen05.mma kind::f8f6f4, no block scales);
+ *   a [m, k] e4m3 or e5m2 bytes (a_format), row-major; b [n, k] e4m3 bytes, row-major -- the memory of the
+ *   reference's column-major [k, n] operand; a_row_scale [m], b_row_scale [n] fp32 (the DEQUANTISATION scales:
+ *   reciprocals of the quantisation scales); bias [n] fp32 or bf16 (bias_dtype DTQ_F32 / DTQ_BF16) or NULL;
+ *   n % 8 == 0, k % 16 == 0; `kernel` as for dtq_mx_gemm_bf16.
+ * Replaces driss_torch::sweep_mm (src/sweep_mm.cu:11-88) and its CUTLASS Sm90 kernels
+ * (src/scaled_mm_kernels/f8f8bf16_rowwise_kernel.h:101-280, epilogue :151-175), which exist for Hopper only; their
+ * tuning arguments (fast accumulation, cluster shape, transposition, swizzle) have no counterpart here.
+ */
+int dtq_rowwise_fp8_bf16(const void *a, const void *b, const float *a_row_scale, const float *b_row_scale, const void *bias,
+                         int bias_dtype, void *out_bf16, int64_t m, int64_t n, int64_t k, int a_format, int kernel,
+                         void *workspace, size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

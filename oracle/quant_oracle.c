@@ -369,6 +369,37 @@ void oracle_mx_gemm_bf16(const uint8_t *a, const uint8_t *b, const uint8_t *sa_b
   }
 }
 
+/* ---- Row-wise scaled fp8 GEMM (the consumer of the row-wise quantisation scales).
+ * out[m,n] = bf16( fp32( fp32(acc * xs[m]) * ws[n] ) + bias[n] ), acc = sum_k A[m,k] B[n,k] accumulated in fp32 on the
+ * tensor cores: the epilogue tree of the reference's CUTLASS kernel, Cast(Add(Bias, Multiply(WScale, Multiply(XScale,
+ * Acc)))) with fp32 compute (src/scaled_mm_kernels/f8f8bf16_rowwise_kernel.h:151-175), operands A e4m3 or e5m2, B e4m3
+ * (src/sweep_mm.cu:20-21).  The sum is formed exactly in double and rounded to fp32 once: bit-exact with the device
+ * when every partial sum is representable in fp32, as for the block-scaled GEMM above. */
+static double e5m2_to_f64(uint8_t b) {
+  const int sign = b >> 7, be = (b >> 2) & 0x1F, man = b & 3;
+  double v;
+  if (be == 0x1F) return man ? NAN : (sign ? -INFINITY : INFINITY);
+  v = be == 0 ? ldexp((double)man, -16) : ldexp(1.0 + man / 4.0, be - 15);
+  return sign ? -v : v;
+}
+
+void oracle_rowwise_gemm_bf16(const uint8_t *a, const uint8_t *b, const float *xs, const float *ws, const float *bias,
+                              uint16_t *out, int64_t M, int64_t N, int64_t K, int a_kind) {
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    for (int64_t n = 0; n < N; ++n) {
+      double acc = 0.0;
+      for (int64_t k = 0; k < K; ++k)
+        acc += (a_kind == ORACLE_E5M2 ? e5m2_to_f64(a[m * K + k]) : e4m3_to_f64(a[m * K + k])) * e4m3_to_f64(b[n * K + k]);
+      volatile float f = (float)acc;
+      f = f * xs[m];
+      f = f * ws[n];
+      if (bias) f = f + bias[n];
+      out[m * N + n] = f64_to_bf16_rne((double)f);
+    }
+  }
+}
+
 uint16_t oracle_f32_to_bf16(float f) { return f64_to_bf16_rne((double)f); }
 uint16_t oracle_bf16_mul(uint16_t a, uint16_t b) {
   return f64_to_bf16_rne((double)bf16_to_f32(a) * (double)bf16_to_f32(b));

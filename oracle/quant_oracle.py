@@ -71,6 +71,8 @@ def lib() -> C.CDLL:
         L.oracle_mx_quantize.restype = None
         L.oracle_mx_gemm_bf16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i32]
         L.oracle_mx_gemm_bf16.restype = None
+        L.oracle_rowwise_gemm_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32]
+        L.oracle_rowwise_gemm_bf16.restype = None
         L.oracle_f32_to_e2m1.argtypes = [f32]
         L.oracle_f32_to_e2m1.restype = C.c_uint8
         L.oracle_f16_to_f32.argtypes = [C.c_uint16]
@@ -215,6 +217,23 @@ def mx_gemm_bf16(a: torch.Tensor, b_nk: torch.Tensor, a_scale_blocked: torch.Ten
     out = torch.empty(m, n, dtype=torch.int16)
     lib().oracle_mx_gemm_bf16(a8.data_ptr(), b8.data_ptr(), sa.data_ptr(), sb.data_ptr(), out.data_ptr(), m, n, k,
                               2 if fp4 else 0)
+    return out.view(torch.bfloat16)
+
+
+def rowwise_gemm_bf16(a: torch.Tensor, b_nk: torch.Tensor, a_row_scale: torch.Tensor, b_row_scale: torch.Tensor,
+                      bias: torch.Tensor | None = None) -> torch.Tensor:
+    """The row-wise scaled fp8 GEMM: ``a`` [M, K] e4m3 / e5m2, ``b_nk`` [N, K] e4m3, fp32 scales [M] and [N], optional
+    bias [N] (given in fp32); returns bf16 [M, N]."""
+    a8, b8 = a.contiguous().view(torch.uint8), b_nk.contiguous().view(torch.uint8)
+    m, k = a8.shape
+    n = b8.shape[0]
+    xs = a_row_scale.contiguous().float().view(-1)
+    ws = b_row_scale.contiguous().float().view(-1)
+    assert xs.numel() == m and ws.numel() == n and b8.shape[1] == k
+    bf = None if bias is None else bias.contiguous().float()
+    out = torch.empty(m, n, dtype=torch.int16)
+    lib().oracle_rowwise_gemm_bf16(a8.data_ptr(), b8.data_ptr(), xs.data_ptr(), ws.data_ptr(),
+                                   None if bf is None else bf.data_ptr(), out.data_ptr(), m, n, k, _OUT[a.dtype])
     return out.view(torch.bfloat16)
 
 
