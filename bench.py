@@ -742,6 +742,7 @@ def main():
     elapsed_ms = t_start.elapsed_time(t_end)
     clocks = sampler.stop() if rank == 0 else None
     # per-kernel durations: the same K steps once more, now with an event after every kernel
+    barrier()  # rank 0 has just spent time stopping the clock sampler: start together again
     events = []
     m_start, m_end = event_pair()
     m_start.record()

@@ -19,7 +19,7 @@
 //   * warps 2..9 are the epilogue: tcgen05.ld 32 columns at a time, fp32 -> bf16, 64-byte row
 //     segments straight to global memory; the accumulator is released as soon as it is in registers,
 //     so the next tile's MMAs overlap the stores.
-// No cluster, no multicast: every CTA loads its own operands (A and B of an 8192^3 problem both fit
+// One CTA, no cluster: every CTA loads its own operands (A and B of an 8192^3 problem both fit
 // in L2).  Every wait is bounded: a wait that runs out records DTQ_ERR_TIMEOUT in the status word,
 // raises the CTA's abort flag, the roles drain what they have in flight, tensor memory is freed and
 // the kernel returns.
@@ -135,6 +135,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, volati
     }
   }
 }
+// The same wait by all lanes of a converged warp, with one answer for the warp.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, unsigned parity, volatile int *abort) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort));
+}
+// True in one lane of a converged warp, the same lane every time.  The producer and the MMA issuer walk their
+// loops as whole warps and let the elected lane issue the asynchronous instructions: everything those
+// instructions take as operands (descriptors, coordinates, barrier addresses) is then the same in all lanes,
+// which lets the compiler keep it in the warp's uniform registers, where TMA and tcgen05 instructions read
+// their operands from.  A loop walked by a single lane instead pays a transfer into uniform registers for
+// every operand of every instruction: measured here, 55 to 75 clocks per tcgen05 instruction, which made the
+// issuing thread, not the tensor cores, the limit of the kernel.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t elected;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+  return elected != 0;
+}
+// A value that is the same in every lane, in a form the compiler can see is.
+__device__ __forceinline__ uint32_t warp_uniform(uint32_t v) { return __shfl_sync(0xFFFFFFFFu, v, 0); }
 
 // Tiled TMA load of a box at (x = byte column, y = row) into this CTA's shared memory.
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
@@ -143,10 +161,10 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
                "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y)
                : "memory");
 }
-// 1-D bulk copy (16-byte aligned, multiple of 16 bytes).
-__device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst)),
-               "l"(src), "r"(bytes), "r"(smem_addr(bar))
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+                   smem_addr(dst)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
 
@@ -257,24 +275,23 @@ __device__ __forceinline__ void apply_rowwise(uint32_t (&v)[32], const RowwiseEp
 }
 
 struct GemmParams {
-  const uint8_t *sfa;  // blocked scales of A: atoms [ceil(M/128)][katoms] of 512 bytes
-  const uint8_t *sfb;  // blocked scales of B: atoms [ceil(N/128)][katoms]
   RowwiseEpilogue rowwise;
-  uint16_t *out;       // bf16 [M, N]
+  uint16_t *out;  // bf16 [M, N]
   int M, N, K;
-  int m_tiles, n_tiles, k_stages, katoms, n_atoms;
+  int m_tiles, n_tiles, k_stages;
   int *status;
 };
 
 template <typename SH, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, GemmParams p) {
   constexpr int kBN = SH::BN, kStagesG = SH::STAGES, kAcc = SH::ACC, kAtomsB = SH::BN / 128;
   constexpr int kKAtoms = Format<MODE>::kKAtoms;
   extern __shared__ unsigned char smem_raw[];
   GemmSmem<SH, MODE> &sm =
       *reinterpret_cast<GemmSmem<SH, MODE> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = int(warp_uniform(threadIdx.x >> 5)), lane = threadIdx.x & 31;
   volatile int *abort = &sm.abort;
 
   if (threadIdx.x == 0) {
@@ -289,94 +306,95 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     sm.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // scale staging starts as zeros: an atom that does not exist (N or K not a multiple of the tile) is never copied
-  for (int i = threadIdx.x; i < int(sizeof(sm.sfb) / 4); i += kGemmThreads) reinterpret_cast<uint32_t *>(sm.sfb)[i] = 0;
-  for (int i = threadIdx.x; i < int(sizeof(sm.sfa) / 4); i += kGemmThreads) reinterpret_cast<uint32_t *>(sm.sfa)[i] = 0;
   if (warp == 1) {  // the MMA warp owns tensor memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&sm.tmem_base)),
                  "r"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the zero fill is read by tcgen05.cp (async proxy)
   tmem_fence_before();
   __syncthreads();
   tmem_fence_after();
-  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem = warp_uniform(sm.tmem_base);
   const int total_tiles = p.m_tiles * p.n_tiles;
 
   if (warp == 0) {
-    // ---- producer ---------------------------------------------------------------------------------
-    if (lane == 0) {
-      int64_t it = 0;  // stage uses so far
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int mt, nt;
-        tile_coords(tile, p.m_tiles, p.n_tiles, &mt, &nt);
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const int s = int(it % kStagesG);
-          const unsigned round = unsigned(it / kStagesG);
-          if (*abort || (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1u, abort))) {
-            ok = false;
-            break;
-          }
-          const int atoms_b = Format<MODE>::kScaled ? min(kAtomsB, p.n_atoms - nt * kAtomsB) : 0;
-          // the atoms along K are adjacent in memory
-          const unsigned sf_bytes = Format<MODE>::kScaled ? 512u * min(kKAtoms, p.katoms - ks * kKAtoms) : 0u;
-          mbar_expect_tx(&sm.full[s], kBM * kBK + kBN * kBK + (Format<MODE>::kScaled ? sf_bytes * (1 + atoms_b) : 0u));
-          tma_load_2d(sm.a[s], &map_a, ks * kBK, mt * kBM, &sm.full[s]);
-          tma_load_2d(sm.b[s], &map_b, ks * kBK, nt * kBN, &sm.full[s]);
-          if constexpr (Format<MODE>::kScaled) {
-            bulk_load_1d(sm.sfa[s], p.sfa + (int64_t(mt) * p.katoms + ks * kKAtoms) * 512, sf_bytes, &sm.full[s]);
-            for (int h = 0; h < atoms_b; ++h)
-              bulk_load_1d(sm.sfb[s] + h * kKAtoms * 512, p.sfb + (int64_t(nt * kAtomsB + h) * p.katoms + ks * kKAtoms) * 512,
-                           sf_bytes, &sm.full[s]);
+    // ---- producer: the warp walks the loop, the elected lane issues ------------------------------------
+    uint32_t stage = 0, phase = 0;  // `phase`: parity of the current pass over the ring of stages
+    bool first_pass = true, ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int mt, nt;
+      tile_coords(tile, p.m_tiles, p.n_tiles, &mt, &nt);
+      for (int ks = 0; ks < p.k_stages; ++ks) {
+        // the MMAs that read this stage's previous contents (one pass ago) must have finished
+        if (!first_pass && !mbar_wait_warp(&sm.empty[stage], phase ^ 1u, abort)) {
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          // a whole box always arrives: rows, columns and scale atoms past the end of the arrays come as zeros
+          mbar_expect_tx(&sm.full[stage],
+                         kBM * kBK + kBN * kBK + (Format<MODE>::kScaled ? (1 + kAtomsB) * kKAtoms * 512 : 0));
+          tma_load_2d(sm.a[stage], &map_a, ks * kBK, mt * kBM, &sm.full[stage]);
+          tma_load_2d(sm.b[stage], &map_b, ks * kBK, nt * kBN, &sm.full[stage]);
+          if constexpr (Format<MODE>::kScaled) {  // one box each: A's atoms along K; B's for kAtomsB rows of atoms
+            tma_load_3d(sm.sfa[stage], &map_sfa, 0, ks * kKAtoms, mt, &sm.full[stage]);
+            tma_load_3d(sm.sfb[stage], &map_sfb, 0, ks * kKAtoms, nt * kAtomsB, &sm.full[stage]);
           }
         }
+        __syncwarp();
+        if (++stage == kStagesG) {
+          stage = 0;
+          phase ^= 1u;
+          first_pass = false;
+        }
       }
-      if (!ok) {
-        // Give up, but not with copies on their way into this CTA's shared memory: wait (bounded) for the
-        // newest copy of every stage; they complete without anybody's help.
-        atomicExch(p.status, DTQ_ERR_TIMEOUT);
-        *abort = 1;
-        for (int64_t j = it - 1; j >= 0 && j > it - 1 - kStagesG; --j)
-          mbar_wait(&sm.full[j % kStagesG], unsigned(j / kStagesG) & 1u, nullptr);
+    }
+    if (!ok && lane == 0) {
+      // Give up, but not with copies on their way into this CTA's shared memory: wait (bounded) for the newest
+      // copy of every stage (this pass's below `stage`, the previous pass's from there on); they complete
+      // without anybody's help.
+      atomicExch(p.status, DTQ_ERR_TIMEOUT);
+      *abort = 1;
+      for (uint32_t j = 0; j < uint32_t(kStagesG); ++j) {
+        if (j < stage) mbar_wait(&sm.full[j], phase, nullptr);
+        else if (!first_pass) mbar_wait(&sm.full[j], phase ^ 1u, nullptr);
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer -------------------------------------------------------------------------------
-    if (lane == 0) {
-      int64_t it = 0;
-      int local_tile = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
-        // the epilogue must have taken this accumulator's previous tile out of tensor memory
-        const int acc = local_tile % kAcc, use = local_tile / kAcc;
-        if (use > 0 && !mbar_wait(&sm.tmem_empty[acc], (use - 1) & 1u, abort)) {
+    // ---- MMA issuer: the warp walks the loop, the elected lane issues ---------------------------------------
+    uint32_t stage = 0, phase = 0;
+    int local_tile = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local_tile) {
+      // the epilogue must have taken this accumulator's previous tile out of tensor memory
+      const int acc = local_tile % kAcc, use = local_tile / kAcc;
+      if (use > 0 && !mbar_wait_warp(&sm.tmem_empty[acc], (use - 1) & 1u, abort)) {
+        ok = false;
+        break;
+      }
+      tmem_fence_after();
+      const uint32_t d_tmem = tmem + uint32_t(acc * kBN);
+      for (int ks = 0; ks < p.k_stages; ++ks) {
+        if (!mbar_wait_warp(&sm.full[stage], phase, abort)) {
           ok = false;
           break;
         }
         tmem_fence_after();
-        const uint32_t d_tmem = tmem + uint32_t(acc * kBN);
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const int s = int(it % kStagesG);
-          if (!mbar_wait(&sm.full[s], unsigned(it / kStagesG) & 1u, abort)) {
-            ok = false;
-            break;
-          }
-          tmem_fence_after();
+        if (elect_one()) {
           // this stage's scales: shared memory -> tensor memory, ordered before the MMAs below.  Tensor-memory
           // columns: A's atom j along K at kSfaCol + 4 j; B's at kSfbCol + j * 4 kAtomsB + 4 h (h = 128 tile columns)
           if constexpr (Format<MODE>::kScaled) {
 #pragma unroll
             for (int j = 0; j < kKAtoms; ++j) {
-              copy_scale_atom<false>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[s] + j * 512));
+              copy_scale_atom<false>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[stage] + j * 512));
 #pragma unroll
               for (int h = 0; h < kAtomsB; ++h)
-                copy_scale_atom<false>(tmem + kSfbCol + j * 4 * kAtomsB + 4 * h, smem_addr(sm.sfb[s] + (h * kKAtoms + j) * 512));
+                copy_scale_atom<false>(tmem + kSfbCol + j * 4 * kAtomsB + 4 * h,
+                                       smem_addr(sm.sfb[stage] + (h * kKAtoms + j) * 512));
             }
           }
-          const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
+          const uint32_t a_addr = smem_addr(sm.a[stage]), b_addr = smem_addr(sm.b[stage]);
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) {  // four instructions of 32 operand bytes inside the 128-byte swizzle span
             const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
@@ -385,14 +403,21 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                   instr_desc(id, kBN, kBM, Format<MODE>::kFormatBits | p.rowwise.operand_format_bits), accumulate,
                                   (tmem + kSfaCol + 4 * j) | (id << 30), (tmem + kSfbCol + j * 4 * kAtomsB) | (id << 30));
           }
-          umma_commit(&sm.empty[s]);  // the stage is free once these MMAs have read it
+          umma_commit(&sm.empty[stage]);  // the stage is free once these MMAs have read it
         }
-        if (ok) umma_commit(&sm.tmem_full[acc]);  // the accumulator is complete once all MMAs so far have finished
+        __syncwarp();
+        if (++stage == kStagesG) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
-      if (!ok) {
-        atomicExch(p.status, DTQ_ERR_TIMEOUT);
-        *abort = 1;
-      }
+      // the accumulator is complete once all MMAs so far have finished
+      if (ok && elect_one()) umma_commit(&sm.tmem_full[acc]);
+      __syncwarp();
+    }
+    if (!ok && lane == 0) {
+      atomicExch(p.status, DTQ_ERR_TIMEOUT);
+      *abort = 1;
     }
   } else {
     // ---- epilogue: 8 warps; warp w reads lanes 32 (w % 4) .. + 31, column half (w - 2) / 4 -------------------
@@ -456,7 +481,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tmem_fence_before();
   __syncthreads();
   if (warp == 1) {
-    if (*abort && lane == 0) {
+    if (*abort && elect_one()) {  // the lane that issued the MMAs: a commit follows the issuing thread's own
       // MMAs may still be in flight: a commit that arrives on a barrier nobody else uses, and a bounded wait for it
       mbar_init(&sm.tmem_full[0], 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -475,7 +500,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // tcgen05.mma.cta_group::2 multiplies M = 256 (each CTA supplies 128 rows of A and receives their 128 x 256
 // accumulator in its own tensor memory) by N = 256 (each CTA supplies 128 of the 256 rows of B), so every CTA
 // loads 16 + 16 KB per stage instead of 16 + 32: a third less traffic per flop, and room for 6 stages.
-//   * both CTAs' producers load their own halves (TMA, .cta_group::2, no multicast) and signal the LEADER
+//   * both CTAs' producers load their own halves (TMA, .cta_group::2, each CTA for itself) and signal the LEADER
 //     CTA's `full` barrier (the even CTA of the pair); the leader alone expects the bytes of both;
 //   * the scale atoms come in through a 3-D tensor map over the blocked scale array ([atom row][atom column]
 //     [512 bytes]), so that a missing atom is simply filled with zeros; every CTA needs its own A atom and
@@ -557,8 +582,8 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int kKAtoms = Format<MODE>::kKAtoms;
   extern __shared__ unsigned char smem_raw[];
   PairSmem<MODE> &sm = *reinterpret_cast<PairSmem<MODE> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int warp = int(warp_uniform(threadIdx.x >> 5)), lane = threadIdx.x & 31;
+  const uint32_t rank = warp_uniform(cluster_ctarank());  // 0 = leader
   const bool leader = rank == 0;
   const uint32_t peer = rank ^ 1u;
   volatile int *abort = &sm.abort;
@@ -585,92 +610,102 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   cluster_sync_all();  // both CTAs' barriers exist before anybody signals them
   tmem_fence_after();
-  const uint32_t tmem = sm.tmem_base;
-  bool failed = false;  // meaningful in the role threads
+  const uint32_t tmem = warp_uniform(sm.tmem_base);
 
   if (warp == 0) {
-    // ---- producer (one lane in each CTA) -----------------------------------------------------------------
-    if (lane == 0) {
-      int64_t it = 0;
-      bool ok = true;
-      for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
-        int mp, nt;
-        tile_coords(tile, p.m_pairs, p.n_tiles, &mp, &nt);
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const int s = int(it % kPairStages);
-          const unsigned round = unsigned(it / kPairStages);
-          if (*abort || (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1u, abort))) {
-            ok = false;
-            break;
-          }
-          const uint32_t bar = map_to_cta(smem_addr(&sm.full[s]), 0);  // the leader's barrier
+    // ---- producer (in each CTA): the warp walks the loop, the elected lane issues ------------------------------
+    uint32_t stage = 0, phase = 0;
+    bool first_pass = true, ok = true;
+    for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters) {
+      int mp, nt;
+      tile_coords(tile, p.m_pairs, p.n_tiles, &mp, &nt);
+      for (int ks = 0; ks < p.k_stages; ++ks) {
+        if (!first_pass && !mbar_wait_warp(&sm.empty[stage], phase ^ 1u, abort)) {
+          ok = false;
+          break;
+        }
+        if (elect_one()) {
+          const uint32_t bar = map_to_cta(smem_addr(&sm.full[stage]), 0);  // the leader's barrier
           if (leader)
-            mbar_expect_tx(&sm.full[s], 2 * (kBM * kBK + kPairBN / 2 * kBK + (Format<MODE>::kScaled ? 3 * kKAtoms * 512 : 0)));
-          tma_pair_load_2d(sm.a[s], &map_a, ks * kBK, mp * 256 + int(rank) * kBM, bar);
-          tma_pair_load_2d(sm.b[s], &map_b, ks * kBK, nt * kPairBN + int(rank) * (kPairBN / 2), bar);
+            mbar_expect_tx(&sm.full[stage],
+                           2 * (kBM * kBK + kPairBN / 2 * kBK + (Format<MODE>::kScaled ? 3 * kKAtoms * 512 : 0)));
+          tma_pair_load_2d(sm.a[stage], &map_a, ks * kBK, mp * 256 + int(rank) * kBM, bar);
+          tma_pair_load_2d(sm.b[stage], &map_b, ks * kBK, nt * kPairBN + int(rank) * (kPairBN / 2), bar);
           if constexpr (Format<MODE>::kScaled) {
-            tma_pair_load_3d(sm.sfa[s], &map_sfa, 0, ks * kKAtoms, mp * 2 + int(rank), bar);
-            tma_pair_load_3d(sm.sfb[s], &map_sfb, 0, ks * kKAtoms, nt * 2, bar);
+            tma_pair_load_3d(sm.sfa[stage], &map_sfa, 0, ks * kKAtoms, mp * 2 + int(rank), bar);
+            tma_pair_load_3d(sm.sfb[stage], &map_sfb, 0, ks * kKAtoms, nt * 2, bar);
           }
         }
-      }
-      if (!ok) {
-        atomicExch(p.status, DTQ_ERR_TIMEOUT);
-        failed = true;
-        *abort = 1;
-        st_cluster_u32(map_to_cta(smem_addr(&sm.abort), peer), 1u);
+        __syncwarp();
+        if (++stage == kPairStages) {
+          stage = 0;
+          phase ^= 1u;
+          first_pass = false;
+        }
       }
     }
+    if (!ok && lane == 0) {
+      atomicExch(p.status, DTQ_ERR_TIMEOUT);
+      *abort = 1;
+      st_cluster_u32(map_to_cta(smem_addr(&sm.abort), peer), 1u);
+    }
   } else if (warp == 1) {
-    // ---- MMA issuer: the leader's lane 0 drives both SMs' tensor cores ---------------------------------------
-    if (lane == 0 && leader) {
-      int64_t it = 0;
+    // ---- MMA issuer: the leader's warp walks the loop, its elected lane drives both SMs' tensor cores ---------
+    if (leader) {
+      uint32_t stage = 0, phase = 0;
       int local_tile = 0;
       bool ok = true;
       const uint32_t peer_full = map_to_cta(smem_addr(&sm.tmem_full), 1);
       for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++local_tile) {
-        if (local_tile > 0 && !mbar_wait(&sm.tmem_empty, (local_tile - 1) & 1u, abort)) {
+        if (local_tile > 0 && !mbar_wait_warp(&sm.tmem_empty, (local_tile - 1) & 1u, abort)) {
           ok = false;
           break;
         }
         tmem_fence_after();
-        for (int ks = 0; ks < p.k_stages; ++ks, ++it) {
-          const int s = int(it % kPairStages);
-          if (!mbar_wait(&sm.full[s], unsigned(it / kPairStages) & 1u, abort)) {
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!mbar_wait_warp(&sm.full[stage], phase, abort)) {
             ok = false;
             break;
           }
           tmem_fence_after();
-          if constexpr (Format<MODE>::kScaled) {
+          if (elect_one()) {
+            if constexpr (Format<MODE>::kScaled) {
 #pragma unroll
-            for (int j = 0; j < kKAtoms; ++j) {  // each CTA's shared memory -> that CTA's tensor memory, columns as above
-              copy_scale_atom<true>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[s] + j * 512));
+              for (int j = 0; j < kKAtoms; ++j) {  // each CTA's shared memory -> that CTA's tensor memory, columns as above
+                copy_scale_atom<true>(tmem + kSfaCol + 4 * j, smem_addr(sm.sfa[stage] + j * 512));
 #pragma unroll
-              for (int h = 0; h < 2; ++h)
-                copy_scale_atom<true>(tmem + kSfbCol + j * 8 + 4 * h, smem_addr(sm.sfb[s] + (h * kKAtoms + j) * 512));
+                for (int h = 0; h < 2; ++h)
+                  copy_scale_atom<true>(tmem + kSfbCol + j * 8 + 4 * h, smem_addr(sm.sfb[stage] + (h * kKAtoms + j) * 512));
+              }
             }
-          }
-          const uint32_t a_addr = smem_addr(sm.a[s]), b_addr = smem_addr(sm.b[s]);
+            const uint32_t a_addr = smem_addr(sm.a[stage]), b_addr = smem_addr(sm.b[stage]);
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) {
-            const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
-            const uint32_t j = Format<MODE>::k_atom(k), id = Format<MODE>::sf_id(k);
-            issue_mma<MODE, true>(tmem, operand_desc(a_addr + k * 32), operand_desc(b_addr + k * 32),
-                                 instr_desc(id, kPairBN, 256, Format<MODE>::kFormatBits | p.rowwise.operand_format_bits), accumulate,
-                                 (tmem + kSfaCol + 4 * j) | (id << 30), (tmem + kSfbCol + j * 8) | (id << 30));
+            for (uint32_t k = 0; k < 4; ++k) {
+              const uint32_t accumulate = (ks > 0 || k > 0) ? 1u : 0u;
+              const uint32_t j = Format<MODE>::k_atom(k), id = Format<MODE>::sf_id(k);
+              issue_mma<MODE, true>(tmem, operand_desc(a_addr + k * 32), operand_desc(b_addr + k * 32),
+                                   instr_desc(id, kPairBN, 256, Format<MODE>::kFormatBits | p.rowwise.operand_format_bits),
+                                   accumulate, (tmem + kSfaCol + 4 * j) | (id << 30), (tmem + kSfbCol + j * 8) | (id << 30));
+            }
+            // the stage is free in both CTAs once these MMAs have read it
+            const uint32_t empty_bar = smem_addr(&sm.empty[stage]);
+            umma_commit_pair(empty_bar);
+            umma_commit_pair(map_to_cta(empty_bar, 1));
           }
-          // the stage is free in both CTAs once these MMAs have read it
-          umma_commit_pair(smem_addr(&sm.empty[s]));
-          umma_commit_pair(map_to_cta(smem_addr(&sm.empty[s]), 1));
+          __syncwarp();
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
-        if (ok) {  // both CTAs' halves of the accumulator are complete once all MMAs so far have finished
+        if (ok && elect_one()) {  // both CTAs' halves of the accumulator are complete once all MMAs so far have finished
           umma_commit_pair(smem_addr(&sm.tmem_full));
           umma_commit_pair(peer_full);
         }
+        __syncwarp();
       }
-      if (!ok) {
+      if (!ok && lane == 0) {
         atomicExch(p.status, DTQ_ERR_TIMEOUT);
-        failed = true;
         *abort = 1;
         st_cluster_u32(map_to_cta(smem_addr(&sm.abort), peer), 1u);
       }
@@ -686,7 +721,6 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!mbar_wait(&sm.tmem_full, local_tile & 1u, abort)) {
         if (lane == 0) {
           atomicExch(p.status, DTQ_ERR_TIMEOUT);
-          failed = true;
           *abort = 1;
           st_cluster_u32(map_to_cta(smem_addr(&sm.abort), peer), 1u);
         }
@@ -733,7 +767,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 
   // ---- teardown ---------------------------------------------------------------------------------------------
-  (void)failed;  // whoever gave up has already raised both CTAs' abort flags
+  // whoever gave up has already raised both CTAs' abort flags
   tmem_fence_before();
   __syncthreads();
   if (*abort) {
@@ -896,13 +930,18 @@ int launch_shape(const GemmCall &c, const DeviceInfo &dev) {
     DTQ_CUDA_TRY(cudaFuncSetAttribute(mx_gemm_kernel<SH, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev_id].store(1, std::memory_order_release);
   }
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_sfa, map_sfb;
   if (int e = make_operand_map(&map_a, c.a, c.m, c.k_bytes, kBM)) return e;
   if (int e = make_operand_map(&map_b, c.b, c.n, c.k_bytes, SH::BN)) return e;
+  if constexpr (Format<MODE>::kScaled) {
+    if (int e = make_scale_map(&map_sfa, c.sfa, ceil_div64(c.m, 128), c.katoms, 1, Format<MODE>::kKAtoms)) return e;
+    if (int e = make_scale_map(&map_sfb, c.sfb, ceil_div64(c.n, 128), c.katoms, SH::BN / 128, Format<MODE>::kKAtoms)) return e;
+  } else {  // never dereferenced by the kernel
+    map_sfa = map_a;
+    map_sfb = map_a;
+  }
   GemmParams p;
   p.rowwise = c.rowwise;
-  p.sfa = static_cast<const uint8_t *>(c.sfa);
-  p.sfb = static_cast<const uint8_t *>(c.sfb);
   p.out = static_cast<uint16_t *>(c.out);
   p.M = static_cast<int>(c.m);
   p.N = static_cast<int>(c.n);
@@ -910,12 +949,10 @@ int launch_shape(const GemmCall &c, const DeviceInfo &dev) {
   p.m_tiles = static_cast<int>(ceil_div64(c.m, kBM));
   p.n_tiles = static_cast<int>(ceil_div64(c.n, SH::BN));
   p.k_stages = static_cast<int>(ceil_div64(c.k_bytes, kBK));
-  p.katoms = static_cast<int>(c.katoms);
-  p.n_atoms = static_cast<int>(ceil_div64(c.n, 128));
   p.status = c.status;
   const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
   const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-  mx_gemm_kernel<SH, MODE><<<grid, kGemmThreads, smem, c.st>>>(map_a, map_b, p);
+  mx_gemm_kernel<SH, MODE><<<grid, kGemmThreads, smem, c.st>>>(map_a, map_b, map_sfa, map_sfb, p);
   return cuda_status(cudaGetLastError());
 }
 
