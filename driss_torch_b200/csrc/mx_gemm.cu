@@ -274,6 +274,20 @@ __device__ __forceinline__ void apply_rowwise(uint32_t (&v)[32], const RowwiseEp
   }
 }
 
+// 32 accumulator columns of this thread's lane of tensor memory into registers (asynchronous: tmem_load_wait).
+__device__ __forceinline__ void tmem_load_32(uint32_t (&v)[32], uint32_t taddr) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 struct GemmParams {
   RowwiseEpilogue rowwise;
   uint16_t *out;  // bf16 [M, N]
@@ -439,23 +453,19 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int64_t row = int64_t(mt) * kBM + quad * 32 + lane;
       uint32_t packed[kChunks][16];  // this thread's columns of one row as bf16 pairs
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        uint32_t v[32];
+      for (int c = 0; c < kChunks; c += 2) {  // two loads in flight per wait: the accumulator is handed back sooner
+        uint32_t v[2][32];
         const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(acc * kBN + half * kHalfCols + c * 32);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-            : "r"(taddr)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if constexpr (MODE == kRowwise)
-          apply_rowwise(v, p.rowwise, row, int64_t(nt) * kBN + half * kHalfCols + c * 32, p.M, p.N);
+        tmem_load_32(v[0], taddr);
+        tmem_load_32(v[1], taddr + 32);
+        tmem_load_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) packed[c][i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+        for (int u = 0; u < 2; ++u) {
+          if constexpr (MODE == kRowwise)
+            apply_rowwise(v[u], p.rowwise, row, int64_t(nt) * kBN + half * kHalfCols + (c + u) * 32, p.M, p.N);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) packed[c + u][i] = pack_bf16(v[u][2 * i], v[u][2 * i + 1]);
+        }
       }
       // the accumulator is in registers: hand tensor memory back before storing
       tmem_fence_before();
@@ -730,22 +740,19 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int64_t row = int64_t(mp) * 256 + int64_t(rank) * kBM + quad * 32 + lane;
       uint32_t packed[4][16];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
+      for (int c = 0; c < 4; c += 2) {  // two loads in flight per wait
+        uint32_t v[2][32];
         const uint32_t taddr = tmem + (uint32_t(quad * 32) << 16) + uint32_t(half * 128 + c * 32);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-            : "r"(taddr)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if constexpr (MODE == kRowwise) apply_rowwise(v, p.rowwise, row, int64_t(nt) * kPairBN + half * 128 + c * 32, p.M, p.N);
+        tmem_load_32(v[0], taddr);
+        tmem_load_32(v[1], taddr + 32);
+        tmem_load_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) packed[c][i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+        for (int u = 0; u < 2; ++u) {
+          if constexpr (MODE == kRowwise)
+            apply_rowwise(v[u], p.rowwise, row, int64_t(nt) * kPairBN + half * 128 + (c + u) * 32, p.M, p.N);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) packed[c + u][i] = pack_bf16(v[u][2 * i], v[u][2 * i + 1]);
+        }
       }
       tmem_fence_before();
       __syncwarp();
@@ -958,18 +965,23 @@ int launch_shape(const GemmCall &c, const DeviceInfo &dev) {
 
 template <int MODE>
 int launch_gemm(const GemmCall &c, int kernel, const DeviceInfo &dev) {
-  // Which kernel.  All of them are bound by what an SM can pull out of L2, so the estimate is rounds of tiles on
-  // the busiest SM times the operand bytes a CTA loads per round: 48 KB per stage for a wide tile, 32 KB for a
-  // narrow one, 32 KB for a CTA's half of an SM pair's 256 x 256 tile (which is worth a wide tile of output).
+  // Which kernel: estimated time = a fixed part (launch, set-up, filling the pipeline, the last epilogue) plus
+  // rounds of tiles on the busiest SM x stages of 128 operand bytes along K x the time of such a stage, all in
+  // microseconds as measured on a B200 (steady state, 1.3 to 1.5 GHz under the power cap): the SM pair's
+  // 256 x 256 tile costs 0.36 per stage but 10 to start, a 128 x 256 tile 0.42 and 8, a 128 x 128 tile 0.30 and 6.
+  // So large problems run on SM pairs, and problems of a tile or two per SM on the narrow kernel, whose
+  // smaller tiles also spread a small output over more SMs.
   const int64_t m_tiles = ceil_div64(c.m, kBM);
-  const double wide = static_cast<double>(ceil_div64(m_tiles * ceil_div64(c.n, 256), dev.sm_count)) * 48.0;
-  const double narrow = static_cast<double>(ceil_div64(m_tiles * ceil_div64(c.n, 128), dev.sm_count)) * 32.0 * 1.15;
+  const double stages = static_cast<double>(ceil_div64(c.k_bytes, kBK));
+  const double wide = 8.0 + static_cast<double>(ceil_div64(m_tiles * ceil_div64(c.n, 256), dev.sm_count)) * stages * 0.42;
+  const double narrow = 6.0 + static_cast<double>(ceil_div64(m_tiles * ceil_div64(c.n, 128), dev.sm_count)) * stages * 0.30;
   int dev_id = 0, max_clusters = 0;
   DTQ_CUDA_TRY(cudaGetDevice(&dev_id));
   if (int e = pair_cluster_capacity<MODE>(dev_id, &max_clusters)) return e;
   const double pair =
-      max_clusters > 0 ? static_cast<double>(ceil_div64(ceil_div64(c.m, 256) * ceil_div64(c.n, 256), max_clusters)) * 32.0 * 1.05
-                       : 1e30;
+      max_clusters > 0
+          ? 10.0 + static_cast<double>(ceil_div64(ceil_div64(c.m, 256) * ceil_div64(c.n, 256), max_clusters)) * stages * 0.36
+          : 1e30;
   if (kernel == DTQ_GEMM_PAIR && max_clusters <= 0) return DTQ_ERR_CUDA_BASE + static_cast<int>(cudaErrorNotSupported);
   if (kernel == DTQ_GEMM_AUTO)
     kernel = (pair <= wide && pair <= narrow) ? DTQ_GEMM_PAIR : (narrow < wide ? DTQ_GEMM_NARROW : DTQ_GEMM_WIDE);
