@@ -65,6 +65,13 @@ __device__ __forceinline__ void stg_stream(void *p, uint4 v) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Asks L2 to fetch `bytes` (a multiple of 16) from the 16-byte aligned global address `p`.  Nothing is
+// delivered to the thread and nothing observable changes: L2 is where this GPU's memory is kept coherent,
+// so a line fetched early is the line a later load would have fetched, whoever writes it in between.
+__device__ __forceinline__ void l2_prefetch_bulk(const void *p, unsigned bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // ---- number formats --------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }

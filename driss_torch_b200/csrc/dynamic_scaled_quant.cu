@@ -259,6 +259,7 @@ dsq_fused_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, float 
 }
 
 // ---- cast phase alone ---------------------------------------------------------------------------------
+constexpr int kCastPrefetchTiles = 6;  // tiles per block asked of L2 while the block waits for the amax
 // BOUNDED: *amax_p is the maximum of this very input (no product can overflow).
 template <int IN, int OUT, int UNROLL, bool BOUNDED>
 __global__ void __launch_bounds__(kThreads, 2048 / kThreads)
@@ -266,6 +267,17 @@ cast_with_amax_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, c
                       float *__restrict__ scale_out, float *__restrict__ amax_out, int64_t numel) {
   using C = DsqChunk<IN, OUT, BOUNDED>;
   pdl_launch_dependents();
+  const int64_t nchunks = numel / C::kElems;
+  constexpr int64_t kTile = int64_t(kThreads) * UNROLL;
+  const int64_t ntiles = (nchunks + kTile - 1) / kTile;
+  // The amax may be a while in coming (behind it sits the end of a kernel, or an exchange between GPUs) and the
+  // memory system idles meanwhile: ask L2 for this block's first tiles now.  Harmless whatever the kernel before
+  // this one is still writing (see l2_prefetch_bulk).
+  if (threadIdx.x < kCastPrefetchTiles) {
+    const int64_t t = blockIdx.x + int64_t(threadIdx.x) * gridDim.x;
+    if (t < ntiles && (ntiles - t) * kTile <= nchunks)
+      l2_prefetch_bulk(in + (ntiles - 1 - t) * kTile, unsigned(kTile * sizeof(uint4)));
+  }
   pdl_wait();  // launched so that it may become resident under the tail of the kernel that delivers the amax
   const float amax_in = *amax_p;
   const float amax = fmaxf(amax_in, 0.0f);
@@ -276,10 +288,7 @@ cast_with_amax_stream(const uint4 *__restrict__ in, uint8_t *__restrict__ out, c
     if (scale_out) *scale_out = bad ? amax_in : static_cast<float>(sd.sd);
     if (amax_out) *amax_out = bad ? amax_in : amax;
   }
-  const int64_t nchunks = numel / C::kElems;
-  constexpr int64_t kTile = int64_t(kThreads) * UNROLL;
   // highest addresses first: what the kernel before this one read last (an amax, an MX cast) may still be in L2
-  const int64_t ntiles = (nchunks + kTile - 1) / kTile;
   for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const int64_t tile = ntiles - 1 - t;
     const int64_t first = tile * kTile + threadIdx.x;
