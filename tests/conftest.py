@@ -56,3 +56,14 @@ def ref_ops():
         pytest.skip("oracle/_ref not built (make -f oracle/Makefile.ref)")
     torch.ops.load_library(str(REF_LIB))
     return torch.ops.DrissTorchRef
+
+
+@pytest.fixture(scope="session")
+def ref_gemm_ops():
+    """The unmodified reference MX GEMMs (torch.ops.DrissTorchRefGemm: the reference's CUTLASS instantiations built
+    from its own source), if they were built.  That library never travels with a multi-GPU run."""
+    lib = REF_LIB.parent / "libdriss_torch_ref_gemm.so"
+    if not lib.exists():
+        pytest.skip("oracle/_ref/libdriss_torch_ref_gemm.so not built (make -f oracle/Makefile.ref gemm)")
+    torch.ops.load_library(str(lib))
+    return torch.ops.DrissTorchRefGemm

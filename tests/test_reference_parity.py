@@ -117,3 +117,47 @@ def test_mx_wide_range_patterns_and_degenerate_blocks(ref_ops):
         rp, rs = ref_ops.mx_fp8_quantize(a, 32, 1, False, torch.float8_e4m3fn)
         p, s = dt.mx_fp8_quantize(a)
         assert torch.equal(as_bytes(p), as_bytes(rp)) and torch.equal(as_bytes(s), as_bytes(rs))
+
+
+# test/test_mx.py:41-57 (M, K, N), and the benchmark's shapes
+GEMM_SIZES = [(128, 128, 128), (256, 256, 256), (384, 384, 384), (512, 512, 512), (768, 768, 768), (1024, 1024, 1024),
+              (128, 256, 384), (256, 384, 512), (129, 256, 384), (133, 512, 528), (4096, 4096, 4096), (2048, 1024, 8192)]
+
+
+@pytest.mark.parametrize("kernel", ["pair", "wide", "narrow", "auto"])
+@pytest.mark.parametrize("size", GEMM_SIZES, ids=lambda s: f"{s[0]}x{s[1]}x{s[2]}")
+def test_mx_fp8_bf16_equals_the_reference_kernel_bit_for_bit(ref_gemm_ops, size, kernel):
+    # Same operands through the reference's CUTLASS kernel and through each of ours: fp32 accumulation over K in the
+    # same order (128 at a time, 32 per instruction), one rounding to bf16 -- the results are the same bits, on
+    # random data, not only on exactly summable inputs.
+    import driss_torch_b200 as dt
+    from driss_torch_b200 import _cabi
+
+    m, k, n = size
+    g = torch.Generator(device="cuda").manual_seed(m * 7 + k * 3 + n)
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    b = (torch.randn(n, k, device="cuda", generator=g) * 0.25).to(torch.bfloat16)
+    pa, sa = dt.mx_fp8_quantize_blocked(a)
+    pb, sb = dt.mx_fp8_quantize_blocked(b)
+    want = ref_gemm_ops.mx_fp8_bf16(pa, pb.t(), sa, sb)
+    got = _cabi.mx_fp8_bf16(pa, pb, sa, sb, kernel=kernel)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16)), \
+        f"{(got.view(torch.int16) != want.view(torch.int16)).sum().item()} of {got.numel()} outputs differ"
+
+
+@pytest.mark.parametrize("kernel", ["pair", "wide", "narrow"])
+@pytest.mark.parametrize("size", [(128, 128, 128), (512, 512, 512), (129, 256, 384), (133, 512, 528), (2048, 2048, 2048)],
+                         ids=lambda s: f"{s[0]}x{s[1]}x{s[2]}")
+def test_mx_fp4_bf16_equals_the_reference_kernel_bit_for_bit(ref_gemm_ops, size, kernel):
+    import driss_torch_b200 as dt
+    from driss_torch_b200 import _cabi
+
+    m, k, n = size
+    g = torch.Generator(device="cuda").manual_seed(m + k + n)
+    a = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    b = torch.randn(n, k, device="cuda", generator=g).to(torch.bfloat16)
+    pa, sa = dt.mx_fp4_quantize(a, blocked=True)
+    pb, sb = dt.mx_fp4_quantize(b, blocked=True)
+    want = ref_gemm_ops.mx_fp4_bf16(pa, pb.t(), sa, sb)
+    got = _cabi.mx_fp8_bf16(pa, pb, sa, sb, kernel=kernel, fp4=True)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
