@@ -131,7 +131,7 @@ def mx_fp4_bf16(a: Tensor, b: Tensor, a_scale: Tensor, b_scale: Tensor) -> Tenso
     """Matrix multiplication of two MXFP4 operands (e2m1 values packed two per byte, the lower index in the low
     nibble; E8M0 scales of 32 elements along K, blocked layout) (driss_torch/__init__.py:98-111): ``a`` [M, K/2]
     bytes row-major, ``b`` [K/2, N] column-major (``w.t()`` of a row-major [N, K/2] payload); returns bf16 [M, N].
-    ``mx_fp4_quantize`` produces the payloads; its row-major scales go through ``mx_blocked_scales``."""
+    ``mx_fp4_quantize(x, blocked=True)`` produces the payloads and the scales in that layout."""
     return ops.mx_fp4_bf16(a, b, a_scale, b_scale)
 
 
