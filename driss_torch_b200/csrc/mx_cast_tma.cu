@@ -4,7 +4,7 @@
 // from the warps that convert.  A persistent CTA = one producer thread + eight consumer warps;
 // full/empty mbarriers per stage; every wait is bounded and reports through a status word.
 // No tensor map is needed (MX blocks run along the contiguous dimension, so a tile is a flat
-// 16 KiB span) and nothing is multicast.
+// 16 KiB span); every copy is for the CTA that issues it, there is no cluster.
 //
 // Kept beside the register-path kernel as a measured alternative (the benchmark's per-op table
 // times both): on B200 the register path is faster for this reuse-free stream, so the default

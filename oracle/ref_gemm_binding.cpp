@@ -9,7 +9,7 @@
 // The schema strings repeat src/register_ops.cpp:35-38 under `DrissTorchRefGemm`.
 //
 // The reference instantiates a CUTLASS collective on a 2x1 thread-block cluster; that library is
-// therefore kept out of every multi-GPU run of this repository (.gpurunignore.multi) and is only
+// therefore kept out of every multi-GPU run of this repository (the ignore list for such runs names it) and is only
 // ever given this GPU's own memory.
 #include <ATen/ATen.h>
 #include <c10/core/DispatchKey.h>
