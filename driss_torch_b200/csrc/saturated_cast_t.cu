@@ -188,8 +188,10 @@ cast_transposed_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, 
     if (scale_out) *scale_out = C::scale_value(s);
     if (amax_out) *amax_out = fmaxf(*scale, 0.0f);
   }
-  const int64_t row0 = (blockIdx.x / col_tiles) * kTileRows;
-  const int64_t col0 = (blockIdx.x % col_tiles) * kTileCols;
+  // highest rows first: behind an amax (or any other pass over the input) the end of the tensor may still be in L2
+  const int64_t t = int64_t(gridDim.x) - 1 - blockIdx.x;
+  const int64_t row0 = (t / col_tiles) * kTileRows;
+  const int64_t col0 = (t % col_tiles) * kTileCols;
   if (row0 + kTileRows <= rows && col0 + kTileCols <= cols)
     transposed_tile<C, BOTH, true>(tile, in, out, out_t, s, rows, cols, row0, col0);
   else
