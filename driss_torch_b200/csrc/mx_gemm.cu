@@ -3,26 +3,30 @@
 // The consumer of the MX casts: e4m3 operands with one E8M0 scale per 32 elements along K, both
 // scale tensors in the blocked (128 x 4 atoms of 512 bytes) layout that mx_fp8_quantize_blocked
 // emits.  Replaces driss_torch::mx_fp8_bf16 (src/mx_fp8_bf16.cu:42-163 run_gemm, :168-215 validate,
-// :217-241), which instantiates a CUTLASS Sm100 block-scaled collective with 128x128x128 tiles.
+// :217-241), which instantiates a CUTLASS Sm100 block-scaled collective with 128x128x128 tiles; and, from
+// the same source, mx_fp4_bf16 (:243-271) and the row-wise scaled GEMM behind sweep_mm (src/sweep_mm.cu,
+// src/scaled_mm_kernels/f8f8bf16_rowwise_kernel.h:151-175), see Format below.
 //
-// Hand-written for sm_100a:
-//   * one persistent CTA per SM walks 128 x 256 output tiles; K advances in stages of 128 bytes;
-//   * warp 0 (one lane) is the producer: per stage two tiled TMA loads (A 128 x 128 B, B 256 x 128 B,
-//     128-byte swizzle, out-of-bounds rows and columns filled with zeros) and up to three 512-byte
-//     bulk copies of scale atoms, all counted on the stage's `full` mbarrier; 4 stages = 198 KB;
-//   * warp 1 (one lane) issues the tensor-core work: tcgen05.cp moves the stage's scale atoms from
-//     shared memory into tensor memory (32 rows x 16 bytes, replicated to the four lane quadrants,
-//     which is exactly one blocked atom), then four tcgen05.mma kind::mxf8f6f4.block_scale
-//     instructions (M 128, N 256, K 32), the k-block picking its scale byte through the descriptor's
-//     scale-factor id; tcgen05.commit releases the stage (`empty`) and finally hands the accumulator
-//     (128 lanes x 256 fp32 columns of tensor memory) to the epilogue;
-//   * warps 2..9 are the epilogue: tcgen05.ld 32 columns at a time, fp32 -> bf16, 64-byte row
-//     segments straight to global memory; the accumulator is released as soon as it is in registers,
-//     so the next tile's MMAs overlap the stores.
-// One CTA, no cluster: every CTA loads its own operands (A and B of an 8192^3 problem both fit
-// in L2).  Every wait is bounded: a wait that runs out records DTQ_ERR_TIMEOUT in the status word,
-// raises the CTA's abort flag, the roles drain what they have in flight, tensor memory is freed and
-// the kernel returns.
+// Hand-written for sm_100a.  Three kernels from one source (chosen per call by a measured cost model, see
+// launch_gemm): an SM pair on a 256 x 256 tile (tcgen05.mma.cta_group::2, further down), and one CTA per SM on a
+// 128 x 256 or a 128 x 128 tile (this kernel).  Common to all:
+//   * persistent CTAs of 320 threads walk the output tiles; K advances in stages of 128 bytes;
+//   * warp 0 is the producer: per stage tiled TMA loads of the operands (boxes of 128 bytes of K, 128-byte
+//     swizzle, rows and columns past the edges filled with zeros) and of the stage's scale atoms (a 3-D tensor
+//     map over the blocked scale array, an atom past the end arrives as zeros), all counted on the stage's `full`
+//     mbarrier;
+//   * warp 1 issues the tensor-core work: tcgen05.cp moves the stage's scale atoms from shared memory into
+//     tensor memory (32 rows x 16 bytes, replicated to the four lane quadrants, which is exactly one blocked
+//     atom), then four tcgen05.mma (K = 32 bytes of every operand row each), the k-block picking its scale byte
+//     through the descriptor's scale-factor id; tcgen05.commit releases the stage (`empty`) and finally hands
+//     the accumulator (128 lanes x up to 256 fp32 columns of tensor memory) to the epilogue;
+//   * both of those warps walk their loops as whole warps with one elected lane issuing (see elect_one);
+//   * warps 2..9 are the epilogue: tcgen05.ld 2 x 32 columns at a time, fp32 -> bf16, 64-byte row segments
+//     straight to global memory; the accumulator is released as soon as it is in registers, so the next tile's
+//     MMAs overlap the stores.
+// No load is shared between CTAs: every CTA loads its own operands (A and B of an 8192^3 problem both fit in
+// L2).  Every wait is bounded: a wait that runs out records DTQ_ERR_TIMEOUT in the status word, raises the CTA's
+// abort flag, the roles drain what they have in flight, tensor memory is freed and the kernel returns.
 #include <cuda.h>
 
 #include <atomic>
