@@ -311,6 +311,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       *reinterpret_cast<GemmSmem<SH, MODE> *>(smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u));
   const int warp = int(warp_uniform(threadIdx.x >> 5)), lane = threadIdx.x & 31;
   volatile int *abort = &sm.abort;
+  // Programmatic dependent launch, both ways: what is queued behind this kernel with that attribute may become
+  // resident as this grid's CTAs leave, and this kernel's own set-up below (barriers, tensor memory, the tensor
+  // maps in its parameters) may run under the tail of the kernel before it; nothing in global memory is touched
+  // before pdl_wait.
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesG; ++s) {
@@ -333,6 +338,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tmem_fence_before();
   __syncthreads();
   tmem_fence_after();
+  pdl_wait();  // the operands, the scales and the output buffer belong to this kernel from here on
   const uint32_t tmem = warp_uniform(sm.tmem_base);
   const int total_tiles = p.m_tiles * p.n_tiles;
 
@@ -603,6 +609,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   volatile int *abort = &sm.abort;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int total_tiles = p.m_pairs * p.n_tiles;
+  pdl_launch_dependents();  // as in the single-CTA kernel
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
@@ -624,6 +631,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   cluster_sync_all();  // both CTAs' barriers exist before anybody signals them
   tmem_fence_after();
+  pdl_wait();
   const uint32_t tmem = warp_uniform(sm.tmem_base);
 
   if (warp == 0) {
@@ -847,6 +855,7 @@ int make_scale_map(CUtensorMap *map, const void *base, int64_t atom_rows, int64_
 
 constexpr int kMaxGemmDevices = 64;
 
+// Clusters of two, launched as a programmatic dependent of what is before it on the stream (attr: room for two).
 void cluster_launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, int grid, size_t smem, cudaStream_t st) {
   *cfg = cudaLaunchConfig_t{};
   cfg->gridDim = dim3(grid);
@@ -857,8 +866,10 @@ void cluster_launch_config(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *attr, i
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg->attrs = attr;
-  cfg->numAttrs = 1;
+  cfg->numAttrs = 2;
 }
 
 // The SM-pair kernel: clusters of two CTAs, as many as the device can hold at once (at most one CTA per SM).
@@ -876,8 +887,9 @@ int pair_cluster_capacity(int dev_id, int *max_clusters) {
       int n = 0;
       if (cudaFuncSetAttribute(mx_gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess) {
         cudaLaunchConfig_t cfg;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         cluster_launch_config(&cfg, attr, 2, smem, nullptr);
+        cfg.numAttrs = 1;  // the occupancy query wants the cluster shape only
         if (cudaOccupancyMaxActiveClusters(&n, mx_gemm_pair_kernel<MODE>, &cfg) != cudaSuccess) n = 0;
       }
       (void)cudaGetLastError();  // a device without cluster support is not an error of this call
@@ -924,7 +936,7 @@ int launch_pair(const GemmCall &c, int max_clusters) {
   const int64_t tiles = int64_t(p.m_pairs) * p.n_tiles;
   const int clusters = static_cast<int>(tiles < max_clusters ? tiles : max_clusters);
   cudaLaunchConfig_t cfg;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   cluster_launch_config(&cfg, attr, 2 * clusters, sizeof(PairSmem<MODE>) + 1024, c.st);
   return cuda_status(cudaLaunchKernelEx(&cfg, mx_gemm_pair_kernel<MODE>, map_a, map_b, map_sfa, map_sfb, p));
 }
@@ -963,8 +975,8 @@ int launch_shape(const GemmCall &c, const DeviceInfo &dev) {
   p.status = c.status;
   const int64_t tiles = int64_t(p.m_tiles) * p.n_tiles;
   const int grid = static_cast<int>(tiles < dev.sm_count ? tiles : dev.sm_count);
-  mx_gemm_kernel<SH, MODE><<<grid, kGemmThreads, smem, c.st>>>(map_a, map_b, map_sfa, map_sfb, p);
-  return cuda_status(cudaGetLastError());
+  return cuda_status(launch_after_dependency(mx_gemm_kernel<SH, MODE>, dim3(grid), dim3(kGemmThreads), size_t(smem), c.st, map_a,
+                                             map_b, map_sfa, map_sfb, p));
 }
 
 template <int MODE>
