@@ -56,6 +56,7 @@ mx_amax_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint
                int64_t nchunks, Workspace *ws) {
   __shared__ uint32_t warp_cand[kThreadsA / 32];
   pdl_launch_dependents();  // the finishing warp may become resident now; it waits for this grid to complete
+  pdl_wait();               // and this grid itself may have become resident under the tail of the kernel before it
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int64_t kTile = int64_t(kThreadsA) * kUnrollA;
   uint32_t cand = 0;
@@ -138,8 +139,8 @@ int launch_mx_amax(const void *in_bf16, void *payload, void *scales, float *amax
   const int grid = balanced_grid(tiles, int64_t(dev.sm_count) * (1 << 20));
   Workspace *ws = static_cast<Workspace *>(workspace);
   if (numel > 0)
-    mx_amax_kernel<<<grid, kThreadsA, 0, st>>>(static_cast<const uint4 *>(in_bf16), static_cast<uint8_t *>(payload),
-                                               static_cast<uint8_t *>(scales), nchunks, ws);
+    DTQ_CUDA_TRY(launch_after_dependency(mx_amax_kernel, dim3(grid), dim3(kThreadsA), 0, st, static_cast<const uint4 *>(in_bf16),
+                                         static_cast<uint8_t *>(payload), static_cast<uint8_t *>(scales), nchunks, ws));
   // an empty shard still takes part in the exchange
   return cuda_status(launch_after_dependency(mx_amax_finish_kernel<P2P>, dim3(1), dim3(32), 0, st, amax_out, ws, px));
 }

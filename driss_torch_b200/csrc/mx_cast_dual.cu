@@ -125,6 +125,10 @@ mx_dual_kernel(const uint16_t *__restrict__ in, uint8_t *__restrict__ payload, u
                uint8_t *__restrict__ payload_t, uint8_t *__restrict__ scales_t, int64_t rows, int64_t cols,
                int64_t row_tiles, int64_t col_tiles) {
   __shared__ __align__(16) uint32_t tile[kTile][kTileWords];
+  // programmatic dependent launch, both ways (see dtq_device.cuh): blocks may become resident under the tail of the
+  // kernel before this one, and what is queued behind this one under its own tail
+  pdl_launch_dependents();
+  pdl_wait();
   // grouped numbering: groups of kGroupRowTiles row tiles; inside a group row tiles vary fastest
   const int64_t pid = blockIdx.x;
   const int64_t per_group = kGroupRowTiles * col_tiles;
@@ -158,10 +162,11 @@ int launch_dual(const void *in_bf16, void *payload, void *scales_e8m0, void *pay
   const int64_t row_tiles = ceil_div64(rows, kTile), col_tiles = ceil_div64(cols, kTile);
   if (row_tiles > 0x7FFFFFFFLL / col_tiles) return DTQ_ERR_TOO_LARGE;  // grid.x
   auto kernel = row_out ? mx_dual_kernel<BLOCKED, true> : mx_dual_kernel<BLOCKED, false>;
-  kernel<<<static_cast<unsigned>(row_tiles * col_tiles), kThreadsDual, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t *>(in_bf16), static_cast<uint8_t *>(payload), static_cast<uint8_t *>(scales_e8m0),
-      static_cast<uint8_t *>(payload_t), static_cast<uint8_t *>(scales_t_e8m0), rows, cols, row_tiles, col_tiles);
-  return cuda_status(cudaGetLastError());
+  return cuda_status(launch_after_dependency(kernel, dim3(static_cast<unsigned>(row_tiles * col_tiles)), dim3(kThreadsDual), 0,
+                                             static_cast<cudaStream_t>(stream), static_cast<const uint16_t *>(in_bf16),
+                                             static_cast<uint8_t *>(payload), static_cast<uint8_t *>(scales_e8m0),
+                                             static_cast<uint8_t *>(payload_t), static_cast<uint8_t *>(scales_t_e8m0), rows, cols,
+                                             row_tiles, col_tiles));
 }
 }  // namespace
 }  // namespace dtq

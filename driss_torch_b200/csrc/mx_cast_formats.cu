@@ -147,6 +147,10 @@ template <int IN, int FMT>
 __global__ void __launch_bounds__(kThreadsF, 2048 / kThreadsF)
 mx_formats_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ payload, uint8_t *__restrict__ scales,
                   int64_t nchunks, int64_t kblocks) {  // kblocks > 0: scales in the MX GEMM's blocked layout, that many per row
+  // programmatic dependent launch, both ways (see dtq_device.cuh): blocks may become resident under the tail of the
+  // kernel before this one, and what is queued behind this one under its own tail
+  pdl_launch_dependents();
+  pdl_wait();
   using I = MxIn<IN>;
   using O = MxOut<FMT>;
   constexpr int kLanes = 32 / I::kElems;                        // lanes per MX block
@@ -190,9 +194,9 @@ int launch_formats(const void *in, void *payload, void *scales, int64_t numel, i
   const int64_t nchunks = numel / I::kElems;
   const int64_t tiles = ceil_div64(nchunks, int64_t(kThreadsF) * kUnrollF);
   const int grid = balanced_grid(tiles, int64_t(dev.sm_count) * (1 << 20));
-  mx_formats_kernel<IN, FMT><<<grid, kThreadsF, 0, st>>>(static_cast<const uint4 *>(in), static_cast<uint8_t *>(payload),
-                                                         static_cast<uint8_t *>(scales), nchunks, kblocks);
-  return cuda_status(cudaGetLastError());
+  return cuda_status(launch_after_dependency(mx_formats_kernel<IN, FMT>, dim3(grid), dim3(kThreadsF), 0, st,
+                                             static_cast<const uint4 *>(in), static_cast<uint8_t *>(payload),
+                                             static_cast<uint8_t *>(scales), nchunks, kblocks));
 }
 
 template <int IN>

@@ -86,6 +86,10 @@ rowwise_regs_kernel(const uint4 *__restrict__ in, uint8_t *__restrict__ out, flo
   using R = RowIn<IN>;
   constexpr int kTeam = 32 * TEAM_WARPS;
   __shared__ float smem32[32];
+  // programmatic dependent launch, both ways (see dtq_device.cuh): blocks may become resident under the tail of the
+  // kernel before this one, and what is queued behind this one under its own tail
+  pdl_launch_dependents();
+  pdl_wait();
   int64_t row;
   int t;
   if constexpr (TEAM_WARPS == 1) {
@@ -181,9 +185,9 @@ int launch_regs(const void *in, void *out, float *amax_out, float *scale_out, in
                 cudaStream_t st) {
   const unsigned grid = static_cast<unsigned>(TEAM_WARPS == 1 ? ceil_div64(rows, kWarps) : rows);
   const int threads = TEAM_WARPS == 1 ? kThreads : 32 * TEAM_WARPS;
-  rowwise_regs_kernel<IN, OUT, CHUNKS, TEAM_WARPS><<<grid, threads, 0, st>>>(
-      static_cast<const uint4 *>(in), static_cast<uint8_t *>(out), amax_out, scale_out, rows, chunks_per_row);
-  return cuda_status(cudaGetLastError());
+  return cuda_status(launch_after_dependency(rowwise_regs_kernel<IN, OUT, CHUNKS, TEAM_WARPS>, dim3(grid), dim3(threads), 0, st,
+                                             static_cast<const uint4 *>(in), static_cast<uint8_t *>(out), amax_out, scale_out,
+                                             rows, chunks_per_row));
 }
 
 // Smallest team that keeps a thread at <= 4 chunks (64 bytes in flight); the largest team may
