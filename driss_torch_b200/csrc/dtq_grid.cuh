@@ -110,6 +110,14 @@ struct PeerExchange {
 __device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long *p) {
   unsigned long long v;
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -126,18 +134,20 @@ __device__ __forceinline__ unsigned int peer_exchange_max(const PeerExchange &px
   unsigned int value = 0;
   bool mine_ok = true;
   if (lane < px.world) {
-    st_release_sys(px.buffer[lane] + parity * kMaxPeers + px.rank,
+    // The 64-bit word {epoch, value} is the whole message: one store, one load, nothing else to order against it
+    // (a release / acquire pair at system scope costs a fence on each side of the link).
+    st_relaxed_sys(px.buffer[lane] + parity * kMaxPeers + px.rank,
                    (static_cast<unsigned long long>(px.epoch) << 32) | local_bits);
     const unsigned long long *mine = px.buffer[px.rank] + parity * kMaxPeers + lane;
     unsigned int spins = 0;
-    unsigned long long v = ld_acquire_sys(mine);
+    unsigned long long v = ld_relaxed_sys(mine);
     while (static_cast<unsigned int>(v >> 32) != px.epoch) {
       if (++spins > px.spin_limit) {
         mine_ok = false;
         break;
       }
       __nanosleep(40);
-      v = ld_acquire_sys(mine);
+      v = ld_relaxed_sys(mine);
     }
     value = static_cast<unsigned int>(v);
   }
