@@ -236,6 +236,48 @@ def gemm_table(dev, iters: int, warmup: int = 3):
         rows.append(d)
         del pa, pb, sa, sb, out
     torch.cuda.empty_cache()
+
+    # sweep_mm: the row-wise scaled fp8 GEMM behind the row-wise quantisation.  The reference's kernels for it are
+    # Hopper-only, so the comparison is the library's row-wise scaled matmul (torch._scaled_mm -> cuBLASLt), same
+    # operands and scales, where this torch build has one for the device.
+    for (m, n, k) in [(8192, 8192, 8192), (16384, 8192, 4096)]:
+        x = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
+        w = torch.randn(n, k, generator=gen, device=dev).to(torch.bfloat16)
+        xq, _, xs = dtq.dynamic_scaled_quant_rowwise(x, E4M3)
+        wq, _, ws_ = dtq.dynamic_scaled_quant_rowwise(w, E4M3)
+        x_deq, w_deq = (1.0 / xs).reshape(m).contiguous(), (1.0 / ws_).reshape(n).contiguous()
+        del x, w
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        time.sleep(0.5)
+        lib = None
+        try:
+            got = torch._scaled_mm(xq, wq.t(), x_deq.reshape(m, 1), w_deq.reshape(1, n), out_dtype=torch.bfloat16)
+            lib = lambda i: torch._scaled_mm(xq, wq.t(), x_deq.reshape(m, 1), w_deq.reshape(1, n), out_dtype=torch.bfloat16)
+            del got
+        except Exception:
+            lib = None
+        mine, theirs = [], []
+        for _ in range(2):
+            mine.append(time_rotating(lambda i: _cabi.rowwise_fp8_bf16(xq, wq, x_deq, w_deq, out=out, ws=ws), 1, iters, warmup))
+            if lib is not None:
+                theirs.append(time_rotating(lib, 1, iters, warmup))
+        ms = statistics.mean(t[0] for t in mine)
+        flops = 2.0 * m * n * k
+        d = {"config": "gemm", "op": "sweep_mm (row-wise scaled fp8 GEMM)", "shape": [m, n, k], "us": round(ms * 1e3, 2),
+             "us_single_launch": round(statistics.mean(t[1] for t in mine) * 1e3, 2),
+             "TFLOPs": round(flops / (ms * 1e-3) / 1e12, 1),
+             "note": "e4m3 x e4m3, fp32 accumulation, per-row scales of both operands applied to the accumulator, bf16 out; "
+                     "operands from dynamic_scaled_quant_rowwise; timed like the MX GEMM lines",
+             "device_status": _cabi.workspace_status(ws)}
+        if bf16_peak:
+            d["x_measured_bf16_peak"] = round(flops / (ms * 1e-3) / 1e12 / bf16_peak, 3)
+        if theirs:
+            lms = statistics.mean(t[0] for t in theirs)
+            d["library_scaled_mm_us"] = round(lms * 1e3, 2)
+            d["speedup_vs_library_scaled_mm"] = round(lms / ms, 2)
+        rows.append(d)
+        del xq, wq, xs, ws_, x_deq, w_deq, out
+    torch.cuda.empty_cache()
     return rows
 
 

@@ -261,19 +261,39 @@ struct RowwiseEpilogue {
   int bias_is_bf16;
   uint32_t operand_format_bits;  // a_format << 7 | b_format << 10 (e4m3 = 0, e5m2 = 1)
 };
-// 32 consecutive accumulator columns of one row (fp32 bit patterns) through the row-wise epilogue, in place.
-__device__ __forceinline__ void apply_rowwise(uint32_t (&v)[32], const RowwiseEpilogue &e, int64_t row, int64_t col0, int M, int N) {
-  const float xs = row < M ? __ldg(e.row_scale + row) : 0.0f;
+// What a thread of the epilogue needs of the scales for one tile, fetched BEFORE it waits for the accumulator (none of
+// it depends on the MMAs): its row's scale, and for each 32-column chunk of its columns the scale and bias of column
+// `lane` of the chunk; the value for column i of a chunk then comes from lane i by shuffle.  Columns past N get 0.
+template <int CHUNKS>
+struct RowwiseRegs {
+  float xs;
+  float cs[CHUNKS], bs[CHUNKS];
+  bool has_bias;
+};
+template <int CHUNKS>
+__device__ __forceinline__ void load_rowwise(RowwiseRegs<CHUNKS> &r, const RowwiseEpilogue &e, int64_t row, int64_t col0, int lane,
+                                             int M, int N) {
+  r.xs = row < M ? __ldg(e.row_scale + row) : 0.0f;
+  r.has_bias = e.bias != nullptr;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int64_t col = col0 + c * 32 + lane;
+    const bool live = col < N;
+    r.cs[c] = live ? __ldg(e.col_scale + col) : 0.0f;
+    r.bs[c] = 0.0f;
+    if (live && r.has_bias)
+      r.bs[c] = e.bias_is_bf16 ? __uint_as_float(uint32_t(__ldg(static_cast<const uint16_t *>(e.bias) + col)) << 16)
+                               : __ldg(static_cast<const float *>(e.bias) + col);
+  }
+}
+// 32 consecutive accumulator columns of one row (fp32 bit patterns) through the row-wise epilogue, in place:
+// bf16((acc * x_scale[row]) * w_scale[col] + bias[col]), every step rounded to fp32 as the reference's epilogue tree does.
+__device__ __forceinline__ void apply_rowwise(uint32_t (&v)[32], float xs, float cs, float bs, bool has_bias) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
-    const int64_t col = col0 + i;
-    float f = 0.0f;
-    if (col < N) {
-      f = __fmul_rn(__fmul_rn(__uint_as_float(v[i]), xs), __ldg(e.col_scale + col));
-      if (e.bias)
-        f = __fadd_rn(f, e.bias_is_bf16 ? __uint_as_float(uint32_t(__ldg(static_cast<const uint16_t *>(e.bias) + col)) << 16)
-                                        : __ldg(static_cast<const float *>(e.bias) + col));
-    }
+    float f = __fmul_rn(__fmul_rn(__uint_as_float(v[i]), xs), __shfl_sync(0xFFFFFFFFu, cs, i));
+    const float b = __shfl_sync(0xFFFFFFFFu, bs, i);
+    if (has_bias) f = __fadd_rn(f, b);
     v[i] = __float_as_uint(f);
   }
 }
@@ -452,6 +472,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int mt, nt;
       tile_coords(tile, p.m_tiles, p.n_tiles, &mt, &nt);
       const int acc = local_tile % kAcc, use = local_tile / kAcc;
+      const int64_t row = int64_t(mt) * kBM + quad * 32 + lane;
+      RowwiseRegs<kChunks> rw;
+      if constexpr (MODE == kRowwise)
+        load_rowwise<kChunks>(rw, p.rowwise, row, int64_t(nt) * kBN + half * kHalfCols, lane, p.M, p.N);
       if (!mbar_wait(&sm.tmem_full[acc], use & 1u, abort)) {
         if (lane == 0) {
           atomicExch(p.status, DTQ_ERR_TIMEOUT);
@@ -460,7 +484,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         break;
       }
       tmem_fence_after();
-      const int64_t row = int64_t(mt) * kBM + quad * 32 + lane;
       uint32_t packed[kChunks][16];  // this thread's columns of one row as bf16 pairs
 #pragma unroll
       for (int c = 0; c < kChunks; c += 2) {  // two loads in flight per wait: the accumulator is handed back sooner
@@ -471,8 +494,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_load_wait();
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-          if constexpr (MODE == kRowwise)
-            apply_rowwise(v[u], p.rowwise, row, int64_t(nt) * kBN + half * kHalfCols + (c + u) * 32, p.M, p.N);
+          if constexpr (MODE == kRowwise) apply_rowwise(v[u], rw.xs, rw.cs[c + u], rw.bs[c + u], rw.has_bias);
 #pragma unroll
           for (int i = 0; i < 16; ++i) packed[c + u][i] = pack_bf16(v[u][2 * i], v[u][2 * i + 1]);
         }
@@ -740,6 +762,9 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int tile = cluster_id; tile < total_tiles; tile += n_clusters, ++local_tile) {
       int mp, nt;
       tile_coords(tile, p.m_pairs, p.n_tiles, &mp, &nt);
+      const int64_t row = int64_t(mp) * 256 + int64_t(rank) * kBM + quad * 32 + lane;
+      RowwiseRegs<4> rw;
+      if constexpr (MODE == kRowwise) load_rowwise<4>(rw, p.rowwise, row, int64_t(nt) * kPairBN + half * 128, lane, p.M, p.N);
       if (!mbar_wait(&sm.tmem_full, local_tile & 1u, abort)) {
         if (lane == 0) {
           atomicExch(p.status, DTQ_ERR_TIMEOUT);
@@ -749,7 +774,6 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         break;
       }
       tmem_fence_after();
-      const int64_t row = int64_t(mp) * 256 + int64_t(rank) * kBM + quad * 32 + lane;
       uint32_t packed[4][16];
 #pragma unroll
       for (int c = 0; c < 4; c += 2) {  // two loads in flight per wait
@@ -760,8 +784,7 @@ mx_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tmem_load_wait();
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-          if constexpr (MODE == kRowwise)
-            apply_rowwise(v[u], p.rowwise, row, int64_t(nt) * kPairBN + half * 128 + (c + u) * 32, p.M, p.N);
+          if constexpr (MODE == kRowwise) apply_rowwise(v[u], rw.xs, rw.cs[c + u], rw.bs[c + u], rw.has_bias);
 #pragma unroll
           for (int i = 0; i < 16; ++i) packed[c + u][i] = pack_bf16(v[u][2 * i], v[u][2 * i + 1]);
         }
