@@ -161,3 +161,30 @@ def test_mx_fp4_bf16_equals_the_reference_kernel_bit_for_bit(ref_gemm_ops, size,
     want = ref_gemm_ops.mx_fp4_bf16(pa, pb.t(), sa, sb)
     got = _cabi.mx_fp8_bf16(pa, pb, sa, sb, kernel=kernel, fp4=True)
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("kernel", ["pair", "wide", "narrow"])
+def test_mx_fp8_bf16_special_values_equal_the_reference_kernel(ref_gemm_ops, kernel):
+    # Every e4m3 byte pattern as an operand (the two NaN encodings included) and every E8M0 scale byte (0 = 2^-127 and
+    # 255 = NaN included), at random positions: the same tensor-core instructions see the same inputs in both kernels,
+    # so the outputs -- infinities, NaNs and their bf16 encodings included -- are the same bits.
+    from driss_torch_b200 import _cabi
+
+    m, n, k = 256, 512, 512
+    g = torch.Generator().manual_seed(99)
+    a = torch.randint(0, 256, (m, k), generator=g, dtype=torch.int32).to(torch.uint8)
+    b = torch.randint(0, 256, (n, k), generator=g, dtype=torch.int32).to(torch.uint8)
+    # keep most rows free of NaN operands so that finite results are compared too
+    a[16:] = torch.where((a[16:] & 0x7F) == 0x7F, torch.zeros_like(a[16:]), a[16:])
+    b[16:] = torch.where((b[16:] & 0x7F) == 0x7F, torch.zeros_like(b[16:]), b[16:])
+    sa = torch.randint(110, 140, (m, k // 32), generator=g, dtype=torch.int32).to(torch.uint8)
+    sb = torch.randint(110, 140, (n, k // 32), generator=g, dtype=torch.int32).to(torch.uint8)
+    sa[3, 2], sa[40, 0], sb[5, 1], sb[77, 3] = 255, 0, 255, 0
+    sab = qo.to_blocked(sa, m, k // 32).cuda().view(torch.float8_e8m0fnu)
+    sbb = qo.to_blocked(sb, n, k // 32).cuda().view(torch.float8_e8m0fnu)
+    ad, bd = a.cuda().view(torch.float8_e4m3fn), b.cuda().view(torch.float8_e4m3fn)
+    want = ref_gemm_ops.mx_fp8_bf16(ad, bd.t(), sab, sbb)
+    got = _cabi.mx_fp8_bf16(ad, bd, sab, sbb, kernel=kernel)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16)), \
+        f"{(got.view(torch.int16) != want.view(torch.int16)).sum().item()} of {got.numel()} outputs differ"
+    assert got.float().isnan().any() and got.float().isfinite().any()
