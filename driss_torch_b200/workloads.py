@@ -59,6 +59,9 @@ def make_cfg2(rows=None, cols=None, device="cpu") -> torch.Tensor:
 
 
 def make_cfg3(rows=None, cols=None, device="cpu") -> torch.Tensor:
+    """Lognormal magnitudes, random signs, 1 % exact zeros.  On the CPU two calls can differ in the last bit of a few
+    elements (``exp`` runs as vector or scalar code depending on where its buffer starts): generate once and hand
+    the same tensor to everything that is to be compared.  The same holds for ``make_cfg4`` (``pow``)."""
     w = WORKLOADS["cfg3"]
     g = _gen(w.seed, device)
     shape = (rows or w.rows, cols or w.cols)
